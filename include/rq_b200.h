@@ -1,0 +1,171 @@
+/*
+ * rq_b200.h -- C ABI of the B200 (sm_100a) packed-KV kernels.
+ *
+ * Two operators, the same two the reference's extension module `residual_quantization._cuda`
+ * exports (plugins/residual_quantization/csrc/dispatch/binding.cpp:19-37):
+ *
+ *   rq_quantize   replaces  quantize()   plugins/residual_quantization/csrc/common/api.h:22-31
+ *                                        (quantize/api.cpp:8-95, quantize/launch.cuh:45-86)
+ *   rq_attention  replaces  attention()  plugins/residual_quantization/csrc/common/api.h:11-20
+ *                                        (attention/api.cpp:8-115, attention/launch.cuh:34-132)
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless stated otherwise, `stream` is a
+ * cudaStream_t passed as void*.  Nothing here allocates, synchronizes or reads device memory on the host,
+ * so both calls can be captured in a CUDA graph and replayed with changing slot mappings, sequence lengths
+ * and block tables.  All functions return RQ_OK (0) or a negative RqStatus; they never throw and never abort.
+ * rq_last_error() gives a human-readable message for the calling thread's most recent failure.
+ *
+ * Page layout (identical to the reference, plugins/residual_quantization/csrc/common/cache.cuh:10-106):
+ * the cache is uint8 [2][num_blocks][heads][page_tokens][page_width], plane 0 = K, plane 1 = V.  One
+ * (plane, block, head) page is page_tokens*page_width bytes, record-major: record r (loop order) occupies
+ * bytes [P*off_r, P*off_{r+1}); inside a record: codes [P][D*bits/8], FP8-e4m3 scales [P][D/group], FP8-e4m3
+ * offsets [P][D/group], bf16 alpha [P].  Four consecutive channels share a storage word (uint8 for INT2,
+ * little-endian uint16 for INT4), channel c at bit (c%4)*bits.
+ */
+#ifndef RQ_B200_H_
+#define RQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RQ_MAX_RECORDS 8
+
+typedef enum RqStatus {
+    RQ_OK = 0,
+    RQ_ERR_INVALID_ARGUMENT = -1, /* a shape, pointer, alignment or enum is wrong (the TORCH_CHECKs of api.cpp) */
+    RQ_ERR_UNSUPPORTED = -2,      /* no kernel is compiled for this (head_dim, records, mode, ...) combination
+                                     (kernel_registry.h:66-72 raises the same way) */
+    RQ_ERR_WORKSPACE = -3,        /* workspace missing, misaligned or too small */
+    RQ_ERR_CUDA = -4,             /* a CUDA runtime call failed; rq_last_error() holds its message */
+    RQ_ERR_DEVICE_TIMEOUT = -5    /* reported by rq_attention_status(): a bounded on-chip wait gave up */
+} RqStatus;
+
+typedef enum RqReferenceMode { RQ_REFERENCE_ANCHOR = 0, RQ_REFERENCE_ADJACENT = 1 } RqReferenceMode; /* common/types.h:3 */
+typedef enum RqCoefficient { RQ_COEFF_UNIT = 0, RQ_COEFF_NORM = 1, RQ_COEFF_LS = 2 } RqCoefficient;  /* quantize/types.h:4 */
+
+/* Where the least-squares coefficient and the residual are formed.
+ * KERNEL:      in rotated coordinates against the bf16 reconstruction of the anchor, as the reference's CUDA
+ *              quantizer does (quantize/kernel.cuh:76-120).
+ * CALIBRATION: in original coordinates with bf16 prediction and bf16 residual target, as the reference's
+ *              PyTorch statement does (scripts/calibration/quantization.py:16-71).
+ * Both store the same fields in the same layout. */
+typedef enum RqChain { RQ_CHAIN_KERNEL = 0, RQ_CHAIN_CALIBRATION = 1 } RqChain;
+
+typedef enum RqRotationKind {
+    RQ_ROTATION_NONE = 0,
+    /* R[h] = diag(sign[h]) * H_D * scale, y = x @ R.  `data` = uint32 [heads][head_dim/32], bit c%32 of word c/32
+     * set when sign[h][c] is -1.  H_128 is the Sylvester matrix, H_96 = Paley-12 (x) Sylvester-8
+     * (scripts/calibration/rotation_math.py:6-32). */
+    RQ_ROTATION_SIGNED_HADAMARD = 1,
+    /* dense fp16 [heads][head_dim][head_dim], y = x @ R (common/api.h:42-55). */
+    RQ_ROTATION_DENSE_FP16 = 2
+} RqRotationKind;
+
+typedef struct RqRotation {
+    int32_t kind;     /* RqRotationKind */
+    float scale;      /* SIGNED_HADAMARD: magnitude of the matrix entries, e.g. (float)fp16(1/sqrt(D)) */
+    const void* data; /* see RqRotationKind */
+} RqRotation;
+
+/* One KV group: its records in loop order and how residuals refer to the anchor
+ * (common/cache.cuh:10-67, the registry key of dispatch/kernel_registry.h:16-18). */
+typedef struct RqGroupSpec {
+    int32_t num_records;
+    int32_t bits[RQ_MAX_RECORDS];       /* 2 or 4 */
+    int32_t group_size[RQ_MAX_RECORDS]; /* 16 or 32 */
+    int32_t anchor_index;
+    int32_t reference_mode; /* RqReferenceMode */
+    int32_t heads;
+    int32_t head_dim;    /* 128 or 96 */
+    int32_t page_tokens; /* 16 or 32 */
+} RqGroupSpec;
+
+/* Bytes per token of one (head, plane): sum over records of D*bits/8 + 2*D/group + 2
+ * (cache.cuh:14-17; install_model.py:34-38 computes the same).  Negative RqStatus on a bad spec. */
+int32_t rq_page_width(const RqGroupSpec* spec);
+/* Byte offset (per token) of record `index` inside a page row; index == num_records gives the page width. */
+int32_t rq_record_offset(const RqGroupSpec* spec, int32_t index);
+
+typedef struct RqQuantizeArgs {
+    RqGroupSpec spec;
+    /* One K and one V tensor per record, bf16 [>= num_tokens][heads][head_dim], last two dims packed,
+     * row stride in ELEMENTS (common/api.h:33-40). */
+    const void* key[RQ_MAX_RECORDS];
+    const void* value[RQ_MAX_RECORDS];
+    int64_t key_stride[RQ_MAX_RECORDS];
+    int64_t value_stride[RQ_MAX_RECORDS];
+    void* kv_cache;          /* uint8 [2][num_blocks][heads][page_tokens][page_width], contiguous */
+    int64_t num_blocks;
+    int64_t plane_stride;    /* bytes between plane 0 and plane 1 (kv_cache.stride(0)) */
+    const int64_t* slot_mapping; /* [num_tokens]; slot = block*page_tokens + offset; negative = skip */
+    int64_t num_tokens;
+    RqRotation key_rotation;
+    RqRotation value_rotation;
+    const float* key_mean;   /* fp32 [num_records][heads][head_dim] in rotated coordinates, or NULL */
+    int32_t coefficient;     /* RqCoefficient */
+    int32_t chain;           /* RqChain */
+    void* stream;
+} RqQuantizeArgs;
+
+/* Rotate, quantize and bit-pack the K/V rows of every record of a group into their pages.  One launch. */
+int32_t rq_quantize(const RqQuantizeArgs* args);
+
+typedef struct RqAttentionArgs {
+    RqGroupSpec spec;
+    /* bf16 [num_query_rows][heads][head_dim], last two dims packed, row strides in ELEMENTS.
+     * key/value hold the live (current) token of every query row (attention/types.h:31-40). */
+    const void* query;
+    const void* key;
+    const void* value;
+    void* output;
+    int64_t query_stride, key_stride, value_stride, output_stride;
+    int32_t num_query_rows; /* rows of the tensors (graph capture size); rows >= query_start_loc[num_requests]
+                               are padding and are left untouched (prepare.cuh:405-406, merge.cuh:16) */
+    const void* kv_cache;
+    int64_t num_blocks;
+    int64_t plane_stride;
+    const int32_t* query_start_loc; /* [num_requests + 1] */
+    const int32_t* seq_lens;        /* [num_requests]; a row attends to seq_len-1 cached tokens + the live one */
+    const int32_t* block_table;     /* [>= num_requests][block_table_stride] */
+    int32_t num_requests;
+    int32_t block_table_stride;
+    int32_t max_blocks_per_request; /* block_table.size(1) */
+    RqRotation key_rotation;
+    RqRotation value_rotation;      /* kind NONE when the model's weights absorbed it (weights.py:9-37) */
+    const float* key_mean;          /* fp32 [num_records][heads][head_dim], rotated coordinates, or NULL */
+    int32_t loop_index;             /* which record of the group this layer slot reads, 0 <= loop < num_records */
+    int32_t num_splits;             /* KV partitions per query row; 0 = let rq_attention_default_splits choose */
+    void* workspace;                /* rq_attention_workspace_bytes() bytes, 256-byte aligned, zeroed once with
+                                       rq_attention_workspace_init() before its first use */
+    size_t workspace_bytes;
+    void* stream;
+} RqAttentionArgs;
+
+/* Partition count the library would pick for this shape on the current device (a pure host function of its
+ * arguments and the SM count, so it is stable across CUDA-graph replays). */
+int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32_t max_blocks_per_request,
+                                    int32_t page_tokens);
+/* Bytes of scratch one rq_attention call needs: per-partition (max, denominator, value sums), one arrival
+ * counter per (row, head) and a status word.  The reference allocates the equivalent per call
+ * (attention/launch.cuh:85-98). */
+size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits);
+/* Zero the counters and the status word (asynchronous, on `stream`).  Needed once per workspace; every call
+ * leaves the counters zero again. */
+int32_t rq_attention_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+/* Split-KV online-softmax decode attention over the packed pages.  One launch. */
+int32_t rq_attention(const RqAttentionArgs* args);
+/* Synchronizes `stream` and reads the workspace status word: RQ_OK, or RQ_ERR_DEVICE_TIMEOUT if a bounded
+ * wait inside the kernel ever gave up since the last init (outputs of that call are then undefined). */
+int32_t rq_attention_status(const void* workspace, void* stream);
+
+const char* rq_last_error(void);
+const char* rq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RQ_B200_H_ */

@@ -1,0 +1,691 @@
+// Packed paged decode attention (anchor reference mode), one launch per call.
+//
+// Replaces the reference's three kernels -- attention_prepare_kernel, attention_kernel, attention_merge_kernel
+// (plugins/residual_quantization/csrc/attention/prepare.cuh:391-430, compute.cuh:226-727, merge.cuh:9-84) --
+// and its page staging (attention/async_copy.cuh:109-168).
+//
+// Shape of the computation
+//   CTA  = one (query row, KV partition, head); grid = rows * splits * heads, heads fastest so that CTAs that
+//          run together read neighbouring pages of the same block.
+//   warp = an independent consumer of every 4th page of the partition with its OWN ring of shared-memory
+//          stages, filled by 1-D bulk async copies (cp.async.bulk + mbarrier complete_tx) that lane 0 issues
+//          STAGES pages ahead.  There is no CTA-wide barrier inside the page loop.
+//   lane = (token slot, 32-channel slice): 4 lanes per token, 8 tokens per warp step.  A slice is exactly one
+//          INT4 g32 anchor group, so scale/offset handling is per lane, not per channel.
+//   maths: codes are expanded to half2 pairs with the 0x6400 magic-number trick (no int->float conversions),
+//          K: per-slice dot products against the rotated, pre-scaled query, factored as
+//             scale * sum(q*code) + offset * sum(q);
+//          softmax: one online-softmax stream per 4-lane token slot (fp32 max/denominator, base-2 exponent);
+//          V: half2 FMAs with the probability folded into the group scale, flushed to fp32 every 8 tokens; the
+//             offset part is accumulated once per group instead of per channel.
+//   merge: each warp folds its 8 streams, the CTA folds its 4 warps, and -- when the row has several
+//          partitions -- the LAST CTA to arrive (one atomic ticket per (row, head)) folds the partitions, adds the
+//          live token, undoes an explicit value rotation and stores bf16.  No second launch, no spin wait.
+//
+// The query rotation (signed Walsh-Hadamard) is fused into the prologue of every CTA (128 values, one warp).
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel raises the workspace status word, drains what it
+// can and returns.
+#include <atomic>
+
+#include "rq_common.cuh"
+#include "rq_kernels.h"
+
+namespace rq {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// P[i][j] == -1  <=>  bit j of kPaleyRow[i]  <=>  bit i of kPaleyCol[j]
+__constant__ uint32_t kPaleyRowA[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0xed0, 0xda2,
+                                        0xb46, 0x68e, 0xd1c, 0xa3a, 0, 0, 0, 0};
+__constant__ uint32_t kPaleyColA[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc,
+                                        0x5b8, 0xb70, 0x6e2, 0xdc4, 0, 0, 0, 0};
+
+template <int D_, int AB_, int AG_, int RB_, int RG_, int P_, bool MEAN_>
+struct Config {
+    static constexpr int D = D_, AB = AB_, AG = AG_, RB = RB_, RG = RG_, P = P_;
+    static constexpr bool kMean = MEAN_, kResidual = RB_ != 0;
+    static_assert(AB == 4 && AG == 32, "anchor record must be INT4 with 32-channel groups");
+    static_assert(RB == 0 || RB == 2, "residual record must be INT2");
+    static_assert(D == 128 || D == 96, "head_dim 128 or 96");
+    static constexpr int kAnchorCode = D * AB / 8, kAnchorGroups = D / AG;
+    static constexpr int kAnchorBytes = P * (kAnchorCode + 2 * kAnchorGroups);  // staged without its alpha column
+    static constexpr int kResidualCode = kResidual ? D * RB / 8 : 0;
+    static constexpr int kResidualGroups = kResidual ? D / RG : 0;
+    static constexpr int kResidualBytes = kResidual ? P * (kResidualCode + 2 * kResidualGroups + 2) : 0;
+    static constexpr int kPlaneBytes = kAnchorBytes + kResidualBytes;
+    static constexpr int kStageBytes = 2 * kPlaneBytes;
+    static constexpr int kStagesRaw = 14336 / kStageBytes;
+    static constexpr int kStages = kStagesRaw < 2 ? 2 : (kStagesRaw > 6 ? 6 : kStagesRaw);
+    static constexpr int kRingBytes = kStages * kStageBytes;
+    static_assert(kAnchorBytes % 16 == 0 && kResidualBytes % 16 == 0, "bulk copies need 16-byte multiples");
+    static_assert(kRingBytes >= 32 * 33 * 4, "the ring doubles as the warp's merge scratch");
+    // shared memory map (bytes)
+    static constexpr int kOffRing = 0;
+    static constexpr int kOffQuery = kOffRing + kWarps * kRingBytes;       // float[D]
+    static constexpr int kOffWarpAcc = kOffQuery + D * 4;                  // float[kWarps][D]
+    static constexpr int kOffWarpStat = kOffWarpAcc + kWarps * D * 4;      // float[kWarps][2] + float misc[8]
+    static constexpr int kOffBarriers = kOffWarpStat + 64;                 // uint64[kWarps][kStages]
+    static constexpr int kSmemBytes = kOffBarriers + kWarps * kStages * 8;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Bounded wait.  false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+    return d;
+}
+__device__ __forceinline__ __half2 as_half2(uint32_t bits) { return *reinterpret_cast<const __half2*>(&bits); }
+
+// Eight INT4 codes of one 32-bit word -> four half2 pairs (channel i, channel i+4), i = 0..3.
+__device__ __forceinline__ void expand_int4(uint32_t word, __half2 (&out)[4]) {
+    const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f), k16th = __float2half2_rn(0.0625f);
+    const uint32_t upper = word >> 8;
+    out[0] = __hsub2(as_half2((word & 0x000F000Fu) | 0x64006400u), k1024);
+    out[1] = __hfma2(as_half2((word & 0x00F000F0u) | 0x64006400u), k16th, __hneg2(k64));
+    out[2] = __hsub2(as_half2((upper & 0x000F000Fu) | 0x64006400u), k1024);
+    out[3] = __hfma2(as_half2((upper & 0x00F000F0u) | 0x64006400u), k16th, __hneg2(k64));
+}
+// Sixteen INT2 codes of one 32-bit word -> eight half2 pairs: out[4*b + i] = (channel 8b+i, channel 8b+i+4).
+__device__ __forceinline__ void expand_int2(uint32_t word, __half2 (&out)[8]) {
+    const __half2 k1024 = __float2half2_rn(1024.f);
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        const uint32_t t = prmt(word, 0u, b == 0 ? 0x4140u : 0x4342u);  // bytes [2b, 0, 2b+1, 0]
+        out[4 * b + 0] = __hsub2(as_half2((t & 0x00030003u) | 0x64006400u), k1024);
+        out[4 * b + 1] = __hfma2(as_half2((t & 0x000C000Cu) | 0x64006400u), __float2half2_rn(0.25f), __float2half2_rn(-256.f));
+        out[4 * b + 2] = __hfma2(as_half2((t & 0x00300030u) | 0x64006400u), __float2half2_rn(0.0625f), __float2half2_rn(-64.f));
+        out[4 * b + 3] = __hfma2(as_half2((t & 0x00C000C0u) | 0x64006400u), __float2half2_rn(0.015625f), __float2half2_rn(-16.f));
+    }
+}
+__device__ __forceinline__ float half2_sum(__half2 v) { return __low2float(v) + __high2float(v); }
+
+// Rotated, pre-scaled query of this (row, head) into shared memory: qs[c] = (q @ R)[c] * D^-1/2 * log2(e).
+// Executed by warp 0; lane L owns channels 4L .. 4L+3.
+template <int D>
+__device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs) {
+    const int lane = threadIdx.x & 31;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool owner = 4 * lane < D;
+    if (owner) {
+        const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + 4 * lane;
+        const uint2 raw = *reinterpret_cast<const uint2*>(q);
+        x[0] = bf16_bits_to_float(raw.x & 0xffffu);
+        x[1] = bf16_bits_to_float(raw.x >> 16);
+        x[2] = bf16_bits_to_float(raw.y & 0xffffu);
+        x[3] = bf16_bits_to_float(raw.y >> 16);
+    }
+    float scale = rsqrtf(static_cast<float>(D)) * kLog2e;
+    if (p.key_sign != nullptr) {
+        if (owner) {
+            const uint32_t sign = p.key_sign[head * (D / 32) + (lane >> 3)] >> (4 * (lane & 7));
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if ((sign >> i) & 1u) x[i] = -x[i];
+        }
+        butterflies_in_lane<4>(x);
+        butterfly_across_lanes<4>(x, 1, (lane & 1) != 0);
+        if (D == 128) {
+            butterfly_across_lanes<4>(x, 2, (lane & 2) != 0);
+            butterfly_across_lanes<4>(x, 4, (lane & 4) != 0);
+            butterfly_across_lanes<4>(x, 8, (lane & 8) != 0);
+            butterfly_across_lanes<4>(x, 16, (lane & 16) != 0);
+        } else {
+            const uint32_t mask = kPaleyColA[(lane >> 1) & 15];
+            float out[4];
+#pragma unroll
+            for (int a = 0; a < 12; ++a) {
+                const bool negative = (mask >> a) & 1u;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float v = __shfl_sync(kFullMask, x[i], 2 * a + (lane & 1));
+                    const float t = negative ? -v : v;
+                    out[i] = a == 0 ? t : out[i] + t;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[i] = out[i];
+        }
+        scale *= p.key_rscale;
+    }
+    if (owner) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qs[4 * lane + i] = x[i] * scale;
+    }
+}
+
+// Undo an explicit value rotation on the history sum: h <- ((h H^T) * rscale) * sign.  Warp 0, in place in smem.
+template <int D>
+__device__ __forceinline__ void unrotate_history(const AttentionParams& p, int head, float* hist) {
+    const int lane = threadIdx.x & 31;
+    const bool owner = 4 * lane < D;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (owner) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = hist[4 * lane + i];
+    }
+    butterflies_in_lane<4>(x);
+    butterfly_across_lanes<4>(x, 1, (lane & 1) != 0);
+    if (D == 128) {
+        butterfly_across_lanes<4>(x, 2, (lane & 2) != 0);
+        butterfly_across_lanes<4>(x, 4, (lane & 4) != 0);
+        butterfly_across_lanes<4>(x, 8, (lane & 8) != 0);
+        butterfly_across_lanes<4>(x, 16, (lane & 16) != 0);
+    } else {
+        const uint32_t mask = kPaleyRowA[(lane >> 1) & 15];
+        float out[4];
+#pragma unroll
+        for (int a = 0; a < 12; ++a) {
+            const bool negative = (mask >> a) & 1u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float v = __shfl_sync(kFullMask, x[i], 2 * a + (lane & 1));
+                const float t = negative ? -v : v;
+                out[i] = a == 0 ? t : out[i] + t;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = out[i];
+    }
+    if (owner) {
+        const uint32_t sign = p.value_sign[head * (D / 32) + (lane >> 3)] >> (4 * (lane & 7));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float v = x[i] * p.value_rscale;
+            hist[4 * lane + i] = ((sign >> i) & 1u) ? -v : v;
+        }
+    }
+}
+
+template <class C>
+__global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_constant__ AttentionParams p) {
+    constexpr int D = C::D, P = C::P;
+    extern __shared__ __align__(128) uint8_t smem[];
+    float* qs = reinterpret_cast<float*>(smem + C::kOffQuery);
+    float* warp_acc = reinterpret_cast<float*>(smem + C::kOffWarpAcc);
+    float* warp_stat = reinterpret_cast<float*>(smem + C::kOffWarpStat);  // [w][2] then misc at [8..15]
+    uint64_t* barriers = reinterpret_cast<uint64_t*>(smem + C::kOffBarriers);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int heads = p.heads, splits = p.splits;
+    const int head = blockIdx.x % heads;
+    const int split = (blockIdx.x / heads) % splits;
+    const int row = blockIdx.x / (heads * splits);
+
+    // ---- which request, which pages -----------------------------------------------------------------
+    const int num_requests = p.num_requests;
+    if (row >= p.query_start_loc[num_requests]) return;  // graph padding: leave the output row untouched
+    int request = min(row, num_requests - 1);
+    if (!(p.query_start_loc[request] <= row && row < p.query_start_loc[request + 1])) {
+        int lo = 0, hi = num_requests - 1;  // largest r with query_start_loc[r] <= row
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (p.query_start_loc[mid] <= row) lo = mid; else hi = mid - 1;
+        }
+        request = lo;
+    }
+    const int history = max(0, p.seq_lens[request] - 1);
+    const int pages = (history + P - 1) / P;
+    const int chunk = (pages + splits - 1) / splits;
+    const int page_begin = min(pages, split * chunk), page_end = min(pages, page_begin + chunk);
+    // pages of this warp: page_begin + warp, + kWarps, ...
+    const int warp_pages = page_begin + warp < page_end ? (page_end - page_begin - warp + kWarps - 1) / kWarps : 0;
+    const int32_t* table = p.block_table + static_cast<int64_t>(request) * p.block_table_stride;
+
+    // ---- per-warp ring: init barriers, start the first copies ----------------------------------------
+    uint8_t* ring = smem + C::kOffRing + warp * C::kRingBytes;
+    const uint32_t ring_addr = smem_addr(ring);
+    const uint32_t bar_addr = smem_addr(barriers + warp * C::kStages);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < C::kStages; ++s) mbar_init(bar_addr + 8 * s, 1);
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    const int64_t page_bytes = static_cast<int64_t>(P) * p.page_width;
+    const uint8_t* head_base = p.cache + head * page_bytes;
+    const int64_t block_bytes = heads * page_bytes;
+    const int anchor_at = P * p.anchor_offset, residual_at = P * p.residual_offset;
+    auto issue = [&](int block, int stage) {  // lane 0 only
+        const uint8_t* k_page = head_base + block * block_bytes;
+        const uint8_t* v_page = k_page + p.plane_stride;
+        const uint32_t dst = ring_addr + stage * C::kStageBytes, bar = bar_addr + 8 * stage;
+        mbar_expect_tx(bar, C::kStageBytes);
+        bulk_load(dst, k_page + anchor_at, C::kAnchorBytes, bar);
+        if (C::kResidual) bulk_load(dst + C::kAnchorBytes, k_page + residual_at, C::kResidualBytes, bar);
+        bulk_load(dst + C::kPlaneBytes, v_page + anchor_at, C::kAnchorBytes, bar);
+        if (C::kResidual)
+            bulk_load(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, C::kResidualBytes, bar);
+    };
+    // block ids of this warp's next 32 pages, one per lane
+    int batch_base = 0;
+    int my_block = 0;
+    auto load_batch = [&](int base) {
+        batch_base = base;
+        my_block = base + lane < warp_pages ? table[page_begin + warp + kWarps * (base + lane)] : 0;
+    };
+    load_batch(0);
+    int issued = 0;
+    {
+        const int first = min(C::kStages, warp_pages);
+        for (; issued < first; ++issued) {
+            const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
+            if (lane == 0) issue(block, issued);
+        }
+    }
+
+    // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
+    if (warp == 0) prepare_query<D>(p, row, head, qs);
+    __syncthreads();
+
+    const int j = lane & 3;              // slice: channels 32j .. 32j+31
+    const bool slice_ok = 32 * j < D;
+    const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
+    __half2 q2[16];                      // pair 4b+i = (channel 8b+i, channel 8b+i+4) of the slice
+    float qsum0 = 0.f, qsum1 = 0.f;      // sum of the (half-rounded) query over channels 0..15 / 16..31 of the slice
+    float qmean = 0.f;                   // sum_c q[c] * mean[anchor][c] over the slice (residual loops with a mean)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c0 = 32 * js + 8 * b + i;
+            const __half2 pair = slice_ok ? __floats2half2_rn(qs[c0], qs[c0 + 4]) : __float2half2_rn(0.f);
+            q2[4 * b + i] = pair;
+            const float s = half2_sum(pair);
+            if (b < 2) qsum0 += s; else qsum1 += s;
+            if (C::kMean && C::kResidual && slice_ok) {
+                const float* mean = p.mean + (static_cast<int64_t>(p.anchor_index) * heads + head) * D;
+                qmean += __low2float(pair) * mean[c0] + __high2float(pair) * mean[c0 + 4];
+            }
+        }
+    }
+    const float qsum = qsum0 + qsum1;
+
+    // ---- page loop -----------------------------------------------------------------------------------
+    float m = -INFINITY, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
+    __half2 acc_h[16];
+    float acc[32];
+    float acc_off0 = 0.f, acc_off1 = 0.f;  // offset part of V for channels 0..15 / 16..31 of the slice
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc_h[i] = __float2half2_rn(0.f);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    int pending = 0;
+    bool failed = false;
+    const int slot = lane >> 2;          // token slot 0..7 inside a warp step
+
+    auto flush = [&]() {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float2 f = __half22float2(acc_h[i]);
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
+            acc_h[i] = __float2half2_rn(0.f);
+        }
+        pending = 0;
+    };
+
+    int stage = 0;
+    uint32_t parity = 0;
+    int it_done = 0;  // pages fully consumed
+    for (int it = 0; it < warp_pages; ++it) {
+        if (!mbar_wait(bar_addr + 8 * stage, parity)) failed = true;
+        if (__any_sync(kFullMask, failed)) { failed = true; break; }
+        const uint8_t* k_anchor = ring + stage * C::kStageBytes;
+        const uint8_t* k_residual = k_anchor + C::kAnchorBytes;
+        const uint8_t* v_anchor = k_anchor + C::kPlaneBytes;
+        const uint8_t* v_residual = v_anchor + C::kAnchorBytes;
+        const int first_token = (page_begin + warp + kWarps * it) * P;
+        const int valid = min(P, history - first_token);
+
+#pragma unroll
+        for (int sub = 0; sub < P / 8; ++sub) {
+            const int t = sub * 8 + slot;
+            const bool live_token = t < valid;
+            // ---------------- K: score of token t against the query slice ----------------
+            float part;
+            float alpha = 1.f;
+            {
+                const uint4 codes = *reinterpret_cast<const uint4*>(k_anchor + t * C::kAnchorCode + 16 * js);
+                const uint8_t* meta = k_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
+                const float scale = fp8_decode(meta[0]), offset = fp8_decode(meta[P * C::kAnchorGroups]);
+                const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+                __half2 d0 = __float2half2_rn(0.f), d1 = __float2half2_rn(0.f);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    __half2 c[4];
+                    expand_int4(words[w], c);
+                    d0 = __hfma2(q2[4 * w + 0], c[0], d0);
+                    d1 = __hfma2(q2[4 * w + 1], c[1], d1);
+                    d0 = __hfma2(q2[4 * w + 2], c[2], d0);
+                    d1 = __hfma2(q2[4 * w + 3], c[3], d1);
+                }
+                part = scale * (half2_sum(d0) + half2_sum(d1)) + offset * qsum;
+            }
+            if (C::kResidual) {
+                alpha = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(
+                    k_residual + P * (C::kResidualCode + 2 * C::kResidualGroups) + 2 * t));
+                if (C::kMean) part += qmean;
+                part *= alpha;
+                const uint2 codes = *reinterpret_cast<const uint2*>(k_residual + t * C::kResidualCode + 8 * js);
+                __half2 c[8];
+                __half2 d0 = __float2half2_rn(0.f), d1 = __float2half2_rn(0.f);
+                expand_int2(codes.x, c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d0 = __hfma2(q2[i], c[i], d0);
+                expand_int2(codes.y, c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d1 = __hfma2(q2[8 + i], c[i], d1);
+                const uint8_t* meta = k_residual + P * C::kResidualCode + t * C::kResidualGroups;
+                if (C::RG == 32) {
+                    const float scale = fp8_decode(meta[js]), offset = fp8_decode(meta[P * C::kResidualGroups + js]);
+                    part += scale * (half2_sum(d0) + half2_sum(d1)) + offset * qsum;
+                } else {
+                    const float s0 = fp8_decode(meta[2 * js]), s1 = fp8_decode(meta[2 * js + 1]);
+                    const float o0 = fp8_decode(meta[P * C::kResidualGroups + 2 * js]);
+                    const float o1 = fp8_decode(meta[P * C::kResidualGroups + 2 * js + 1]);
+                    part += s0 * half2_sum(d0) + o0 * qsum0 + s1 * half2_sum(d1) + o1 * qsum1;
+                }
+            }
+            part += __shfl_xor_sync(kFullMask, part, 1);
+            part += __shfl_xor_sync(kFullMask, part, 2);
+            const float score = live_token ? part : -INFINITY;
+
+            // ---------------- online softmax of the token slot ----------------
+            if (score > m) {
+                const float f = fast_exp2(m - score);  // m == -inf gives 0
+                l *= f;
+                acc_off0 *= f;
+                acc_off1 *= f;
+                const __half2 f2 = __float2half2_rn(f);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc_h[i] = __hmul2(acc_h[i], f2);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] *= f;
+                m = score;
+            }
+            const float prob = live_token ? fast_exp2(score - m) : 0.f;
+            l += prob;
+
+            // ---------------- V: accumulate prob * V_hat[t] over the slice ----------------
+            {
+                const uint4 codes = *reinterpret_cast<const uint4*>(v_anchor + t * C::kAnchorCode + 16 * js);
+                const uint8_t* meta = v_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
+                const float pa = prob * alpha;
+                const float scale = fp8_decode(meta[0]), offset = fp8_decode(meta[P * C::kAnchorGroups]);
+                const __half2 w2 = __float2half2_rn(pa * scale);
+                const float off = pa * offset;
+                acc_off0 += off;
+                acc_off1 += off;
+                const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    __half2 c[4];
+                    expand_int4(words[w], c);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc_h[4 * w + i] = __hfma2(w2, c[i], acc_h[4 * w + i]);
+                }
+            }
+            if (C::kResidual) {
+                const uint2 codes = *reinterpret_cast<const uint2*>(v_residual + t * C::kResidualCode + 8 * js);
+                const uint8_t* meta = v_residual + P * C::kResidualCode + t * C::kResidualGroups;
+                __half2 w0, w1;
+                if (C::RG == 32) {
+                    const float scale = fp8_decode(meta[js]), offset = fp8_decode(meta[P * C::kResidualGroups + js]);
+                    w0 = w1 = __float2half2_rn(prob * scale);
+                    acc_off0 += prob * offset;
+                    acc_off1 += prob * offset;
+                } else {
+                    w0 = __float2half2_rn(prob * fp8_decode(meta[2 * js]));
+                    w1 = __float2half2_rn(prob * fp8_decode(meta[2 * js + 1]));
+                    acc_off0 += prob * fp8_decode(meta[P * C::kResidualGroups + 2 * js]);
+                    acc_off1 += prob * fp8_decode(meta[P * C::kResidualGroups + 2 * js + 1]);
+                }
+                __half2 c[8];
+                expand_int2(codes.x, c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc_h[i] = __hfma2(w0, c[i], acc_h[i]);
+                expand_int2(codes.y, c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc_h[8 + i] = __hfma2(w1, c[i], acc_h[8 + i]);
+            }
+            if (++pending == 8) flush();
+        }
+
+        __syncwarp();  // every lane has finished reading this stage
+        if (issued < warp_pages) {
+            if (issued - batch_base == 32) load_batch(issued);
+            const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
+            if (lane == 0) {
+                fence_proxy_async();
+                issue(block, stage);
+            }
+            ++issued;
+        }
+        if (++stage == C::kStages) { stage = 0; parity ^= 1u; }
+        it_done = it + 1;
+    }
+    if (failed) {
+        if (lane == 0) atomicExch(p.status, 1);
+        // Copies already issued still target this CTA's shared memory: give each one more bounded wait.
+        int s2 = stage;
+        uint32_t par2 = parity;
+        for (int k = it_done; k < issued; ++k) {
+            mbar_wait(bar_addr + 8 * s2, par2);
+            if (++s2 == C::kStages) { s2 = 0; par2 ^= 1u; }
+        }
+    }
+    flush();
+
+    // ---- fold the 8 token slots of the warp ------------------------------------------------------------
+    float m_warp = m;
+    m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 4));
+    m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 8));
+    m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 16));
+    const float f_slot = m == -INFINITY ? 0.f : fast_exp2(m - m_warp);
+    float l_warp = l * f_slot;
+    l_warp += __shfl_xor_sync(kFullMask, l_warp, 4);
+    l_warp += __shfl_xor_sync(kFullMask, l_warp, 8);
+    l_warp += __shfl_xor_sync(kFullMask, l_warp, 16);
+    __syncwarp();
+    {
+        float* scratch = reinterpret_cast<float*>(ring) + lane * 33;  // [32 lanes][33]: conflict-free both ways
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            const int pair = e >> 1, b = pair >> 2, i = pair & 3;
+            const int local = 8 * b + i + 4 * (e & 1);  // channel inside the slice
+            const float off = local < 16 ? acc_off0 : acc_off1;
+            scratch[local] = (acc[e] + off) * f_slot;
+        }
+    }
+    __syncwarp();
+    if (4 * lane < D) {
+        const float* scratch = reinterpret_cast<const float*>(ring);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = 4 * lane + i, slice = c >> 5, local = c & 31;
+            float sum = 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) sum += scratch[(4 * g + slice) * 33 + local];
+            warp_acc[warp * D + c] = sum;
+        }
+    }
+    if (lane == 0) {
+        warp_stat[2 * warp] = m_warp;
+        warp_stat[2 * warp + 1] = l_warp;
+    }
+    __syncthreads();
+
+    // ---- fold the warps of the CTA: thread c owns channel c ---------------------------------------------
+    float part_m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) part_m = fmaxf(part_m, warp_stat[2 * w]);
+    float part_l = 0.f, value = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const float mw = warp_stat[2 * w];
+        const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - part_m);
+        part_l += warp_stat[2 * w + 1] * f;
+        if (tid < D) value += warp_acc[w * D + tid] * f;
+    }
+
+    // ---- several partitions: park the partial, the last CTA to arrive folds them -----------------------
+    float* misc = warp_stat + 8;
+    if (splits > 1) {
+        float* mine = p.partials + ((static_cast<int64_t>(row) * heads + head) * splits + split) * (D + 2);
+        if (tid == 0) { mine[0] = part_m; mine[1] = part_l; }
+        if (tid < D) mine[2 + tid] = value;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int ticket = atomicAdd(p.counters + row * heads + head, 1);
+            misc[0] = ticket == splits - 1 ? 1.f : 0.f;
+            if (ticket == splits - 1) p.counters[row * heads + head] = 0;  // ready for the next call
+        }
+        __syncthreads();
+        if (misc[0] == 0.f) return;
+        __threadfence();
+        const float* all = p.partials + (static_cast<int64_t>(row) * heads + head) * splits * (D + 2);
+        part_m = -INFINITY;
+        for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * (D + 2)));
+        part_l = 0.f;
+        value = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = __ldcg(all + s * (D + 2));
+            const float f = ms == -INFINITY ? 0.f : fast_exp2(ms - part_m);
+            part_l += __ldcg(all + s * (D + 2) + 1) * f;
+            if (tid < D) value += __ldcg(all + s * (D + 2) + 2 + tid) * f;
+        }
+    }
+
+    // ---- live token, normalisation, optional inverse value rotation, store -------------------------------
+    if (warp == 0) {
+        float dot = 0.f, shift = 0.f;
+        if (4 * lane < D) {
+            const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + 4 * lane;
+            const __nv_bfloat16* k = p.key + static_cast<int64_t>(row) * p.key_stride + head * D + 4 * lane;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dot += __bfloat162float(q[i]) * __bfloat162float(k[i]);
+            if (C::kMean) {
+                // history scores leave out q.mean[loop]; the live score drops the same constant (prepare.cuh:229)
+                const float* mean = p.mean + (static_cast<int64_t>(p.loop_index) * heads + head) * D + 4 * lane;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) shift += qs[4 * lane + i] * mean[i];
+            }
+        }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) {
+            dot += __shfl_xor_sync(kFullMask, dot, d);
+            shift += __shfl_xor_sync(kFullMask, shift, d);
+        }
+        if (lane == 0) misc[1] = dot * rsqrtf(static_cast<float>(D)) * kLog2e - shift;
+    }
+    __syncthreads();
+    const float live = misc[1];
+    const float total_m = fmaxf(part_m, live);
+    const float f_hist = part_l > 0.f ? fast_exp2(part_m - total_m) : 0.f;
+    const float f_live = fast_exp2(live - total_m);
+    const float denom = part_l * f_hist + f_live;
+    float hist = tid < D ? value * f_hist / denom : 0.f;
+    if (p.value_sign != nullptr) {
+        float* buffer = warp_acc;  // free again
+        __syncthreads();
+        if (tid < D) buffer[tid] = hist;
+        __syncthreads();
+        if (warp == 0) unrotate_history<D>(p, head, buffer);
+        __syncthreads();
+        if (tid < D) hist = buffer[tid];
+    }
+    if (tid < D) {
+        const float v_live = __bfloat162float(p.value[static_cast<int64_t>(row) * p.value_stride + head * D + tid]);
+        p.output[static_cast<int64_t>(row) * p.output_stride + head * D + tid] =
+            __float2bfloat16_rn(hist + v_live * (f_live / denom));
+    }
+}
+
+template <class C>
+cudaError_t launch_one(const AttentionParams& p, cudaStream_t stream) {
+    // Raise the dynamic shared memory limit once per device (bit d of the mask = device d is configured).
+    static std::atomic<unsigned long long> configured{0ull};
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    const unsigned long long bit = 1ull << (device & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        err = cudaFuncSetAttribute(attention_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (err != cudaSuccess) return err;
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    const int64_t blocks = static_cast<int64_t>(p.num_rows) * p.splits * p.heads;
+    attention_kernel<C><<<static_cast<unsigned>(blocks), kThreads, C::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int D, int RB, int RG, int P>
+cudaError_t launch_mean(bool has_mean, const AttentionParams& p, cudaStream_t stream) {
+    if (has_mean) return launch_one<Config<D, 4, 32, RB, RG, P, true>>(p, stream);
+    return launch_one<Config<D, 4, 32, RB, RG, P, false>>(p, stream);
+}
+
+template <int D, int P>
+cudaError_t launch_residual(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream) {
+    if (v.residual_bits == 0) return launch_mean<D, 0, 32, P>(v.has_mean, p, stream);
+    if (v.residual_bits == 2 && v.residual_group == 32) return launch_mean<D, 2, 32, P>(v.has_mean, p, stream);
+    if (v.residual_bits == 2 && v.residual_group == 16) return launch_mean<D, 2, 16, P>(v.has_mean, p, stream);
+    return cudaErrorInvalidDeviceFunction;
+}
+
+}  // namespace
+
+bool attention_variant_available(const AttentionVariant& v) {
+    if (v.head_dim != 128 && v.head_dim != 96) return false;
+    if (v.page_tokens != 16 && v.page_tokens != 32) return false;
+    if (v.anchor_bits != 4 || v.anchor_group != 32) return false;
+    if (v.residual_bits == 0) return true;
+    return v.residual_bits == 2 && (v.residual_group == 16 || v.residual_group == 32);
+}
+
+cudaError_t launch_attention(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream) {
+    if (!attention_variant_available(v)) return cudaErrorInvalidDeviceFunction;
+    if (v.head_dim == 128)
+        return v.page_tokens == 16 ? launch_residual<128, 16>(v, p, stream) : launch_residual<128, 32>(v, p, stream);
+    return v.page_tokens == 16 ? launch_residual<96, 16>(v, p, stream) : launch_residual<96, 32>(v, p, stream);
+}
+
+}  // namespace rq

@@ -1,0 +1,320 @@
+// C ABI: argument validation (the checks of the reference's quantize/api.cpp:8-95 and attention/api.cpp:8-115
+// restated on plain pointers), kernel selection (dispatch/kernel_registry.h:48-75) and launches.
+// No allocation, no synchronization, no host read of device memory on the launch path.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "rq_kernels.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(g_error, sizeof(g_error), format, args);
+    va_end(args);
+    return code;
+}
+
+int fail_cuda(cudaError_t err, const char* what) {
+    return fail(RQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int check_spec(const RqGroupSpec* s) {
+    if (s == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null group spec");
+    if (s->num_records < 1 || s->num_records > RQ_MAX_RECORDS)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "a group needs 1..%d records, got %d", RQ_MAX_RECORDS, s->num_records);
+    if (s->head_dim != 128 && s->head_dim != 96)
+        return fail(RQ_ERR_UNSUPPORTED, "no kernel for head_dim=%d (128 or 96)", s->head_dim);
+    if (s->page_tokens != 16 && s->page_tokens != 32)
+        return fail(RQ_ERR_UNSUPPORTED, "no kernel for page_tokens=%d (16 or 32)", s->page_tokens);
+    if (s->heads < 1) return fail(RQ_ERR_INVALID_ARGUMENT, "heads must be positive");
+    for (int r = 0; r < s->num_records; ++r) {
+        if (s->bits[r] != 2 && s->bits[r] != 4)
+            return fail(RQ_ERR_UNSUPPORTED, "record %d: bits=%d (2 or 4)", r, s->bits[r]);
+        if (s->group_size[r] != 16 && s->group_size[r] != 32)
+            return fail(RQ_ERR_UNSUPPORTED, "record %d: group size %d (16 or 32)", r, s->group_size[r]);
+    }
+    if (s->anchor_index < 0 || s->anchor_index >= s->num_records)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "anchor_index %d outside the %d records", s->anchor_index, s->num_records);
+    if (s->reference_mode != RQ_REFERENCE_ANCHOR && s->reference_mode != RQ_REFERENCE_ADJACENT)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "unknown packed reference mode %d", s->reference_mode);
+    if (s->reference_mode == RQ_REFERENCE_ADJACENT && s->anchor_index != 0)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "adjacent reference requires anchor_index 0");
+    return RQ_OK;
+}
+
+int record_bytes(const RqGroupSpec* s, int r) {
+    return s->head_dim * s->bits[r] / 8 + 2 * s->head_dim / s->group_size[r] + 2;
+}
+
+int check_rotation(const RqRotation& r, const char* name) {
+    if (r.kind == RQ_ROTATION_NONE) return RQ_OK;
+    if (r.kind == RQ_ROTATION_SIGNED_HADAMARD) {
+        if (r.data == nullptr || !aligned(r.data, 4))
+            return fail(RQ_ERR_INVALID_ARGUMENT, "%s: sign masks must be a 4-byte aligned device pointer", name);
+        if (!(r.scale > 0.f)) return fail(RQ_ERR_INVALID_ARGUMENT, "%s: scale must be positive", name);
+        return RQ_OK;
+    }
+    if (r.kind == RQ_ROTATION_DENSE_FP16)
+        return fail(RQ_ERR_UNSUPPORTED, "%s: dense fp16 rotations have no kernel yet; register the matrix as a signed "
+                                        "Hadamard rotation", name);
+    return fail(RQ_ERR_INVALID_ARGUMENT, "%s: unknown rotation kind %d", name, r.kind);
+}
+
+constexpr size_t kStatusBytes = 256;
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+const char* rq_last_error(void) { return g_error; }
+const char* rq_version(void) { return "residualquant_b200 0.1 (sm_100a)"; }
+
+int32_t rq_page_width(const RqGroupSpec* spec) { return rq_record_offset(spec, spec ? spec->num_records : 0); }
+
+int32_t rq_record_offset(const RqGroupSpec* spec, int32_t index) {
+    const int status = check_spec(spec);
+    if (status != RQ_OK) return status;
+    if (index < 0 || index > spec->num_records) return fail(RQ_ERR_INVALID_ARGUMENT, "record index %d out of range", index);
+    int offset = 0;
+    for (int r = 0; r < index; ++r) offset += record_bytes(spec, r);
+    return offset;
+}
+
+int32_t rq_quantize(const RqQuantizeArgs* a) {
+    if (a == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null arguments");
+    int status = check_spec(&a->spec);
+    if (status != RQ_OK) return status;
+    const RqGroupSpec& s = a->spec;
+    if (a->num_tokens < 0) return fail(RQ_ERR_INVALID_ARGUMENT, "negative token count");
+    if (a->num_tokens == 0) return RQ_OK;  // quantize/launch.cuh:59
+    if (a->num_tokens > 0x7fffffff / 16) return fail(RQ_ERR_INVALID_ARGUMENT, "too many tokens in one call");
+    const int width = rq_page_width(&s);
+    if (a->kv_cache == nullptr || !aligned(a->kv_cache, 16))
+        return fail(RQ_ERR_INVALID_ARGUMENT, "16-byte aligned uint8 [2, blocks, heads, page tokens, page width] cache required");
+    if (a->num_blocks < 1 || a->plane_stride < a->num_blocks * s.heads * static_cast<int64_t>(s.page_tokens) * width)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "plane stride %lld is smaller than one plane of %lld blocks (page width %d)",
+                    static_cast<long long>(a->plane_stride), static_cast<long long>(a->num_blocks), width);
+    if (a->slot_mapping == nullptr || !aligned(a->slot_mapping, 8))
+        return fail(RQ_ERR_INVALID_ARGUMENT, "contiguous int64 slot mapping required");
+    if (a->coefficient != RQ_COEFF_UNIT && a->coefficient != RQ_COEFF_NORM && a->coefficient != RQ_COEFF_LS)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "unsupported coefficient %d", a->coefficient);
+    if (a->chain != RQ_CHAIN_KERNEL && a->chain != RQ_CHAIN_CALIBRATION)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "unknown chain %d", a->chain);
+    if (a->chain == RQ_CHAIN_CALIBRATION && s.reference_mode != RQ_REFERENCE_ANCHOR)
+        return fail(RQ_ERR_UNSUPPORTED, "the calibration chain is defined for the anchor reference mode");
+    if ((status = check_rotation(a->key_rotation, "key_rotation")) != RQ_OK) return status;
+    if ((status = check_rotation(a->value_rotation, "value_rotation")) != RQ_OK) return status;
+    if (a->key_mean != nullptr && !aligned(a->key_mean, 4))
+        return fail(RQ_ERR_INVALID_ARGUMENT, "fp32 [records, heads, channels] key mean required");
+
+    rq::QuantizeParams p;
+    memset(&p, 0, sizeof(p));
+    bool vector_loads = true;
+    for (int r = 0; r < s.num_records; ++r) {
+        if (a->key[r] == nullptr || a->value[r] == nullptr)
+            return fail(RQ_ERR_INVALID_ARGUMENT, "one K/V input per record required (record %d is null)", r);
+        if (!aligned(a->key[r], 2) || !aligned(a->value[r], 2) || a->key_stride[r] < s.heads * s.head_dim ||
+            a->value_stride[r] < s.heads * s.head_dim)
+            return fail(RQ_ERR_INVALID_ARGUMENT, "bf16 [tokens, heads, channels] with packed trailing strides required");
+        p.key[r] = static_cast<const __nv_bfloat16*>(a->key[r]);
+        p.value[r] = static_cast<const __nv_bfloat16*>(a->value[r]);
+        p.key_stride[r] = a->key_stride[r];
+        p.value_stride[r] = a->value_stride[r];
+        vector_loads = vector_loads && aligned(a->key[r], 16) && aligned(a->value[r], 16) &&
+                       a->key_stride[r] % 8 == 0 && a->value_stride[r] % 8 == 0;
+        p.bits[r] = s.bits[r];
+        p.group[r] = s.group_size[r];
+        p.record_offset[r] = rq_record_offset(&s, r);
+    }
+    p.cache = static_cast<uint8_t*>(a->kv_cache);
+    p.plane_stride = a->plane_stride;
+    p.slots = a->slot_mapping;
+    p.sign[0] = static_cast<const uint32_t*>(a->key_rotation.data);
+    p.sign[1] = static_cast<const uint32_t*>(a->value_rotation.data);
+    p.rscale[0] = a->key_rotation.scale;
+    p.rscale[1] = a->value_rotation.scale;
+    p.rotation[0] = a->key_rotation.kind;
+    p.rotation[1] = a->value_rotation.kind;
+    p.mean = a->key_mean;
+    p.num_tokens = static_cast<int>(a->num_tokens);
+    p.heads = s.heads;
+    p.page_tokens = s.page_tokens;
+    p.page_width = width;
+    p.num_records = s.num_records;
+    p.anchor = s.anchor_index;
+    // A single-record group has only its base record, whatever the reference mode (dispatch/schedules.cuh:24-37).
+    p.mode = s.num_records == 1 ? RQ_REFERENCE_ANCHOR : s.reference_mode;
+    p.coefficient = a->coefficient;
+    p.chain = a->chain;
+    p.vector_loads = vector_loads ? 1 : 0;
+    const cudaError_t err = rq::launch_quantize(p, s.head_dim, static_cast<cudaStream_t>(a->stream));
+    if (err != cudaSuccess) return fail_cuda(err, "quantize launch");
+    return RQ_OK;
+}
+
+int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32_t max_blocks_per_request,
+                                    int32_t page_tokens) {
+    if (num_query_rows < 1 || heads < 1) return 1;
+    static thread_local int sm_count_cache[64] = {0};
+    int device = 0;
+    int sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64) {
+        if (sm_count_cache[device] == 0) {
+            int value = 0;
+            if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0)
+                sm_count_cache[device] = value;
+        }
+        if (sm_count_cache[device] > 0) sms = sm_count_cache[device];
+    }
+    // Aim for about eight CTAs per SM overall (a few resident waves) while keeping at least sixteen pages
+    // (four per warp) in a partition.
+    const int64_t base = static_cast<int64_t>(num_query_rows) * heads;
+    int64_t want = (8LL * sms + base - 1) / base;
+    const int64_t by_length = max_blocks_per_request > 0 ? (max_blocks_per_request + 15) / 16 : 1;
+    if (want > by_length) want = by_length;
+    if (want > 64) want = 64;
+    if (want < 1) want = 1;
+    (void)page_tokens;
+    return static_cast<int32_t>(want);
+}
+
+size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits) {
+    if (num_query_rows < 0 || heads < 1 || head_dim < 1 || num_splits < 1) return 0;
+    const size_t counters = round_up(static_cast<size_t>(num_query_rows) * heads * sizeof(int32_t), 256);
+    const size_t partials =
+        num_splits > 1 ? static_cast<size_t>(num_query_rows) * heads * num_splits * (head_dim + 2) * sizeof(float) : 0;
+    return kStatusBytes + counters + round_up(partials, 256);
+}
+
+int32_t rq_attention_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+    if (workspace == nullptr || !aligned(workspace, 256) || workspace_bytes < kStatusBytes)
+        return fail(RQ_ERR_WORKSPACE, "workspace must be a 256-byte aligned device buffer");
+    const cudaError_t err = cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "workspace init");
+    return RQ_OK;
+}
+
+int32_t rq_attention_status(const void* workspace, void* stream) {
+    if (workspace == nullptr) return fail(RQ_ERR_WORKSPACE, "null workspace");
+    int32_t word = 0;
+    cudaError_t err = cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost,
+                                      static_cast<cudaStream_t>(stream));
+    if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "status read");
+    if (word != 0) return fail(RQ_ERR_DEVICE_TIMEOUT, "a bounded wait inside the attention kernel gave up");
+    return RQ_OK;
+}
+
+int32_t rq_attention(const RqAttentionArgs* a) {
+    if (a == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null arguments");
+    int status = check_spec(&a->spec);
+    if (status != RQ_OK) return status;
+    const RqGroupSpec& s = a->spec;
+    if (a->num_query_rows < 0) return fail(RQ_ERR_INVALID_ARGUMENT, "negative query row count");
+    if (a->num_query_rows == 0) return RQ_OK;  // attention/launch.cuh:46
+    if (a->loop_index < 0 || a->loop_index >= s.num_records) return fail(RQ_ERR_INVALID_ARGUMENT, "invalid loop index");
+    const int64_t row_elems = static_cast<int64_t>(s.heads) * s.head_dim;
+    if (a->query == nullptr || a->key == nullptr || a->value == nullptr || a->output == nullptr)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "Q/K/V/output must be device pointers");
+    if (a->query_stride < row_elems || a->key_stride < row_elems || a->value_stride < row_elems ||
+        a->output_stride < row_elems)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "bf16 [tokens, heads, channels] with packed trailing strides required");
+    if (!aligned(a->query, 8) || !aligned(a->key, 8) || a->query_stride % 4 != 0 || a->key_stride % 4 != 0)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "Q/K addresses and token strides must be 8-byte aligned");
+    if (!aligned(a->value, 2) || !aligned(a->output, 2))
+        return fail(RQ_ERR_INVALID_ARGUMENT, "V/output must be bf16 pointers");
+    const int width = rq_page_width(&s);
+    if (a->kv_cache == nullptr || !aligned(a->kv_cache, 16) || a->plane_stride % 16 != 0)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "16-byte aligned contiguous uint8 KV cache required");
+    if (a->num_blocks < 1 || a->plane_stride < a->num_blocks * s.heads * static_cast<int64_t>(s.page_tokens) * width)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "plane stride %lld is smaller than one plane of %lld blocks (page width %d)",
+                    static_cast<long long>(a->plane_stride), static_cast<long long>(a->num_blocks), width);
+    if (a->query_start_loc == nullptr || a->seq_lens == nullptr || a->block_table == nullptr || a->num_requests < 1)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "int32 query starts [requests+1], sequence lengths [requests] and page table required");
+    if (a->block_table_stride < a->max_blocks_per_request || a->max_blocks_per_request < 0)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "int32 page table with packed rows required");
+    if (a->key_mean != nullptr && !aligned(a->key_mean, 16))
+        return fail(RQ_ERR_INVALID_ARGUMENT, "16-byte aligned contiguous fp32 key mean required");
+    if ((status = check_rotation(a->key_rotation, "key_rotation")) != RQ_OK) return status;
+    if ((status = check_rotation(a->value_rotation, "value_rotation")) != RQ_OK) return status;
+    if (s.reference_mode != RQ_REFERENCE_ANCHOR && s.num_records > 1)
+        return fail(RQ_ERR_UNSUPPORTED, "no compiled packed attention kernel for reference_mode=adjacent");
+
+    rq::AttentionVariant v;
+    v.head_dim = s.head_dim;
+    v.anchor_bits = s.bits[s.anchor_index];
+    v.anchor_group = s.group_size[s.anchor_index];
+    const bool anchor_loop = a->loop_index == s.anchor_index;
+    v.residual_bits = anchor_loop ? 0 : s.bits[a->loop_index];
+    v.residual_group = anchor_loop ? 32 : s.group_size[a->loop_index];
+    v.page_tokens = s.page_tokens;
+    v.has_mean = a->key_mean != nullptr;
+    if (!rq::attention_variant_available(v))
+        return fail(RQ_ERR_UNSUPPORTED,
+                    "No compiled packed CUDA kernel for heads=%d, head_dim=%d, anchor=(%d,%d), loop record=(%d,%d), "
+                    "has_mean=%d, page_tokens=%d",
+                    s.heads, s.head_dim, v.anchor_bits, v.anchor_group, v.residual_bits, v.residual_group,
+                    int(v.has_mean), s.page_tokens);
+
+    int splits = a->num_splits;
+    if (splits == 0)
+        splits = rq_attention_default_splits(a->num_query_rows, s.heads, a->max_blocks_per_request, s.page_tokens);
+    if (splits < 1 || splits > 1024) return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside 1..1024", splits);
+    if (static_cast<int64_t>(a->num_query_rows) * splits * s.heads > 0x7fffffffLL)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "grid too large");
+    const size_t need = rq_attention_workspace_bytes(a->num_query_rows, s.heads, s.head_dim, splits);
+    if (a->workspace == nullptr || !aligned(a->workspace, 256) || a->workspace_bytes < need)
+        return fail(RQ_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required, got %zu", need, a->workspace_bytes);
+
+    rq::AttentionParams p;
+    memset(&p, 0, sizeof(p));
+    p.query = static_cast<const __nv_bfloat16*>(a->query);
+    p.key = static_cast<const __nv_bfloat16*>(a->key);
+    p.value = static_cast<const __nv_bfloat16*>(a->value);
+    p.output = static_cast<__nv_bfloat16*>(a->output);
+    p.query_stride = a->query_stride;
+    p.key_stride = a->key_stride;
+    p.value_stride = a->value_stride;
+    p.output_stride = a->output_stride;
+    p.cache = static_cast<const uint8_t*>(a->kv_cache);
+    p.plane_stride = a->plane_stride;
+    p.query_start_loc = a->query_start_loc;
+    p.seq_lens = a->seq_lens;
+    p.block_table = a->block_table;
+    p.num_rows = a->num_query_rows;
+    p.num_requests = a->num_requests;
+    p.block_table_stride = a->block_table_stride;
+    p.max_blocks = a->max_blocks_per_request;
+    p.key_sign = a->key_rotation.kind == RQ_ROTATION_SIGNED_HADAMARD ? static_cast<const uint32_t*>(a->key_rotation.data) : nullptr;
+    p.value_sign = a->value_rotation.kind == RQ_ROTATION_SIGNED_HADAMARD ? static_cast<const uint32_t*>(a->value_rotation.data) : nullptr;
+    p.key_rscale = a->key_rotation.scale;
+    p.value_rscale = a->value_rotation.scale;
+    p.mean = a->key_mean;
+    p.heads = s.heads;
+    p.page_width = width;
+    p.anchor_offset = rq_record_offset(&s, s.anchor_index);
+    p.residual_offset = rq_record_offset(&s, a->loop_index);
+    p.anchor_index = s.anchor_index;
+    p.loop_index = a->loop_index;
+    p.splits = splits;
+    uint8_t* base = static_cast<uint8_t*>(a->workspace);
+    p.status = reinterpret_cast<int32_t*>(base);
+    p.counters = reinterpret_cast<int32_t*>(base + kStatusBytes);
+    p.partials = reinterpret_cast<float*>(
+        base + kStatusBytes + round_up(static_cast<size_t>(a->num_query_rows) * s.heads * sizeof(int32_t), 256));
+    const cudaError_t err = rq::launch_attention(v, p, static_cast<cudaStream_t>(a->stream));
+    if (err != cudaSuccess) return fail_cuda(err, "attention launch");
+    return RQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,79 @@
+// Internal launch interface between the C ABI (rq_capi.cu) and the kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/rq_b200.h"
+
+namespace rq {
+
+struct QuantizeParams {
+    const __nv_bfloat16* key[RQ_MAX_RECORDS];
+    const __nv_bfloat16* value[RQ_MAX_RECORDS];
+    int64_t key_stride[RQ_MAX_RECORDS];
+    int64_t value_stride[RQ_MAX_RECORDS];
+    uint8_t* cache;
+    int64_t plane_stride;
+    const int64_t* slots;
+    const uint32_t* sign[2];  // per plane: [heads][head_dim/32] sign bit masks (signed-Hadamard rotation)
+    float rscale[2];
+    int rotation[2];          // RqRotationKind per plane
+    const float* mean;        // [records][heads][head_dim] or nullptr
+    int num_tokens, heads, page_tokens, page_width;
+    int num_records, anchor, mode, coefficient, chain;
+    int bits[RQ_MAX_RECORDS], group[RQ_MAX_RECORDS], record_offset[RQ_MAX_RECORDS];
+    int vector_loads;         // rows are 16-byte aligned
+};
+
+cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream);
+
+// Layout of the attention workspace (all offsets multiples of 256 bytes):
+//   [0, 256)                         status word (int32) + padding
+//   [256, 256 + 4*rows*heads)        arrival counters, one int32 per (row, head)
+//   [partials_offset, ...)           float [rows][heads][splits][head_dim + 2]  (max, denominator, value sums)
+struct AttentionParams {
+    const __nv_bfloat16* query;
+    const __nv_bfloat16* key;
+    const __nv_bfloat16* value;
+    __nv_bfloat16* output;
+    int64_t query_stride, key_stride, value_stride, output_stride;
+    const uint8_t* cache;
+    int64_t plane_stride;
+    const int32_t* query_start_loc;
+    const int32_t* seq_lens;
+    const int32_t* block_table;
+    int num_rows, num_requests, block_table_stride, max_blocks;
+    const uint32_t* key_sign;    // signed-Hadamard key rotation or nullptr
+    const uint32_t* value_sign;  // explicit value rotation (undone on the history sum) or nullptr
+    float key_rscale, value_rscale;
+    const float* mean;           // [records][heads][head_dim] or nullptr
+    int heads, page_width;
+    int anchor_offset;           // bytes per token before the anchor record
+    int residual_offset;         // bytes per token before the current loop's record (unused on the anchor loop)
+    int anchor_index, loop_index;
+    int splits;
+    int32_t* status;
+    int32_t* counters;
+    float* partials;
+};
+
+// Kernel variant selector: which residual record (if any) is read next to the INT4/INT2 anchor.
+struct AttentionVariant {
+    int head_dim;       // 128 | 96
+    int anchor_bits;    // 2 | 4
+    int anchor_group;   // 16 | 32
+    int residual_bits;  // 0 (anchor loop) | 2 | 4
+    int residual_group; // 16 | 32 (ignored on the anchor loop)
+    int page_tokens;    // 16 | 32
+    bool has_mean;
+};
+
+// Returns cudaErrorInvalidDeviceFunction when the variant is not compiled in.
+cudaError_t launch_attention(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream);
+bool attention_variant_available(const AttentionVariant& v);
+
+}  // namespace rq

@@ -1,0 +1,336 @@
+// KV-write quantizer: rotate (fused signed Walsh-Hadamard), quantize the anchor record, then the
+// coefficient-scaled residual records against the reconstructed anchor, and bit-pack everything into the
+// paged uint8 cache.  One launch per call.
+//
+// Replaces quantize_kernel / quantize_token / commit_record of the reference
+// (plugins/residual_quantization/csrc/quantize/kernel.cuh:33-228, 236-355) and its TF32-MMA rotation
+// (quantize/rotation.cuh:25-150).  Every operation that feeds a rounding decision is an explicit
+// round-to-nearest binary32 intrinsic in a fixed order, so a CPU restatement reproduces the packed bytes
+// bit for bit.  This file must be compiled with -fmad=false and without --use_fast_math.
+//
+// Work split: a row = one (token, head, plane); 8 lanes own a row, each lane 16 consecutive channels, so a
+// warp owns 4 consecutive tokens of one head and a 128-thread CTA 16 consecutive tokens (one vLLM block when
+// the slots are contiguous).  Grid = (ceil(tokens/16), heads, 2 planes).
+#include "rq_common.cuh"
+#include "rq_kernels.h"
+
+namespace rq {
+namespace {
+
+// P[i][j] == -1  <=>  bit j of kPaleyRow[i]  <=>  bit i of kPaleyCol[j]   (12x12 Paley matrix)
+__constant__ uint32_t kPaleyRow[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0xed0, 0xda2,
+                                       0xb46, 0x68e, 0xd1c, 0xa3a, 0, 0, 0, 0};
+__constant__ uint32_t kPaleyCol[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc,
+                                       0x5b8, 0xb70, 0x6e2, 0xdc4, 0, 0, 0, 0};
+
+// Forward: y = ((sign * x) H) * rscale.  Inverse: x = ((y H^T) * rscale) * sign.
+// `j` is the lane's slice (channels 16j .. 16j+15) inside its 8-lane row group.
+template <int D, bool INVERSE>
+__device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign16, float rscale) {
+    if (!INVERSE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if ((sign16 >> i) & 1u) x[i] = -x[i];
+    }
+    if (D == 128) {
+        butterflies_in_lane<16>(x);
+        butterfly_across_lanes<16>(x, 1, (j & 1) != 0);
+        butterfly_across_lanes<16>(x, 2, (j & 2) != 0);
+        butterfly_across_lanes<16>(x, 4, (j & 4) != 0);
+    } else {
+        // Sylvester-8 inside each block of 8 channels (two blocks per lane) ...
+#pragma unroll
+        for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if ((i & h) == 0) {
+                    const float a = x[i], b = x[i + h];
+                    x[i] = __fadd_rn(a, b);
+                    x[i + h] = __fsub_rn(a, b);
+                }
+            }
+        }
+        // ... then the 12-point Paley transform across blocks: out[a'] = sum_a s(a, a') t[a], a = 0..11.
+        const int lane = threadIdx.x & 31;
+        const int group_base = lane & 24;
+        const uint32_t mask0 = INVERSE ? kPaleyRow[(2 * j) & 15] : kPaleyCol[(2 * j) & 15];
+        const uint32_t mask1 = INVERSE ? kPaleyRow[(2 * j + 1) & 15] : kPaleyCol[(2 * j + 1) & 15];
+        float out[16];
+#pragma unroll
+        for (int a = 0; a < 12; ++a) {
+            const bool neg0 = (mask0 >> a) & 1u, neg1 = (mask1 >> a) & 1u;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                const float v = __shfl_sync(kFullMask, x[8 * (a & 1) + b], group_base + (a >> 1));
+                const float t0 = neg0 ? -v : v, t1 = neg1 ? -v : v;
+                if (a == 0) {
+                    out[b] = t0;
+                    out[8 + b] = t1;
+                } else {
+                    out[b] = __fadd_rn(out[b], t0);
+                    out[8 + b] = __fadd_rn(out[8 + b], t1);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = out[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = __fmul_rn(x[i], rscale);
+    if (INVERSE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if ((sign16 >> i) & 1u) x[i] = -x[i];
+    }
+}
+
+// sum over the row of a[c]*b[c]: 16 sequential (product rounded, then added) terms per lane, then the
+// lanes combine as ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)).
+__device__ __forceinline__ float row_dot(const float (&a)[16], const float (&b)[16]) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc = __fadd_rn(acc, __fmul_rn(a[i], b[i]));
+    acc = __fadd_rn(acc, __shfl_xor_sync(kFullMask, acc, 1));
+    acc = __fadd_rn(acc, __shfl_xor_sync(kFullMask, acc, 2));
+    acc = __fadd_rn(acc, __shfl_xor_sync(kFullMask, acc, 4));
+    return acc;
+}
+
+struct GroupCode {
+    uint32_t code[16];
+    uint8_t scale8, offset8;
+};
+
+// Asymmetric group quantizer (reference: quantize/kernel.cuh:111-158; scripts/calibration/quantization.py:40-53).
+__device__ __forceinline__ GroupCode group_quantize(const float (&z)[16], int bits, int group) {
+    GroupCode out;
+    float low = z[0], high = z[0];
+#pragma unroll
+    for (int i = 1; i < 16; ++i) {
+        low = fminf(low, z[i]);
+        high = fmaxf(high, z[i]);
+    }
+    if (group == 32) {
+        low = fminf(low, __shfl_xor_sync(kFullMask, low, 1));
+        high = fmaxf(high, __shfl_xor_sync(kFullMask, high, 1));
+    }
+    const float levels = bits == 2 ? 3.f : 15.f;
+    const float center = __fmul_rn(__fadd_rn(low, high), 0.5f);
+    const float width = __fsub_rn(high, low);
+    const float radius = bits == 2 ? __fmul_rn(__fmul_rn(width, 0.9f), 0.5f) : __fmul_rn(width, 0.5f);
+    // "+ 0.0f" turns a -0.0 lower bound into +0.0 so the stored byte never depends on which signed zero won a min/max.
+    out.offset8 = fp8_encode(__fadd_rn(__fsub_rn(center, radius), 0.0f));
+    out.scale8 = fp8_encode(__fdiv_rn(__fmul_rn(2.f, radius), levels));
+    const float offset = fp8_decode(out.offset8), scale = fp8_decode(out.scale8);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        uint32_t code = 0;
+        if (scale > 0.f) {
+            const float n = __fdiv_rn(__fsub_rn(z[i], offset), scale);
+            const float fl = floorf(n);
+            const float up = __fsub_rn(n, fl) > 0.5f ? 1.f : 0.f;  // a half rounds down
+            code = static_cast<uint32_t>(fminf(fmaxf(__fadd_rn(fl, up), 0.f), levels));
+        }
+        out.code[i] = code;
+    }
+    return out;
+}
+
+// bf16( code * bf16(scale) + bf16(offset) ) with a single rounding (reference: kernel.cuh:161-186).
+__device__ __forceinline__ float restore_bf16(uint32_t code, float scale, float offset) {
+    return __bfloat162float(__hfma(__ushort2bfloat16_rn(static_cast<unsigned short>(code)),
+                                   __float2bfloat16_rn(scale), __float2bfloat16_rn(offset)));
+}
+__device__ __forceinline__ float bf16_add(float a, float b) {
+    return __bfloat162float(__hadd(__float2bfloat16_rn(a), __float2bfloat16_rn(b)));
+}
+__device__ __forceinline__ float bf16_round(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
+
+template <int D>
+__global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ QuantizeParams p) {
+    constexpr int kSlices = D / 16;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = lane & 7;
+    const int token = blockIdx.x * 16 + warp * 4 + (lane >> 3);
+    const int head = blockIdx.y, plane = blockIdx.z;
+
+    int64_t slot = -1;
+    if (token < p.num_tokens) slot = p.slots[token];
+    if (__ballot_sync(kFullMask, slot >= 0) == 0u) return;  // padding only: nothing to read or write
+    const bool active = slot >= 0 && j < kSlices;
+
+    const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
+    const int64_t* strides = plane == 0 ? p.key_stride : p.value_stride;
+    const bool rotated = p.rotation[plane] == RQ_ROTATION_SIGNED_HADAMARD;
+    const float rscale = p.rscale[plane];
+    uint32_t sign16 = 0;
+    if (rotated && j < kSlices)
+        sign16 = (p.sign[plane][head * (D / 32) + (j >> 1)] >> (16 * (j & 1))) & 0xffffu;
+    const bool centered = plane == 0 && p.mean != nullptr;
+
+    const int P = p.page_tokens;
+    const int tok = active ? static_cast<int>(slot % P) : 0;
+    uint8_t* page = p.cache + plane * p.plane_stride +
+                    (active ? (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width : 0);
+
+    auto load_row = [&](int r, float (&x)[16]) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+        if (!active) return;
+        const __nv_bfloat16* src = sources[r] + static_cast<int64_t>(token) * strides[r] + head * D + 16 * j;
+        if (p.vector_loads) {
+            const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src));
+            const uint4 hi = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x[2 * i] = bf16_bits_to_float(w[i] & 0xffffu);
+                x[2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = __bfloat162float(src[i]);
+        }
+    };
+    auto load_mean = [&](int r, float (&m)[16]) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m[i] = 0.f;
+        if (centered && j < kSlices) {
+            const float* src = p.mean + (static_cast<int64_t>(r) * p.heads + head) * D + 16 * j;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) m[i] = src[i];
+        }
+    };
+    // Quantize z (already centered) as record r, store it, return the codes and parameters.
+    auto commit = [&](int r, const float (&z)[16], uint16_t alpha_bits) -> GroupCode {
+        const int bits = p.bits[r], group = p.group[r];
+        const GroupCode q = group_quantize(z, bits, group);
+        if (active) {
+            const int code_bytes = D * bits / 8, groups = D / group;
+            uint8_t* record = page + static_cast<int64_t>(P) * p.record_offset[r];
+            if (bits == 2) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) word |= q.code[i] << (2 * i);
+                *reinterpret_cast<uint32_t*>(record + tok * code_bytes + 4 * j) = word;
+            } else {
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    lo |= q.code[i] << (4 * i);
+                    hi |= q.code[8 + i] << (4 * i);
+                }
+                *reinterpret_cast<uint2*>(record + tok * code_bytes + 8 * j) = make_uint2(lo, hi);
+            }
+            uint8_t* scales = record + P * code_bytes;
+            uint8_t* offsets = scales + P * groups;
+            if (group == 16) {
+                scales[tok * groups + j] = q.scale8;
+                offsets[tok * groups + j] = q.offset8;
+            } else if ((j & 1) == 0) {
+                scales[tok * groups + (j >> 1)] = q.scale8;
+                offsets[tok * groups + (j >> 1)] = q.offset8;
+            }
+            if (j == 0)
+                *reinterpret_cast<uint16_t*>(record + P * (code_bytes + 2 * groups) + tok * 2) = alpha_bits;
+        }
+        return q;
+    };
+    auto coefficient = [&](const float (&x)[16], const float (&ref)[16]) -> float {
+        if (p.coefficient == RQ_COEFF_UNIT) return 1.f;
+        if (p.coefficient == RQ_COEFF_NORM) {
+            const float num = row_dot(x, x), den = row_dot(ref, ref);
+            return den > 0.f ? __fdiv_rn(__fsqrt_rn(num), fmaxf(__fsqrt_rn(den), 1e-6f)) : 0.f;
+        }
+        const float num = row_dot(x, ref), den = row_dot(ref, ref);
+        return __fdiv_rn(num, fmaxf(den, 1e-12f));
+    };
+
+    const int anchor = p.anchor;
+    float ref[16];  // bf16-valued reconstruction that residuals predict from
+    {
+        float y[16], mean[16];
+        load_row(anchor, y);
+        if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+        load_mean(anchor, mean);
+        if (centered) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = __fsub_rn(y[i], mean[i]);
+        }
+        const GroupCode q = commit(anchor, y, 0x3F80u);
+        const float scale = fp8_decode(q.scale8), offset = fp8_decode(q.offset8);
+        if (p.chain == RQ_CHAIN_KERNEL) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                ref[i] = restore_bf16(q.code[i], scale, offset);
+                if (centered) ref[i] = bf16_add(ref[i], bf16_round(mean[i]));
+            }
+        } else {
+            // decoded value (+ mean) back in original coordinates, rounded to bf16 there
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                ref[i] = __fmaf_rn(static_cast<float>(q.code[i]), scale, offset);
+                if (centered) ref[i] = __fadd_rn(ref[i], mean[i]);
+            }
+            if (rotated) rotate_row<D, true>(ref, j, sign16, rscale);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ref[i] = bf16_round(ref[i]);
+        }
+    }
+
+    for (int r = 0; r < p.num_records; ++r) {
+        if (r == anchor) continue;
+        float y[16], mean[16];
+        load_row(r, y);
+        load_mean(r, mean);
+        uint16_t alpha_bits;
+        if (p.chain == RQ_CHAIN_KERNEL) {
+            if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+            const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref));
+            alpha_bits = __bfloat16_as_ushort(stored);
+            const float alpha = __bfloat162float(stored);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = __fmaf_rn(-ref[i], alpha, y[i]);
+        } else {
+            const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref));
+            alpha_bits = __bfloat16_as_ushort(stored);
+            const float alpha = __bfloat162float(stored);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float prediction = bf16_round(__fmul_rn(ref[i], alpha));
+                y[i] = bf16_round(__fsub_rn(y[i], prediction));
+            }
+            if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+        }
+        if (centered) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = __fsub_rn(y[i], mean[i]);
+        }
+        const GroupCode q = commit(r, y, alpha_bits);
+        if (p.mode == RQ_REFERENCE_ADJACENT) {
+            // the next record predicts from this record's reconstruction (reference: kernel.cuh:195-201)
+            const float scale = fp8_decode(q.scale8), offset = fp8_decode(q.offset8);
+            const __nv_bfloat16 alpha_bf = __ushort_as_bfloat16(alpha_bits);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float restored = restore_bf16(q.code[i], scale, offset);
+                if (centered) restored = bf16_add(restored, bf16_round(mean[i]));
+                ref[i] = __bfloat162float(
+                    __hfma(__float2bfloat16_rn(ref[i]), alpha_bf, __float2bfloat16_rn(restored)));
+            }
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream) {
+    const dim3 grid((p.num_tokens + 15) / 16, p.heads, 2);
+    if (head_dim == 128)
+        quantize_kernel<128><<<grid, 128, 0, stream>>>(p);
+    else
+        quantize_kernel<96><<<grid, 128, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace rq

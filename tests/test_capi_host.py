@@ -1,0 +1,66 @@
+"""The C-ABI library loads without a GPU and exports every function include/rq_b200.h declares (CPU)."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from residualquant_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "rq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(rq_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(built_library):
+    declared = _declared_functions()
+    assert declared, "no declarations found"
+    assert sorted(_lib.EXPORTS) == declared
+    lib = ctypes.CDLL(built_library)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/rq_b200.h but not exported"
+
+
+def test_layout_functions(built_library):
+    lib = _lib.load()
+    spec = _lib.make_spec([[2, 32]] * 3 + [[4, 32]], "anchor", 3, 16, 128, 16)
+    assert lib.rq_page_width(ctypes.byref(spec)) == 200
+    assert [lib.rq_record_offset(ctypes.byref(spec), i) for i in range(5)] == [0, 42, 84, 126, 200]
+    spec = _lib.make_spec([[2, 16]] * 3 + [[4, 32]], "anchor", 3, 16, 128, 32)
+    assert lib.rq_page_width(ctypes.byref(spec)) == 224
+    spec = _lib.make_spec([[2, 32]] * 3 + [[4, 32]], "anchor", 3, 55, 96, 16)
+    assert lib.rq_page_width(ctypes.byref(spec)) == 152
+    spec = _lib.make_spec([[4, 32]], "anchor", 0, 16, 128, 16)
+    assert lib.rq_page_width(ctypes.byref(spec)) == 74
+
+
+def test_bad_specs_return_errors_not_crashes(built_library):
+    lib = _lib.load()
+    spec = _lib.make_spec([[3, 32]], "anchor", 0, 16, 128, 16)
+    assert lib.rq_page_width(ctypes.byref(spec)) == -2
+    assert b"bits=3" in lib.rq_last_error()
+    spec = _lib.make_spec([[2, 32], [2, 32]], "adjacent", 1, 16, 128, 16)
+    assert lib.rq_page_width(ctypes.byref(spec)) == -1
+    spec = _lib.make_spec([[2, 32]], "anchor", 0, 16, 64, 16)
+    assert lib.rq_page_width(ctypes.byref(spec)) == -2
+    with pytest.raises(RuntimeError):
+        _lib.make_spec([[2, 32]], "sideways", 0, 16, 128, 16)
+    assert lib.rq_quantize(None) == -1
+    assert lib.rq_attention(None) == -1
+
+
+def test_workspace_size_and_split_heuristic(built_library):
+    lib = _lib.load()
+    one = lib.rq_attention_workspace_bytes(64, 16, 128, 1)
+    four = lib.rq_attention_workspace_bytes(64, 16, 128, 4)
+    assert one == 256 + 4096 and four == one + 64 * 16 * 4 * 130 * 4
+    assert four % 256 == 0
+    assert lib.rq_attention_workspace_bytes(64, 16, 128, 0) == 0
+    assert 1 <= lib.rq_attention_default_splits(1, 16, 512, 16) <= 64
+    assert lib.rq_attention_default_splits(1, 16, 512, 16) >= lib.rq_attention_default_splits(64, 16, 512, 16)
+    assert lib.rq_attention_default_splits(64, 16, 1, 16) == 1

@@ -1,0 +1,202 @@
+"""Packed paged decode attention on the GPU against the CPU oracle.
+
+Tolerance (stated by the task for bf16 outputs): |got - want| <= 2e-2 + 1e-2 * |want| on every element."""
+
+import numpy as np
+import pytest
+import torch
+
+from tests import gpu_helpers as G
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-2, 1e-2
+
+
+def _check(case, cache_np, loop, splits=0, pad_rows=0):
+    from residualquant_b200 import _cuda
+
+    cache = torch.from_numpy(cache_np).cuda()
+    _cuda.set_attention_splits(splits)
+    try:
+        got = G.gpu_attention(case, cache, loop, pad_rows=pad_rows).float().cpu().numpy()
+    finally:
+        _cuda.set_attention_splits(0)
+    want = helpers.oracle_attention(case, cache_np, loop)
+    rows = len(case.seq_lens)
+    err = np.abs(got[:rows] - want)
+    bound = ATOL + RTOL * np.abs(want)
+    assert np.all(err <= bound), f"loop {loop} splits {splits}: max err {err.max():.4f}, worst excess {np.max(err - bound):.4f}"
+    if pad_rows:
+        assert np.all(got[rows:] == 777.0), "padding rows must stay untouched"
+    return err.max()
+
+
+@pytest.mark.parametrize("head_dim,group,page", [(128, 32, 16), (128, 16, 16), (128, 32, 32), (128, 16, 32),
+                                                 (96, 32, 16), (96, 16, 16), (96, 32, 32)])
+def test_all_loops_match_oracle(head_dim, group, page):
+    case = helpers.make_case(31, head_dim, 3, [300, 1, 2, 17, 64, 129], group, page)
+    cache = helpers.oracle_cache(case)
+    for loop in range(4):
+        _check(case, cache, loop)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
+def test_partition_counts(splits):
+    case = helpers.make_case(32, 128, 2, [700, 40, 1, 333], 32, 16)
+    cache = helpers.oracle_cache(case)
+    for loop in (1, 3):
+        _check(case, cache, loop, splits=splits)
+
+
+@pytest.mark.parametrize("head_dim", [128, 96])
+def test_with_key_mean(head_dim):
+    case = helpers.make_case(33, head_dim, 2, [150, 31], 32, 16, with_mean=True)
+    cache = helpers.oracle_cache(case)
+    for loop in range(4):
+        _check(case, cache, loop, splits=2)
+
+
+def test_rotation_variants():
+    # value rotation absorbed by the model's weights (None), or no rotation at all
+    for rk, rv in ((True, False), (False, False)):
+        case = helpers.make_case(34, 128, 2, [90, 200], 32, 16, rotate_keys=rk, rotate_values=rv)
+        cache = helpers.oracle_cache(case)
+        for loop in (0, 3):
+            _check(case, cache, loop)
+
+
+def test_padding_rows_are_left_untouched():
+    case = helpers.make_case(35, 128, 2, [60, 75], 32, 16)
+    cache = helpers.oracle_cache(case)
+    _check(case, cache, 2, pad_rows=3)
+    _check(case, cache, 2, splits=4, pad_rows=3)
+
+
+def test_long_context_full_shape():
+    """BASELINE shape of one layer: 16 heads x 128, block 16, context 2048 (config 0) for every loop."""
+    case = helpers.make_case(36, 128, 16, [2048], 32, 16)
+    cache = helpers.oracle_cache(case)
+    for loop in range(4):
+        _check(case, cache, loop)
+
+
+def test_gpu_written_cache_feeds_attention():
+    """quantize -> attention end to end on the device, against the oracle fed the same raw rows."""
+    case = helpers.make_case(37, 128, 4, [513, 77], 16, 16)
+    cache_gpu = G.gpu_cache(case)
+    cache_np = helpers.oracle_cache(case)
+    assert np.array_equal(cache_gpu.cpu().numpy(), cache_np)
+    for loop in range(4):
+        got = G.gpu_attention(case, cache_gpu, loop).float().cpu().numpy()
+        want = helpers.oracle_attention(case, cache_np, loop)
+        assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want))
+
+
+def test_cuda_graph_replay_follows_changed_metadata():
+    """One captured decode step (attention of 4 loops + the group's quantize) replayed after the sequence
+    lengths, block table and slot mapping changed on the device (reference: FULL_DECODE_ONLY capture,
+    experiments/kv_memory_latency/measure.py:249-253)."""
+    from residualquant_b200 import _cuda
+
+    case = helpers.make_case(38, 128, 4, [200, 90], 32, 16)
+    L = case.layout
+    records = [list(r) for r in L.records]
+    kr, vr = G.device_rotations(case)
+    cache = torch.from_numpy(helpers.oracle_cache(case)).cuda()
+    r = len(case.seq_lens)
+    q = G.bf16(case.query)
+    live_k = [G.bf16(k[case.live_rows]) for k in case.keys]
+    live_v = [G.bf16(v[case.live_rows]) for v in case.values]
+    outs = [torch.zeros_like(q) for _ in range(4)]
+    qsl = torch.arange(r + 1, dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    live_slots = torch.tensor(
+        [int(case.block_table[i, (case.seq_lens[i] - 1) // 16]) * 16 + (case.seq_lens[i] - 1) % 16 for i in range(r)],
+        dtype=torch.int64, device="cuda")
+
+    def step():
+        for loop in range(4):
+            _cuda.attention(q, live_k[loop], live_v[loop], cache, outs[loop], qsl, seq, table, kr, vr, None,
+                            records, "anchor", 3, loop)
+        _cuda.quantize(list(zip(live_k, live_v)), cache, live_slots, kr, vr, None, records, "anchor", 3, "ls")
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step()                                   # warm-up: creates the workspace outside capture
+    side.synchronize()
+    cache.copy_(torch.from_numpy(helpers.oracle_cache(case)).cuda())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    graph.replay()
+    torch.cuda.synchronize()
+    cache_np = helpers.oracle_cache(case)
+    for loop in range(4):
+        want = helpers.oracle_attention(case, cache_np, loop)
+        got = outs[loop].float().cpu().numpy()
+        assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want))
+    # the step wrote the live token into the cache: now it is history.  Advance every request by one token.
+    from oracle import rq_oracle as O
+    okr, ovr = helpers.oracle_rotations(case)
+    O.quantize([(k[case.live_rows], v[case.live_rows]) for k, v in zip(case.keys, case.values)], cache_np,
+               live_slots.cpu().numpy(), L, okr, ovr, None)
+    assert np.array_equal(cache.cpu().numpy(), cache_np)
+    seq += 1
+    new_slots = []
+    for i in range(r):
+        pos = int(case.seq_lens[i])              # position of the new live token
+        new_slots.append(int(case.block_table[i, pos // 16]) * 16 + pos % 16)
+    live_slots.copy_(torch.tensor(new_slots, dtype=torch.int64))
+    graph.replay()
+    torch.cuda.synchronize()
+    grown = helpers.make_case(38, 128, 4, [200, 90], 32, 16)
+    grown.seq_lens = case.seq_lens + 1
+    for loop in range(4):
+        want = O.attention(case.query, case.keys[loop][case.live_rows], case.values[loop][case.live_rows], cache_np,
+                           np.arange(r + 1, dtype=np.int32), grown.seq_lens, case.block_table, L, loop, okr, ovr, None)
+        got = outs[loop].float().cpu().numpy()
+        assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want))
+    _cuda.attention_status()
+
+
+def test_argument_errors_raise_runtime_error():
+    from residualquant_b200 import _cuda
+
+    case = helpers.make_case(39, 128, 2, [20], 32, 16)
+    L = case.layout
+    records = [list(r) for r in L.records]
+    kr, vr = G.device_rotations(case)
+    cache = torch.from_numpy(helpers.oracle_cache(case)).cuda()
+    q = G.bf16(case.query)
+    out = torch.zeros_like(q)
+    qsl = torch.arange(2, dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    ok = (q, q, q, cache, out, qsl, seq, table, kr, vr, None, records, "anchor", 3, 0)
+
+    def call(**changes):
+        names = ["query", "key", "value", "kv_cache", "output", "query_start_loc", "seq_lens", "block_table",
+                 "key_rotation", "value_rotation", "key_mean", "records", "reference_mode", "anchor_index", "loop_index"]
+        kwargs = dict(zip(names, ok))
+        kwargs.update(changes)
+        _cuda.attention(**kwargs)
+
+    call()
+    with pytest.raises(RuntimeError, match="Invalid loop index"):
+        call(loop_index=4)
+    with pytest.raises(RuntimeError, match="matching shapes"):
+        call(key=q[:, :1].contiguous())
+    with pytest.raises(RuntimeError, match="INT32 sequence lengths"):
+        call(seq_lens=seq.long())
+    with pytest.raises(RuntimeError, match="query starts"):
+        call(query_start_loc=qsl[:1])
+    with pytest.raises(RuntimeError, match="page table"):
+        call(block_table=table.long())
+    with pytest.raises(RuntimeError, match="adjacent"):
+        call(records=[[4, 32], [2, 32], [2, 32], [2, 32]], anchor_index=0, reference_mode="adjacent", loop_index=1)
+    narrow = torch.zeros((2, case.num_blocks, case.heads, 16, 168), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="No compiled packed CUDA kernel"):
+        call(records=[[2, 32]] * 4, loop_index=0, kv_cache=narrow)
