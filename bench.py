@@ -1,0 +1,496 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-KV hot path: decode tokens/s of an Ouro-1.4B-shaped stack of KV groups.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one decode step of the hot path for the whole stack: for each of `layers` physical layers, the
+packed paged decode attention of the 4 loops (4 launches) and the KV-write quantizer of the group (1 launch),
+captured once in a CUDA graph and replayed.  Sequence lengths and slot mappings advance on the device inside
+the graph, as they do under vLLM's decode capture.  Workload (standalone kernel sweep, no model): 16 heads x 128,
+vLLM block size 16, INT4 g32 anchor in the last loop + INT2 g32 residuals, batch 64 at context 8192; seeded
+synthetic K/V (N(0,1) x log-normal channel scales, 4 outlier channels x8 per head, earlier loops
+0.9*anchor + 0.3*N(0,1)), signed-Hadamard rotation, block tables randomly permuted over the page pool.
+
+Printed JSON line:
+  value     tokens/s with every input resident in HBM (CUDA-event time of K graph replays, max over ranks)
+  e2e       tokens/s when each step also copies its q/k/v rows from pinned host memory and reads the outputs back
+  roofline  the dominant kernel (attention of a residual loop): algorithmic packed-KV bytes per launch / CUDA-event
+            time per launch, against the measured HBM copy bandwidth of MEASURED_PEAKS.json
+  cpu_baseline  the CPU oracle (a restatement of the reference's algorithm) timed on a bounded sample, scaled
+            to the same unit
+
+`--impl reference` times that CPU restatement alone (the reference has no native CPU path and its PyTorch
+code cannot travel to the benchmark machine).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tokens/s"
+HEADS, HEAD_DIM, PAGE = 16, 128, 16
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=8)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--context", type=int, default=8192)
+    p.add_argument("--group", type=int, default=32, choices=[16, 32])
+    p.add_argument("--layers", type=int, default=24)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--sweep", action="store_true", help="also time attention alone over the batch x context grid")
+    return p.parse_args()
+
+
+def record_bytes(bits, group, dim=HEAD_DIM):
+    return dim * bits // 8 + 2 * dim // group + 2
+
+
+def attention_bytes(batch, context, group, loop_is_anchor, heads=HEADS, dim=HEAD_DIM):
+    """Algorithmic bytes of one attention launch: every cached token's anchor record without its alpha column,
+    plus the loop's own residual record, for K and V; plus q, live k, live v, out in bf16."""
+    anchor = record_bytes(4, 32, dim) - 2
+    per_token = anchor if loop_is_anchor else anchor + record_bytes(2, group, dim)
+    return batch * (context - 1) * heads * 2 * per_token + batch * heads * dim * 8
+
+
+def quantize_bytes(tokens, group, heads=HEADS, dim=HEAD_DIM):
+    width = 3 * record_bytes(2, group, dim) + record_bytes(4, 32, dim)
+    return 2 * 4 * tokens * heads * dim * 2 + 2 * tokens * heads * width
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------------------
+# CPU restatement (oracle) timed on a bounded sample
+# ----------------------------------------------------------------------------------------------------------
+
+
+def cpu_sample(context, group, layers, batch, sample_context=2048):
+    """One sequence, one layer, context `sample_context`: quantize of the whole prompt (K and V, 4 loops) and the
+    decode attention of the 4 loops.  Returns (tokens/s scaled to the full workload, description)."""
+    from oracle import rq_oracle as O
+    from tests import helpers
+
+    case = helpers.make_case(0, HEAD_DIM, HEADS, [sample_context], group, PAGE)
+    t0 = time.perf_counter()
+    cache = helpers.oracle_cache(case)
+    t1 = time.perf_counter()
+    for loop in range(4):
+        helpers.oracle_attention(case, cache, loop)
+    t2 = time.perf_counter()
+    quantize_per_token = (t1 - t0) / max(1, sample_context - 1)
+    attention_per_cached_token = (t2 - t1) / max(1, sample_context - 1)
+    # one decode step of the full workload for ONE sequence: `layers` x (4 attentions over `context` + 1 write)
+    step_seconds = layers * (attention_per_cached_token * (context - 1) + quantize_per_token)
+    description = (
+        f"numpy oracle, 1 sequence x 1 layer x context {sample_context} (quantize {t1 - t0:.2f}s, "
+        f"4 attentions {t2 - t1:.2f}s), scaled linearly to {layers} layers x context {context}"
+    )
+    return 1.0 / step_seconds, description, (t2 - t0)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    values = []
+    description = ""
+    begin = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        value, description, _ = cpu_sample(args.context, args.group, args.layers, args.batch, sample_context=512)
+        if i >= args.warmup:
+            values.append(value)
+    elapsed = time.perf_counter() - begin
+    value = statistics.median(values)
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": 1000.0 * elapsed / max(1, args.warmup + args.steps),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": description},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args):
+    return {
+        "workload": f"config1 kernel sweep point: batch {args.batch} x context {args.context}, INT2 g{args.group} "
+                    f"residuals + INT4 g32 anchor, {args.layers} layers x 4 loops, 16 heads x 128, block 16, "
+                    "CUDA-graph decode step (4 attention + 1 quantize launch per layer)",
+        "batch_per_gpu": args.batch,
+        "context": args.context,
+        "layers": args.layers,
+        "l2": "inputs larger than L2 (each layer's packed cache is read once per step)",
+    }
+
+
+# ----------------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------------
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        clocks, max_clocks, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in out.strip().splitlines():
+            cells = [c.strip() for c in row.split(",")]
+            if len(cells) < 9:
+                continue
+            try:
+                clocks.append(float(cells[1]))
+                max_clocks.append(float(cells[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, cells[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def build_stack(args, device, torch):
+    """Packed caches of `layers` layers for `batch` sequences of `context` tokens (+ head room), filled by the
+    quantizer kernel from seeded synthetic rows; every layer shares one block table, as under vLLM."""
+    from residualquant_b200 import _cuda, rotation, synth
+
+    records = [[2, args.group]] * 3 + [[4, 32]]
+    width = 3 * record_bytes(2, args.group) + record_bytes(4, 32)
+    head_room = 128
+    blocks_per_seq = (args.context + head_room + PAGE - 1) // PAGE
+    num_blocks = args.batch * blocks_per_seq + 1
+    rng = np.random.default_rng(1234 + int(os.environ.get("RANK", "0")))
+    pool = rng.permutation(num_blocks - 1) + 1          # block 0 stays unused, like vLLM's null block
+    table_np = pool.reshape(args.batch, blocks_per_seq).astype(np.int32)
+    block_table = torch.from_numpy(table_np).to(device)
+    key_rot = rotation.signed_hadamard(synth.signs(rng, HEADS, HEAD_DIM), float(synth.fp16_rsqrt(HEAD_DIM)), device)
+    value_rot = rotation.signed_hadamard(synth.signs(rng, HEADS, HEAD_DIM), float(synth.fp16_rsqrt(HEAD_DIM)), device)
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(99 + int(os.environ.get("RANK", "0")))
+    channel_scale = torch.exp(0.5 * torch.randn(HEADS, HEAD_DIM, device=device, generator=gen))
+    outlier = torch.ones(HEADS, HEAD_DIM, device=device)
+    for h in range(HEADS):
+        outlier[h, torch.randperm(HEAD_DIM, device=device, generator=gen)[:4]] = 8.0
+    channel_scale = channel_scale * outlier
+
+    def rows(tokens):
+        anchor = torch.randn(tokens, HEADS, HEAD_DIM, device=device, generator=gen) * channel_scale
+        loops = [(0.9 * anchor + 0.3 * torch.randn(tokens, HEADS, HEAD_DIM, device=device, generator=gen)).bfloat16()
+                 for _ in range(3)]
+        return loops + [anchor.bfloat16()]
+
+    caches = [torch.zeros((2, num_blocks, HEADS, PAGE, width), dtype=torch.uint8, device=device)]
+    # fill layer 0 sequence by sequence, then clone it into the other layers
+    positions = torch.arange(args.context, device=device)
+    for b in range(args.batch):
+        slots = block_table[b, positions // PAGE].long() * PAGE + positions % PAGE
+        k, v = rows(args.context), rows(args.context)
+        _cuda.quantize(list(zip(k, v)), caches[0], slots, key_rot, None, None, records, "anchor", 3, "ls")
+    torch.cuda.synchronize(device)
+    for _ in range(1, args.layers):
+        caches.append(caches[0].clone())
+    return {
+        "records": records, "caches": caches, "block_table": block_table, "key_rot": key_rot, "value_rot": value_rot,
+        "rows": rows, "width": width,
+    }
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from residualquant_b200 import _cuda
+    from residualquant_b200 import build as kernel_build
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    if rank == 0:
+        kernel_build.build()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        dist.barrier()
+    else:
+        kernel_build.build()
+
+    B, L, layers = args.batch, args.context, args.layers
+    stack = build_stack(args, device, torch)
+    records, caches = stack["records"], stack["caches"]
+    # The model's weights absorb the value rotation in the served configuration (weights.py:9-37 of the reference),
+    # so the kernels see value_rotation=None and V arrives rotated.
+    key_rot = stack["key_rot"]
+    block_table = stack["block_table"]
+
+    # per (layer, loop) inputs of a step, device resident
+    q = torch.randn(layers, 4, B, HEADS, HEAD_DIM, device=device).bfloat16()
+    live = stack["rows"](B * layers)
+    k_live = torch.stack([r.view(layers, B, HEADS, HEAD_DIM) for r in live], dim=1).contiguous()   # [layers, 4, B, H, D]
+    live = stack["rows"](B * layers)
+    v_live = torch.stack([r.view(layers, B, HEADS, HEAD_DIM) for r in live], dim=1).contiguous()
+    out = torch.zeros_like(q)
+    qsl = torch.arange(B + 1, dtype=torch.int32, device=device)
+    seq_lens = torch.full((B,), L, dtype=torch.int32, device=device)
+    slot_mapping = torch.zeros(B, dtype=torch.int64, device=device)
+    batch_index = torch.arange(B, device=device)
+
+    def advance():
+        # position of the live token = seq_len - 1; its slot is where this step's quantize writes
+        position = (seq_lens - 1).long()
+        slot_mapping.copy_(block_table[batch_index, position // PAGE].long() * PAGE + position % PAGE)
+
+    def hot_path():
+        for layer in range(layers):
+            for loop in range(4):
+                _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer], out[layer, loop],
+                                qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
+            _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
+                           key_rot, None, None, records, "anchor", 3, "ls")
+
+    def step_body():
+        advance()
+        hot_path()
+        seq_lens.add_(1)
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        step_body()                      # eager warm-up: workspace, per-variant attributes
+    stream.synchronize()
+    seq_lens.fill_(L)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step_body()
+    seq_lens.fill_(L)
+    torch.cuda.synchronize(device)
+    launches_per_step = layers * 5
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def timed(fn, steps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stream):
+            start.record(stream)
+            for _ in range(steps):
+                fn()
+            stop.record(stream)
+        stop.synchronize()
+        barrier()
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank)
+    # ---------------- device-resident throughput ----------------
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            graph.replay()
+    if rank == 0:
+        sampler.start()
+    ms = timed(graph.replay, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    value = world * B * args.steps / (ms * 1e-3)
+
+    # ---------------- end to end: host rows in, outputs back ----------------
+    seq_lens.fill_(L)
+    host_q = torch.empty(q.shape, dtype=q.dtype).pin_memory().copy_(q)
+    host_k = torch.empty(k_live.shape, dtype=q.dtype).pin_memory().copy_(k_live)
+    host_v = torch.empty(v_live.shape, dtype=q.dtype).pin_memory().copy_(v_live)
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    host_lens = torch.full((B,), L, dtype=torch.int32).pin_memory()
+    h2d = host_q.numel() * 2 * 3 + host_lens.numel() * 4
+    d2h = host_out.numel() * 2
+
+    def e2e_step():
+        q.copy_(host_q, non_blocking=True)
+        k_live.copy_(host_k, non_blocking=True)
+        v_live.copy_(host_v, non_blocking=True)
+        seq_lens.copy_(host_lens, non_blocking=True)
+        graph.replay()
+        host_out.copy_(out, non_blocking=True)
+        host_lens.add_(1)
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            e2e_step()
+    stream.synchronize()
+    host_lens.fill_(L)
+    ms_e2e = timed(e2e_step, args.steps)
+    e2e_value = world * B * args.steps / (ms_e2e * 1e-3)
+
+    # ---------------- dominant kernel alone: attention of a residual loop, one launch per layer ----------------
+    seq_lens.fill_(L)
+
+    def attention_only(loop):
+        def run():
+            for layer in range(layers):
+                _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer], out[layer, loop],
+                                qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
+        return run
+
+    reps = max(1, 48 // layers)
+    ms_res = timed(attention_only(0), 1)                     # warm
+    ms_res = timed(attention_only(0), reps) / (reps * layers)
+    ms_anchor = timed(attention_only(3), reps) / (reps * layers)
+    bytes_res = attention_bytes(B, L, args.group, False)
+    bytes_anchor = attention_bytes(B, L, args.group, True)
+    peak, peak_kind = measured_peak()
+    achieved = bytes_res / (ms_res * 1e-3) / 1e9
+
+    def quantize_only():
+        for layer in range(layers):
+            _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
+                           key_rot, None, None, records, "anchor", 3, "ls")
+    ms_quant = timed(quantize_only, reps) / (reps * layers)
+    _cuda.attention_status(device)
+
+    sweep = None
+    if args.sweep and rank == 0:
+        sweep = []
+        for batch in (1, 8, 32, 64):
+            if batch > B:
+                continue
+            for context in (2048, 4096, 8192):
+                if context > L:
+                    continue
+                lens = torch.full((batch,), context, dtype=torch.int32, device=device)
+                starts = torch.arange(batch + 1, dtype=torch.int32, device=device)
+                for loop in (0, 3):
+                    def run():
+                        for layer in range(layers):
+                            _cuda.attention(q[layer, loop, :batch], k_live[layer, loop, :batch], v_live[layer, loop, :batch],
+                                            caches[layer], out[layer, loop, :batch], starts, lens, block_table[:batch],
+                                            key_rot, None, None, records, "anchor", 3, loop)
+                    timed(run, 1)
+                    t = timed(run, reps) / (reps * layers)
+                    nbytes = attention_bytes(batch, context, args.group, loop == 3)
+                    sweep.append({"batch": batch, "context": context, "loop": loop, "us": 1000 * t,
+                                  "gbs": nbytes / (t * 1e-3) / 1e9, "frac": nbytes / (t * 1e-3) / 1e9 / peak})
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f16 dot products and value sums with fp32 softmax/accumulation (attention); f32 (quantizer)",
+        "data": "synthetic",
+        "config": workload_config(args),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {
+            "bound": "hbm", "kernel": "attention_kernel (residual loop: INT4 anchor + INT2 residual)",
+            "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": None, "algorithmic_bytes_per_launch": bytes_res, "us_per_launch": 1000 * ms_res,
+            "anchor_loop": {"us_per_launch": 1000 * ms_anchor, "achieved": bytes_anchor / (ms_anchor * 1e-3) / 1e9,
+                            "frac": bytes_anchor / (ms_anchor * 1e-3) / 1e9 / peak},
+            "quantize_decode_write": {"us_per_launch": 1000 * ms_quant,
+                                      "achieved": quantize_bytes(B, args.group) / (ms_quant * 1e-3) / 1e9},
+        },
+    }
+    if sweep is not None:
+        line["sweep"] = sweep
+    if not args.no_cpu_baseline:
+        cpu_value, description, _ = cpu_sample(L, args.group, layers, B)
+        line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port", "sample": description}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -447,7 +447,11 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
             {
                 const uint4 codes = *reinterpret_cast<const uint4*>(v_anchor + t * C::kAnchorCode + 16 * js);
                 const uint8_t* meta = v_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
-                const float pa = prob * alpha;
+                float alpha_v = 1.f;  // the V plane stores its own coefficient
+                if (C::kResidual)
+                    alpha_v = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(
+                        v_residual + P * (C::kResidualCode + 2 * C::kResidualGroups) + 2 * t));
+                const float pa = prob * alpha_v;
                 const float scale = fp8_decode(meta[0]), offset = fp8_decode(meta[P * C::kAnchorGroups]);
                 const __half2 w2 = __float2half2_rn(pa * scale);
                 const float off = pa * offset;

@@ -72,8 +72,9 @@ __device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign1
                 }
             }
         }
+        // lanes 6 and 7 of a row group own no channels: keep them at zero so that row sums ignore them
 #pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = out[i];
+        for (int i = 0; i < 16; ++i) x[i] = j < 6 ? out[i] : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) x[i] = __fmul_rn(x[i], rscale);

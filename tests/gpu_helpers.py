@@ -40,7 +40,7 @@ def gpu_attention(case, cache: torch.Tensor, loop_index: int, device="cuda", pad
     if pad_rows:
         pad = torch.zeros((pad_rows,) + tuple(q.shape[1:]), dtype=q.dtype, device=device)
         q, k, v = torch.cat([q, pad]), torch.cat([k, pad]), torch.cat([v, pad])
-    out = torch.full_like(q, 777.0)
+    out = torch.full_like(q, 768.0)
     mean = torch.from_numpy(case.key_mean).to(device) if case.key_mean is not None else None
     _cuda.attention(
         q, k, v, cache, out,

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 import torch
 
+from residualquant_b200 import synth
 from tests import gpu_helpers as G
 from tests import helpers
 
@@ -68,7 +69,7 @@ def test_extreme_values_and_zero_rows():
     for rows in (case.keys, case.values):
         rows[3][3] = 0.0                     # an all-zero anchor row: scale 0, code 0, alpha 0/eps
         rows[0][5] = 0.0
-        rows[3][7] *= 300.0                  # saturates the FP8 scale/offset
+        rows[3][7] = synth.to_bf16_f32(rows[3][7] * 300.0)   # saturates the FP8 scale/offset
         rows[1][9] = rows[3][9]              # residual equal to its anchor
         rows[2][11, :, ::2] = -0.0
     _compare(case)
