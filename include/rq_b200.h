@@ -162,6 +162,22 @@ int32_t rq_attention(const RqAttentionArgs* args);
  * wait inside the kernel ever gave up since the last init (outputs of that call are then undefined). */
 int32_t rq_attention_status(const void* workspace, void* stream);
 
+/* Maximum scratch rq_attention_noalloc can serve: the size of the library's built-in device buffer. */
+#define RQ_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+/* Same operator as rq_attention for callers that are not allowed to allocate device memory -- a serving loop
+ * that runs after the framework froze its memory pool, a plugin that is only handed tensors, code running where a
+ * cudaMalloc would synchronize the device.  (No counterpart in the reference, which allocates five temporaries per
+ * call.)  `workspace` and `workspace_bytes` of the arguments are ignored: the partition results and arrival
+ * counters live in a buffer of RQ_STATIC_SCRATCH_BYTES that is compiled into the library as device memory, so every
+ * GPU that loads the library holds those 8 MiB until the process exits.  A shape whose
+ * rq_attention_workspace_bytes() exceeds that size is rejected with RQ_ERR_WORKSPACE.  The call makes no
+ * cudaMalloc/cudaFree and uses no allocating library.  The first call on each device looks up the buffer's
+ * device address (with that device current) and should therefore be made before any stream capture begins.
+ * Every call clears the status word and the counters it is about to use, on `stream`, before the kernel.  All
+ * calls on a device share the one buffer: two calls whose kernels overlap on the GPU (different streams) race;
+ * keep them on one stream or order them with events. */
+int32_t rq_attention_noalloc(const RqAttentionArgs* args);
+
 const char* rq_last_error(void);
 const char* rq_version(void);
 

@@ -24,6 +24,7 @@ EXPORTS = (
     "rq_attention_workspace_init",
     "rq_attention",
     "rq_attention_status",
+    "rq_attention_noalloc",
     "rq_last_error",
     "rq_version",
 )
@@ -127,6 +128,8 @@ def load() -> ctypes.CDLL:
     lib.rq_attention_workspace_init.restype = ctypes.c_int32
     lib.rq_attention.argtypes = [ctypes.POINTER(RqAttentionArgs)]
     lib.rq_attention.restype = ctypes.c_int32
+    lib.rq_attention_noalloc.argtypes = [ctypes.POINTER(RqAttentionArgs)]
+    lib.rq_attention_noalloc.restype = ctypes.c_int32
     lib.rq_attention_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.rq_attention_status.restype = ctypes.c_int32
     lib.rq_last_error.argtypes = []

@@ -317,4 +317,43 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     return RQ_OK;
 }
 
+// ---- attention without any allocation: scratch compiled into the library -------------------------------
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the address the kernel
+// needs comes from cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[RQ_STATIC_SCRATCH_BYTES];
+
+int32_t rq_attention_noalloc(const RqAttentionArgs* a) {
+    if (a == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null arguments");
+    static thread_local void* addresses[64] = {nullptr};
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
+    if (device < 0 || device >= 64) return fail(RQ_ERR_INVALID_ARGUMENT, "device index %d not supported", device);
+    if (addresses[device] == nullptr) {
+        void* address = nullptr;
+        err = cudaGetSymbolAddress(&address, g_static_scratch);
+        if (err != cudaSuccess) return fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
+        addresses[device] = address;
+    }
+    if (a->num_query_rows <= 0) return rq_attention(a);  // nothing to launch; reuse the argument checks
+    int splits = a->num_splits;
+    if (splits == 0)
+        splits = rq_attention_default_splits(a->num_query_rows, a->spec.heads, a->max_blocks_per_request,
+                                             a->spec.page_tokens);
+    const size_t need = rq_attention_workspace_bytes(a->num_query_rows, a->spec.heads, a->spec.head_dim, splits);
+    if (need == 0 || need > RQ_STATIC_SCRATCH_BYTES)
+        return fail(RQ_ERR_WORKSPACE,
+                    "this shape needs %zu bytes of scratch; the built-in buffer holds %u (use rq_attention with a "
+                    "caller-provided workspace, or fewer splits)", need, RQ_STATIC_SCRATCH_BYTES);
+    // The buffer keeps whatever the previous call left: the status word and the arrival counters must start at zero.
+    const size_t clear = kStatusBytes + round_up(static_cast<size_t>(a->num_query_rows) * a->spec.heads * sizeof(int32_t), 256);
+    err = cudaMemsetAsync(addresses[device], 0, clear, static_cast<cudaStream_t>(a->stream));
+    if (err != cudaSuccess) return fail_cuda(err, "clearing the static scratch");
+    RqAttentionArgs copy = *a;
+    copy.num_splits = splits;
+    copy.workspace = addresses[device];
+    copy.workspace_bytes = RQ_STATIC_SCRATCH_BYTES;
+    return rq_attention(&copy);
+}
+
 }  // extern "C"
