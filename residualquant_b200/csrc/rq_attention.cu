@@ -112,6 +112,48 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t select
 }
 __device__ __forceinline__ __half2 as_half2(uint32_t bits) { return *reinterpret_cast<const __half2*>(&bits); }
 
+// Shared-memory loads by 32-bit shared address (no generic-pointer arithmetic in the hot loop).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+// d = c + a.s16[0] * b.u8[0|2] + a.s16[1] * b.u8[1|3]
+__device__ __forceinline__ int dp2a_lo(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// Two FP8-e4m3 bytes (first in bits 0-7, second in bits 8-15) -> two floats, one hardware conversion.
+__device__ __forceinline__ float2 fp8x2_to_float2(uint32_t pair) {
+    uint32_t h2;
+    asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(h2) : "r"(pair));
+    return __half22float2(as_half2(h2));
+}
+__device__ __forceinline__ uint32_t pack_s16(int lo, int hi) {
+    return (static_cast<uint32_t>(lo) & 0xffffu) | (static_cast<uint32_t>(hi) << 16);
+}
+
 // Eight INT4 codes of one 32-bit word -> four half2 pairs (channel i, channel i+4), i = 0..3.
 __device__ __forceinline__ void expand_int4(uint32_t word, __half2 (&out)[4]) {
     const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f), k16th = __float2half2_rn(0.0625f);
@@ -133,12 +175,11 @@ __device__ __forceinline__ void expand_int2(uint32_t word, __half2 (&out)[8]) {
         out[4 * b + 3] = __hfma2(as_half2((t & 0x00C000C0u) | 0x64006400u), __float2half2_rn(0.015625f), __float2half2_rn(-16.f));
     }
 }
-__device__ __forceinline__ float half2_sum(__half2 v) { return __low2float(v) + __high2float(v); }
 
 // Rotated, pre-scaled query of this (row, head) into shared memory: qs[c] = (q @ R)[c] * D^-1/2 * log2(e).
 // Executed by warp 0; lane L owns channels 4L .. 4L+3.
 template <int D>
-__device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs) {
+__device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs, float* qmax_out) {
     const int lane = threadIdx.x & 31;
     float x[4] = {0.f, 0.f, 0.f, 0.f};
     const bool owner = 4 * lane < D;
@@ -183,10 +224,18 @@ __device__ __forceinline__ void prepare_query(const AttentionParams& p, int row,
         }
         scale *= p.key_rscale;
     }
+    float biggest = 0.f;
     if (owner) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) qs[4 * lane + i] = x[i] * scale;
+        for (int i = 0; i < 4; ++i) {
+            const float v = x[i] * scale;
+            qs[4 * lane + i] = v;
+            biggest = fmaxf(biggest, fabsf(v));
+        }
     }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(kFullMask, biggest, d));
+    if (lane == 0) *qmax_out = biggest;
 }
 
 // Undo an explicit value rotation on the history sum: h <- ((h H^T) * rscale) * sign.  Warp 0, in place in smem.
@@ -311,31 +360,69 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
     }
 
     // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
-    if (warp == 0) prepare_query<D>(p, row, head, qs);
+    float* misc = warp_stat + 8;         // [0] last-arrival flag, [1] live score, [2] max |q|
+    if (warp == 0) prepare_query<D>(p, row, head, qs, misc + 2);
     __syncthreads();
 
+    // The K side runs on integer dot products (dp2a: two s16 x u8 products per instruction): the query slice is
+    // quantized once per CTA to 12 bits (anchor) / 10 bits (residual) of its largest magnitude and pre-shifted so
+    // that codes can be used where they sit in the packed word, without shifting them down:
+    //   INT4 word & 0x0F0F0F0F -> bytes c, word & 0xF0F0F0F0 -> bytes 16c: even channels carry 16*q, odd ones q
+    //   INT2 word & (0x03030303 << 2k) -> bytes 4^k c:                     channel position k carries 4^(3-k)*q
     const int j = lane & 3;              // slice: channels 32j .. 32j+31
     const bool slice_ok = 32 * j < D;
     const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
-    __half2 q2[16];                      // pair 4b+i = (channel 8b+i, channel 8b+i+4) of the slice
-    float qsum0 = 0.f, qsum1 = 0.f;      // sum of the (half-rounded) query over channels 0..15 / 16..31 of the slice
+    const float qmax = misc[2];
+    const float to_anchor = qmax > 0.f ? 2047.f / qmax : 0.f, to_residual = qmax > 0.f ? 511.f / qmax : 0.f;
+    const float anchor_unit = qmax / 2047.f, residual_unit = qmax / 511.f;
+    uint32_t qa[16];                     // anchor operands, 4 per code word
+    uint32_t qr[C::kResidual ? 16 : 1];  // residual operands, 8 per code word
+    float qsum_a = 0.f;                  // sum of the quantized query over the slice, anchor resolution
+    float qsum_r0 = 0.f, qsum_r1 = 0.f;  // residual resolution, channels 0..15 / 16..31 of the slice
     float qmean = 0.f;                   // sum_c q[c] * mean[anchor][c] over the slice (residual loops with a mean)
+    {
+        const float* qslice = qs + 32 * js;
+        int ia[32];
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
+        for (int c = 0; c < 32; ++c) {
+            ia[c] = slice_ok ? __float2int_rn(qslice[c] * to_anchor) : 0;
+            qsum_a += static_cast<float>(ia[c]);
+        }
+        qsum_a *= anchor_unit;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int c0 = 32 * js + 8 * b + i;
-            const __half2 pair = slice_ok ? __floats2half2_rn(qs[c0], qs[c0 + 4]) : __float2half2_rn(0.f);
-            q2[4 * b + i] = pair;
-            const float s = half2_sum(pair);
-            if (b < 2) qsum0 += s; else qsum1 += s;
-            if (C::kMean && C::kResidual && slice_ok) {
-                const float* mean = p.mean + (static_cast<int64_t>(p.anchor_index) * heads + head) * D;
-                qmean += __low2float(pair) * mean[c0] + __high2float(pair) * mean[c0 + 4];
+        for (int w = 0; w < 4; ++w) {
+            qa[4 * w + 0] = pack_s16(16 * ia[8 * w + 0], 16 * ia[8 * w + 2]);
+            qa[4 * w + 1] = pack_s16(16 * ia[8 * w + 4], 16 * ia[8 * w + 6]);
+            qa[4 * w + 2] = pack_s16(ia[8 * w + 1], ia[8 * w + 3]);
+            qa[4 * w + 3] = pack_s16(ia[8 * w + 5], ia[8 * w + 7]);
+        }
+        if (C::kResidual) {
+            int ir[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                ir[c] = slice_ok ? __float2int_rn(qslice[c] * to_residual) : 0;
+                if (c < 16) qsum_r0 += static_cast<float>(ir[c]); else qsum_r1 += static_cast<float>(ir[c]);
+            }
+            qsum_r0 *= residual_unit;
+            qsum_r1 *= residual_unit;
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int shift = 1 << (2 * (3 - k));
+                    qr[8 * v + 2 * k] = pack_s16(shift * ir[16 * v + k], shift * ir[16 * v + 4 + k]);
+                    qr[8 * v + 2 * k + 1] = pack_s16(shift * ir[16 * v + 8 + k], shift * ir[16 * v + 12 + k]);
+                }
+            }
+            if (C::kMean && slice_ok) {
+                const float* mean = p.mean + (static_cast<int64_t>(p.anchor_index) * heads + head) * D + 32 * js;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) qmean += qslice[c] * mean[c];
             }
         }
     }
-    const float qsum = qsum0 + qsum1;
+    const float anchor_dot_unit = anchor_unit * 0.0625f;      // the integer dot product carries a factor 16
+    const float residual_dot_unit = residual_unit * 0.015625f;  // ... a factor 64
 
     // ---- page loop -----------------------------------------------------------------------------------
     float m = -INFINITY, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
@@ -367,10 +454,11 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
     for (int it = 0; it < warp_pages; ++it) {
         if (!mbar_wait(bar_addr + 8 * stage, parity)) failed = true;
         if (__any_sync(kFullMask, failed)) { failed = true; break; }
-        const uint8_t* k_anchor = ring + stage * C::kStageBytes;
-        const uint8_t* k_residual = k_anchor + C::kAnchorBytes;
-        const uint8_t* v_anchor = k_anchor + C::kPlaneBytes;
-        const uint8_t* v_residual = v_anchor + C::kAnchorBytes;
+        const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
+        const uint32_t k_residual = k_anchor + C::kAnchorBytes;
+        const uint32_t v_anchor = k_anchor + C::kPlaneBytes;
+        const uint32_t v_residual = v_anchor + C::kAnchorBytes;
+        constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
         const int first_token = (page_begin + warp + kWarps * it) * P;
         const int valid = min(P, history - first_token);
 
@@ -378,49 +466,47 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
         for (int sub = 0; sub < P / 8; ++sub) {
             const int t = sub * 8 + slot;
             const bool live_token = t < valid;
-            // ---------------- K: score of token t against the query slice ----------------
+            // ---------------- K: score of token t against the query slice (integer dot products) ----------------
             float part;
-            float alpha = 1.f;
             {
-                const uint4 codes = *reinterpret_cast<const uint4*>(k_anchor + t * C::kAnchorCode + 16 * js);
-                const uint8_t* meta = k_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
-                const float scale = fp8_decode(meta[0]), offset = fp8_decode(meta[P * C::kAnchorGroups]);
+                const uint4 codes = lds128(k_anchor + t * C::kAnchorCode + 16 * js);
+                const uint32_t meta = k_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
+                const float2 so = fp8x2_to_float2(lds8(meta) | (lds8(meta + P * C::kAnchorGroups) << 8));
                 const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
-                __half2 d0 = __float2half2_rn(0.f), d1 = __float2half2_rn(0.f);
+                int d0 = 0, d1 = 0;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    __half2 c[4];
-                    expand_int4(words[w], c);
-                    d0 = __hfma2(q2[4 * w + 0], c[0], d0);
-                    d1 = __hfma2(q2[4 * w + 1], c[1], d1);
-                    d0 = __hfma2(q2[4 * w + 2], c[2], d0);
-                    d1 = __hfma2(q2[4 * w + 3], c[3], d1);
+                    const uint32_t even = words[w] & 0x0F0F0F0Fu, odd = words[w] & 0xF0F0F0F0u;
+                    d0 = dp2a_lo(qa[4 * w + 0], even, d0);
+                    d1 = dp2a_hi(qa[4 * w + 1], even, d1);
+                    d0 = dp2a_lo(qa[4 * w + 2], odd, d0);
+                    d1 = dp2a_hi(qa[4 * w + 3], odd, d1);
                 }
-                part = scale * (half2_sum(d0) + half2_sum(d1)) + offset * qsum;
+                part = so.x * (static_cast<float>(d0 + d1) * anchor_dot_unit) + so.y * qsum_a;
             }
             if (C::kResidual) {
-                alpha = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(
-                    k_residual + P * (C::kResidualCode + 2 * C::kResidualGroups) + 2 * t));
+                const float alpha = bf16_bits_to_float(lds16(k_residual + kResidualAlphaAt + 2 * t));
                 if (C::kMean) part += qmean;
                 part *= alpha;
-                const uint2 codes = *reinterpret_cast<const uint2*>(k_residual + t * C::kResidualCode + 8 * js);
-                __half2 c[8];
-                __half2 d0 = __float2half2_rn(0.f), d1 = __float2half2_rn(0.f);
-                expand_int2(codes.x, c);
+                const uint2 codes = lds64(k_residual + t * C::kResidualCode + 8 * js);
+                int d0 = 0, d1 = 0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) d0 = __hfma2(q2[i], c[i], d0);
-                expand_int2(codes.y, c);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) d1 = __hfma2(q2[8 + i], c[i], d1);
-                const uint8_t* meta = k_residual + P * C::kResidualCode + t * C::kResidualGroups;
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t m0 = codes.x & (0x03030303u << (2 * k)), m1 = codes.y & (0x03030303u << (2 * k));
+                    d0 = dp2a_lo(qr[2 * k], m0, d0);
+                    d0 = dp2a_hi(qr[2 * k + 1], m0, d0);
+                    d1 = dp2a_lo(qr[8 + 2 * k], m1, d1);
+                    d1 = dp2a_hi(qr[8 + 2 * k + 1], m1, d1);
+                }
+                const uint32_t meta = k_residual + P * C::kResidualCode + t * C::kResidualGroups;
                 if (C::RG == 32) {
-                    const float scale = fp8_decode(meta[js]), offset = fp8_decode(meta[P * C::kResidualGroups + js]);
-                    part += scale * (half2_sum(d0) + half2_sum(d1)) + offset * qsum;
+                    const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * C::kResidualGroups + js) << 8));
+                    part += so.x * (static_cast<float>(d0 + d1) * residual_dot_unit) + so.y * (qsum_r0 + qsum_r1);
                 } else {
-                    const float s0 = fp8_decode(meta[2 * js]), s1 = fp8_decode(meta[2 * js + 1]);
-                    const float o0 = fp8_decode(meta[P * C::kResidualGroups + 2 * js]);
-                    const float o1 = fp8_decode(meta[P * C::kResidualGroups + 2 * js + 1]);
-                    part += s0 * half2_sum(d0) + o0 * qsum0 + s1 * half2_sum(d1) + o1 * qsum1;
+                    const float2 s01 = fp8x2_to_float2(lds16(meta + 2 * js));
+                    const float2 o01 = fp8x2_to_float2(lds16(meta + P * C::kResidualGroups + 2 * js));
+                    part += s01.x * (static_cast<float>(d0) * residual_dot_unit) + o01.x * qsum_r0 +
+                            s01.y * (static_cast<float>(d1) * residual_dot_unit) + o01.y * qsum_r1;
                 }
             }
             part += __shfl_xor_sync(kFullMask, part, 1);
@@ -445,16 +531,13 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
 
             // ---------------- V: accumulate prob * V_hat[t] over the slice ----------------
             {
-                const uint4 codes = *reinterpret_cast<const uint4*>(v_anchor + t * C::kAnchorCode + 16 * js);
-                const uint8_t* meta = v_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
-                float alpha_v = 1.f;  // the V plane stores its own coefficient
-                if (C::kResidual)
-                    alpha_v = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(
-                        v_residual + P * (C::kResidualCode + 2 * C::kResidualGroups) + 2 * t));
-                const float pa = prob * alpha_v;
-                const float scale = fp8_decode(meta[0]), offset = fp8_decode(meta[P * C::kAnchorGroups]);
-                const __half2 w2 = __float2half2_rn(pa * scale);
-                const float off = pa * offset;
+                const uint4 codes = lds128(v_anchor + t * C::kAnchorCode + 16 * js);
+                const uint32_t meta = v_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
+                const float2 so = fp8x2_to_float2(lds8(meta) | (lds8(meta + P * C::kAnchorGroups) << 8));
+                float pa = prob;  // the V plane stores its own coefficient
+                if (C::kResidual) pa *= bf16_bits_to_float(lds16(v_residual + kResidualAlphaAt + 2 * t));
+                const __half2 w2 = __float2half2_rn(pa * so.x);
+                const float off = pa * so.y;
                 acc_off0 += off;
                 acc_off1 += off;
                 const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
@@ -467,19 +550,21 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
                 }
             }
             if (C::kResidual) {
-                const uint2 codes = *reinterpret_cast<const uint2*>(v_residual + t * C::kResidualCode + 8 * js);
-                const uint8_t* meta = v_residual + P * C::kResidualCode + t * C::kResidualGroups;
+                const uint2 codes = lds64(v_residual + t * C::kResidualCode + 8 * js);
+                const uint32_t meta = v_residual + P * C::kResidualCode + t * C::kResidualGroups;
                 __half2 w0, w1;
                 if (C::RG == 32) {
-                    const float scale = fp8_decode(meta[js]), offset = fp8_decode(meta[P * C::kResidualGroups + js]);
-                    w0 = w1 = __float2half2_rn(prob * scale);
-                    acc_off0 += prob * offset;
-                    acc_off1 += prob * offset;
+                    const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * C::kResidualGroups + js) << 8));
+                    w0 = w1 = __float2half2_rn(prob * so.x);
+                    acc_off0 += prob * so.y;
+                    acc_off1 += prob * so.y;
                 } else {
-                    w0 = __float2half2_rn(prob * fp8_decode(meta[2 * js]));
-                    w1 = __float2half2_rn(prob * fp8_decode(meta[2 * js + 1]));
-                    acc_off0 += prob * fp8_decode(meta[P * C::kResidualGroups + 2 * js]);
-                    acc_off1 += prob * fp8_decode(meta[P * C::kResidualGroups + 2 * js + 1]);
+                    const float2 s01 = fp8x2_to_float2(lds16(meta + 2 * js));
+                    const float2 o01 = fp8x2_to_float2(lds16(meta + P * C::kResidualGroups + 2 * js));
+                    w0 = __float2half2_rn(prob * s01.x);
+                    w1 = __float2half2_rn(prob * s01.y);
+                    acc_off0 += prob * o01.x;
+                    acc_off1 += prob * o01.y;
                 }
                 __half2 c[8];
                 expand_int2(codes.x, c);
@@ -570,7 +655,6 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
     }
 
     // ---- several partitions: park the partial, the last CTA to arrive folds them -----------------------
-    float* misc = warp_stat + 8;
     if (splits > 1) {
         float* mine = p.partials + ((static_cast<int64_t>(row) * heads + head) * splits + split) * (D + 2);
         if (tid == 0) { mine[0] = part_m; mine[1] = part_l; }
