@@ -154,25 +154,33 @@ __device__ __forceinline__ uint32_t pack_s16(int lo, int hi) {
     return (static_cast<uint32_t>(lo) & 0xffffu) | (static_cast<uint32_t>(hi) << 16);
 }
 
+// (word & MASK) | magic in ONE instruction: the mask is an immediate, the magic number lives in a register
+// (two immediates would cost two instructions).
+template <uint32_t MASK>
+__device__ __forceinline__ __half2 splice(uint32_t word, uint32_t magic) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(word), "n"(MASK), "r"(magic));
+    return as_half2(d);
+}
 // Eight INT4 codes of one 32-bit word -> four half2 pairs (channel i, channel i+4), i = 0..3.
-__device__ __forceinline__ void expand_int4(uint32_t word, __half2 (&out)[4]) {
+__device__ __forceinline__ void expand_int4(uint32_t word, uint32_t magic, __half2 (&out)[4]) {
     const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f), k16th = __float2half2_rn(0.0625f);
     const uint32_t upper = word >> 8;
-    out[0] = __hsub2(as_half2((word & 0x000F000Fu) | 0x64006400u), k1024);
-    out[1] = __hfma2(as_half2((word & 0x00F000F0u) | 0x64006400u), k16th, __hneg2(k64));
-    out[2] = __hsub2(as_half2((upper & 0x000F000Fu) | 0x64006400u), k1024);
-    out[3] = __hfma2(as_half2((upper & 0x00F000F0u) | 0x64006400u), k16th, __hneg2(k64));
+    out[0] = __hsub2(splice<0x000F000Fu>(word, magic), k1024);
+    out[1] = __hfma2(splice<0x00F000F0u>(word, magic), k16th, __hneg2(k64));
+    out[2] = __hsub2(splice<0x000F000Fu>(upper, magic), k1024);
+    out[3] = __hfma2(splice<0x00F000F0u>(upper, magic), k16th, __hneg2(k64));
 }
 // Sixteen INT2 codes of one 32-bit word -> eight half2 pairs: out[4*b + i] = (channel 8b+i, channel 8b+i+4).
-__device__ __forceinline__ void expand_int2(uint32_t word, __half2 (&out)[8]) {
+__device__ __forceinline__ void expand_int2(uint32_t word, uint32_t magic, __half2 (&out)[8]) {
     const __half2 k1024 = __float2half2_rn(1024.f);
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
         const uint32_t t = prmt(word, 0u, b == 0 ? 0x4140u : 0x4342u);  // bytes [2b, 0, 2b+1, 0]
-        out[4 * b + 0] = __hsub2(as_half2((t & 0x00030003u) | 0x64006400u), k1024);
-        out[4 * b + 1] = __hfma2(as_half2((t & 0x000C000Cu) | 0x64006400u), __float2half2_rn(0.25f), __float2half2_rn(-256.f));
-        out[4 * b + 2] = __hfma2(as_half2((t & 0x00300030u) | 0x64006400u), __float2half2_rn(0.0625f), __float2half2_rn(-64.f));
-        out[4 * b + 3] = __hfma2(as_half2((t & 0x00C000C0u) | 0x64006400u), __float2half2_rn(0.015625f), __float2half2_rn(-16.f));
+        out[4 * b + 0] = __hsub2(splice<0x00030003u>(t, magic), k1024);
+        out[4 * b + 1] = __hfma2(splice<0x000C000Cu>(t, magic), __float2half2_rn(0.25f), __float2half2_rn(-256.f));
+        out[4 * b + 2] = __hfma2(splice<0x00300030u>(t, magic), __float2half2_rn(0.0625f), __float2half2_rn(-64.f));
+        out[4 * b + 3] = __hfma2(splice<0x00C000C0u>(t, magic), __float2half2_rn(0.015625f), __float2half2_rn(-16.f));
     }
 }
 
@@ -284,6 +292,8 @@ __device__ __forceinline__ void unrotate_history(const AttentionParams& p, int h
 template <class C>
 __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_constant__ AttentionParams p) {
     constexpr int D = C::D, P = C::P;
+    constexpr int kFlushPages = 64 / P;   // a lane adds 8 tokens between flushes
+    constexpr float kSlack = 3.f;         // probabilities stay below 8
     extern __shared__ __align__(128) uint8_t smem[];
     float* qs = reinterpret_cast<float*>(smem + C::kOffQuery);
     float* warp_acc = reinterpret_cast<float*>(smem + C::kOffWarpAcc);
@@ -433,11 +443,19 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
     for (int i = 0; i < 16; ++i) acc_h[i] = __float2half2_rn(0.f);
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    int pending = 0;
     bool failed = false;
     const int slot = lane >> 2;          // token slot 0..7 inside a warp step
+    float carry = 1.f;                   // factor the fp32 sums still have to be multiplied by (deferred rescale)
+    uint32_t magic;                      // 0x6400 0x6400 = half2(1024, 1024); in a register on purpose, see splice()
+    asm volatile("mov.b32 %0, 0x64006400;" : "=r"(magic));
 
+    // half2 partial sums -> fp32 sums; keeps every half2 sum below 8 tokens' worth of weight
     auto flush = [&]() {
+        if (__any_sync(kFullMask, carry != 1.f)) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] *= carry;
+            carry = 1.f;
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const float2 f = __half22float2(acc_h[i]);
@@ -445,7 +463,6 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
             acc[2 * i + 1] += f.y;
             acc_h[i] = __float2half2_rn(0.f);
         }
-        pending = 0;
     };
 
     int stage = 0;
@@ -514,16 +531,17 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
             const float score = live_token ? part : -INFINITY;
 
             // ---------------- online softmax of the token slot ----------------
-            if (score > m) {
+            // `m` is the stream's reference exponent, not its exact maximum: it only moves when a score exceeds it
+            // by more than kSlack, so probabilities stay below 2^kSlack and rescaling is rare.
+            if (score > m + kSlack) {
                 const float f = fast_exp2(m - score);  // m == -inf gives 0
                 l *= f;
                 acc_off0 *= f;
                 acc_off1 *= f;
+                carry *= f;
                 const __half2 f2 = __float2half2_rn(f);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc_h[i] = __hmul2(acc_h[i], f2);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[i] *= f;
                 m = score;
             }
             const float prob = live_token ? fast_exp2(score - m) : 0.f;
@@ -544,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     __half2 c[4];
-                    expand_int4(words[w], c);
+                    expand_int4(words[w], magic, c);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc_h[4 * w + i] = __hfma2(w2, c[i], acc_h[4 * w + i]);
                 }
@@ -567,16 +585,16 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
                     acc_off1 += prob * o01.y;
                 }
                 __half2 c[8];
-                expand_int2(codes.x, c);
+                expand_int2(codes.x, magic, c);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc_h[i] = __hfma2(w0, c[i], acc_h[i]);
-                expand_int2(codes.y, c);
+                expand_int2(codes.y, magic, c);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc_h[8 + i] = __hfma2(w1, c[i], acc_h[8 + i]);
             }
-            if (++pending == 8) flush();
         }
 
+        if ((it + 1) % kFlushPages == 0) flush();
         __syncwarp();  // every lane has finished reading this stage
         if (issued < warp_pages) {
             if (issued - batch_base == 32) load_batch(issued);
