@@ -12,12 +12,14 @@
 //          STAGES pages ahead.  There is no CTA-wide barrier inside the page loop.
 //   lane = (token slot, 32-channel slice): 4 lanes per token, 8 tokens per warp step.  A slice is exactly one
 //          INT4 g32 anchor group, so scale/offset handling is per lane, not per channel.
-//   maths: codes are expanded to half2 pairs with the 0x6400 magic-number trick (no int->float conversions),
-//          K: per-slice dot products against the rotated, pre-scaled query, factored as
-//             scale * sum(q*code) + offset * sum(q);
-//          softmax: one online-softmax stream per 4-lane token slot (fp32 max/denominator, base-2 exponent);
-//          V: half2 FMAs with the probability folded into the group scale, flushed to fp32 every 8 tokens; the
-//             offset part is accumulated once per group instead of per channel.
+//   maths: no code is ever converted to a floating-point number one at a time.
+//          K: integer dot products (dp2a) of the masked code bytes against the rotated query quantized once per CTA
+//             to 12/10 bits, factored per slice as scale * sum(q*code) + offset * sum(q);
+//          softmax: one online-softmax stream per 4-lane token slot (fp32 reference exponent that moves only when a
+//             score exceeds it by more than a slack, denominator and offsets in fp32, base-2 exponent);
+//          V: `word & mask` read as a half2 IS a pair of codes times 2^-24 (subnormal halves are linear in their bit
+//             pattern), so one half2 FMA per channel pair with probability * alpha * scale * 2^11 as the weight;
+//             half2 sums are flushed to fp32 every 8 tokens; the offset part is accumulated once per group.
 //   merge: each warp folds its 8 streams, the CTA folds its 4 warps, and -- when the row has several
 //          partitions -- the LAST CTA to arrive (one atomic ticket per (row, head)) folds the partitions, adds the
 //          live token, undoes an explicit value rotation and stores bf16.  No second launch, no spin wait.
@@ -154,35 +156,29 @@ __device__ __forceinline__ uint32_t pack_s16(int lo, int hi) {
     return (static_cast<uint32_t>(lo) & 0xffffu) | (static_cast<uint32_t>(hi) << 16);
 }
 
-// (word & MASK) | magic in ONE instruction: the mask is an immediate, the magic number lives in a register
-// (two immediates would cost two instructions).
-template <uint32_t MASK>
-__device__ __forceinline__ __half2 splice(uint32_t word, uint32_t magic) {
+// half2 arithmetic on raw 32-bit registers.
+__device__ __forceinline__ uint32_t hfma2_raw(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(word), "n"(MASK), "r"(magic));
-    return as_half2(d);
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
-// Eight INT4 codes of one 32-bit word -> four half2 pairs (channel i, channel i+4), i = 0..3.
-__device__ __forceinline__ void expand_int4(uint32_t word, uint32_t magic, __half2 (&out)[4]) {
-    const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f), k16th = __float2half2_rn(0.0625f);
-    const uint32_t upper = word >> 8;
-    out[0] = __hsub2(splice<0x000F000Fu>(word, magic), k1024);
-    out[1] = __hfma2(splice<0x00F000F0u>(word, magic), k16th, __hneg2(k64));
-    out[2] = __hsub2(splice<0x000F000Fu>(upper, magic), k1024);
-    out[3] = __hfma2(splice<0x00F000F0u>(upper, magic), k16th, __hneg2(k64));
+__device__ __forceinline__ uint32_t hmul2_raw(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
 }
-// Sixteen INT2 codes of one 32-bit word -> eight half2 pairs: out[4*b + i] = (channel 8b+i, channel 8b+i+4).
-__device__ __forceinline__ void expand_int2(uint32_t word, uint32_t magic, __half2 (&out)[8]) {
-    const __half2 k1024 = __float2half2_rn(1024.f);
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-        const uint32_t t = prmt(word, 0u, b == 0 ? 0x4140u : 0x4342u);  // bytes [2b, 0, 2b+1, 0]
-        out[4 * b + 0] = __hsub2(splice<0x00030003u>(t, magic), k1024);
-        out[4 * b + 1] = __hfma2(splice<0x000C000Cu>(t, magic), __float2half2_rn(0.25f), __float2half2_rn(-256.f));
-        out[4 * b + 2] = __hfma2(splice<0x00300030u>(t, magic), __float2half2_rn(0.0625f), __float2half2_rn(-64.f));
-        out[4 * b + 3] = __hfma2(splice<0x00C000C0u>(t, magic), __float2half2_rn(0.015625f), __float2half2_rn(-16.f));
-    }
+__device__ __forceinline__ uint32_t half2_from(float v) {  // (v, v), saturating to the largest finite half
+    uint32_t d;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %1;" : "=r"(d) : "f"(v));
+    return d;
 }
+// V codes are never converted: a half whose raw bits are an integer N < 2048 is the number N * 2^-24 (subnormals and
+// the first normal binade are linear in the bit pattern), so `word & mask` IS a pair of scaled codes and the scale
+// goes into the weight.  weight * 2^11 stays a finite half for |weight| < 32 (it saturates beyond: a V group would
+// need a range above ~240 for that); the half2 sums then carry a factor 2^-13: 11-bit relative precision for sums
+// above 0.5, 2^-11 absolute below.
+constexpr float kWeightUp = 2048.f;
+constexpr float kSumDown = 8192.f;
 
 // Rotated, pre-scaled query of this (row, head) into shared memory: qs[c] = (q @ R)[c] * D^-1/2 * log2(e).
 // Executed by warp 0; lane L owns channels 4L .. 4L+3.
@@ -293,7 +289,7 @@ template <class C>
 __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_constant__ AttentionParams p) {
     constexpr int D = C::D, P = C::P;
     constexpr int kFlushPages = 64 / P;   // a lane adds 8 tokens between flushes
-    constexpr float kSlack = 3.f;         // probabilities stay below 8
+    constexpr float kSlack = 1.f;         // probabilities stay below 2
     extern __shared__ __align__(128) uint8_t smem[];
     float* qs = reinterpret_cast<float*>(smem + C::kOffQuery);
     float* warp_acc = reinterpret_cast<float*>(smem + C::kOffWarpAcc);
@@ -436,20 +432,18 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
 
     // ---- page loop -----------------------------------------------------------------------------------
     float m = -INFINITY, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
-    __half2 acc_h[16];
+    uint32_t acc_b[16];                  // half2 partial sums of V, pair 4b+i = (channel 8b+i, channel 8b+i+4)
     float acc[32];
     float acc_off0 = 0.f, acc_off1 = 0.f;  // offset part of V for channels 0..15 / 16..31 of the slice
 #pragma unroll
-    for (int i = 0; i < 16; ++i) acc_h[i] = __float2half2_rn(0.f);
+    for (int i = 0; i < 16; ++i) acc_b[i] = 0u;
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     bool failed = false;
     const int slot = lane >> 2;          // token slot 0..7 inside a warp step
     float carry = 1.f;                   // factor the fp32 sums still have to be multiplied by (deferred rescale)
-    uint32_t magic;                      // 0x6400 0x6400 = half2(1024, 1024); in a register on purpose, see splice()
-    asm volatile("mov.b32 %0, 0x64006400;" : "=r"(magic));
 
-    // half2 partial sums -> fp32 sums; keeps every half2 sum below 8 tokens' worth of weight
+    // half2 partial sums -> fp32 sums, every 8 tokens of a lane
     auto flush = [&]() {
         if (__any_sync(kFullMask, carry != 1.f)) {
 #pragma unroll
@@ -458,10 +452,10 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float2 f = __half22float2(acc_h[i]);
+            const float2 f = __half22float2(as_half2(acc_b[i]));
             acc[2 * i] += f.x;
             acc[2 * i + 1] += f.y;
-            acc_h[i] = __float2half2_rn(0.f);
+            acc_b[i] = 0u;
         }
     };
 
@@ -469,8 +463,7 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
     uint32_t parity = 0;
     int it_done = 0;  // pages fully consumed
     for (int it = 0; it < warp_pages; ++it) {
-        if (!mbar_wait(bar_addr + 8 * stage, parity)) failed = true;
-        if (__any_sync(kFullMask, failed)) { failed = true; break; }
+        if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
         const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
         const uint32_t k_residual = k_anchor + C::kAnchorBytes;
         const uint32_t v_anchor = k_anchor + C::kPlaneBytes;
@@ -539,9 +532,9 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
                 acc_off0 *= f;
                 acc_off1 *= f;
                 carry *= f;
-                const __half2 f2 = __float2half2_rn(f);
+                const uint32_t f2 = half2_from(f);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc_h[i] = __hmul2(acc_h[i], f2);
+                for (int i = 0; i < 16; ++i) acc_b[i] = hmul2_raw(acc_b[i], f2);
                 m = score;
             }
             const float prob = live_token ? fast_exp2(score - m) : 0.f;
@@ -554,43 +547,57 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
                 const float2 so = fp8x2_to_float2(lds8(meta) | (lds8(meta + P * C::kAnchorGroups) << 8));
                 float pa = prob;  // the V plane stores its own coefficient
                 if (C::kResidual) pa *= bf16_bits_to_float(lds16(v_residual + kResidualAlphaAt + 2 * t));
-                const __half2 w2 = __float2half2_rn(pa * so.x);
                 const float off = pa * so.y;
                 acc_off0 += off;
                 acc_off1 += off;
+                const float weight = pa * so.x * kWeightUp;
+                const uint32_t w_low = half2_from(weight), w_high = half2_from(weight * 0.0625f);
                 const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    __half2 c[4];
-                    expand_int4(words[w], magic, c);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc_h[4 * w + i] = __hfma2(w2, c[i], acc_h[4 * w + i]);
+                    const uint32_t upper = words[w] >> 8;
+                    acc_b[4 * w + 0] = hfma2_raw(words[w] & 0x000F000Fu, w_low, acc_b[4 * w + 0]);
+                    acc_b[4 * w + 1] = hfma2_raw(words[w] & 0x00F000F0u, w_high, acc_b[4 * w + 1]);
+                    acc_b[4 * w + 2] = hfma2_raw(upper & 0x000F000Fu, w_low, acc_b[4 * w + 2]);
+                    acc_b[4 * w + 3] = hfma2_raw(upper & 0x00F000F0u, w_high, acc_b[4 * w + 3]);
                 }
             }
             if (C::kResidual) {
                 const uint2 codes = lds64(v_residual + t * C::kResidualCode + 8 * js);
                 const uint32_t meta = v_residual + P * C::kResidualCode + t * C::kResidualGroups;
-                __half2 w0, w1;
+                float s0, s1;
                 if (C::RG == 32) {
                     const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * C::kResidualGroups + js) << 8));
-                    w0 = w1 = __float2half2_rn(prob * so.x);
+                    s0 = s1 = so.x;
                     acc_off0 += prob * so.y;
                     acc_off1 += prob * so.y;
                 } else {
                     const float2 s01 = fp8x2_to_float2(lds16(meta + 2 * js));
                     const float2 o01 = fp8x2_to_float2(lds16(meta + P * C::kResidualGroups + 2 * js));
-                    w0 = __float2half2_rn(prob * s01.x);
-                    w1 = __float2half2_rn(prob * s01.y);
+                    s0 = s01.x;
+                    s1 = s01.y;
                     acc_off0 += prob * o01.x;
                     acc_off1 += prob * o01.y;
                 }
-                __half2 c[8];
-                expand_int2(codes.x, magic, c);
+                const uint32_t quarter = 0x34003400u, sixteenth = 0x2C002C00u, sixtyfourth = 0x24002400u;  // half2
+                const uint32_t words[2] = {codes.x, codes.y};
+                uint32_t wk[4];  // weights for code positions 0..3 of a byte: w, w/4, w/16, w/64
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc_h[i] = __hfma2(w0, c[i], acc_h[i]);
-                expand_int2(codes.y, magic, c);
+                for (int v = 0; v < 2; ++v) {
+                    if (v == 0 || C::RG == 16) {
+                        wk[0] = half2_from(prob * (v == 0 ? s0 : s1) * kWeightUp);
+                        wk[1] = hmul2_raw(wk[0], quarter);      // exact: powers of two
+                        wk[2] = hmul2_raw(wk[0], sixteenth);
+                        wk[3] = hmul2_raw(wk[0], sixtyfourth);
+                    }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc_h[8 + i] = __hfma2(w1, c[i], acc_h[8 + i]);
+                    for (int b = 0; b < 2; ++b) {
+                        const uint32_t tb = prmt(words[v], 0u, b == 0 ? 0x4140u : 0x4342u);  // bytes [2b, 0, 2b+1, 0]
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            acc_b[8 * v + 4 * b + k] = hfma2_raw(tb & (0x00030003u << (2 * k)), wk[k], acc_b[8 * v + 4 * b + k]);
+                    }
+                }
             }
         }
 
@@ -608,6 +615,8 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
         if (++stage == C::kStages) { stage = 0; parity ^= 1u; }
         it_done = it + 1;
     }
+    __syncwarp();
+    failed = __any_sync(kFullMask, failed);
     if (failed) {
         if (lane == 0) atomicExch(p.status, 1);
         // Copies already issued still target this CTA's shared memory: give each one more bounded wait.
@@ -638,7 +647,7 @@ __global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_con
             const int pair = e >> 1, b = pair >> 2, i = pair & 3;
             const int local = 8 * b + i + 4 * (e & 1);  // channel inside the slice
             const float off = local < 16 ? acc_off0 : acc_off1;
-            scratch[local] = (acc[e] + off) * f_slot;
+            scratch[local] = (acc[e] * kSumDown + off) * f_slot;
         }
     }
     __syncwarp();
