@@ -286,7 +286,7 @@ __device__ __forceinline__ void unrotate_history(const AttentionParams& p, int h
 }
 
 template <class C>
-__global__ void __launch_bounds__(kThreads, 3) attention_kernel(const __grid_constant__ AttentionParams p) {
+__global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_constant__ AttentionParams p) {
     constexpr int D = C::D, P = C::P;
     constexpr int kFlushPages = 64 / P;   // a lane adds 8 tokens between flushes
     constexpr float kSlack = 1.f;         // probabilities stay below 2
