@@ -36,6 +36,12 @@
 namespace rq {
 namespace {
 
+#ifndef RQ_ATTENTION_BULK_COPY
+#define RQ_ATTENTION_BULK_COPY 0
+#endif
+// Page staging engine: 1 = one elected lane issues cp.async.bulk copies that complete on an mbarrier,
+// 0 = every lane issues 16-byte cp.async copies tracked by commit groups (fewer instructions per page).
+constexpr bool kBulkCopy = RQ_ATTENTION_BULK_COPY != 0;
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -88,6 +94,22 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+// 16-byte asynchronous copy global -> shared (L1 bypass), one per lane.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Copy `BYTES` (a multiple of 16) with the whole warp: lane l moves chunks l, l+32, ...
+template <int BYTES>
+__device__ __forceinline__ void warp_copy(uint32_t dst, const uint8_t* src, int lane) {
+    constexpr int kChunks = BYTES / 16;
+#pragma unroll
+    for (int i = 0; i < (kChunks + 31) / 32; ++i) {
+        if (32 * (i + 1) <= kChunks || lane + 32 * i < kChunks) cp_async16(dst + 16 * lane + 512 * i, src + 16 * lane + 512 * i);
+    }
 }
 // Bounded wait.  false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -326,27 +348,41 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     uint8_t* ring = smem + C::kOffRing + warp * C::kRingBytes;
     const uint32_t ring_addr = smem_addr(ring);
     const uint32_t bar_addr = smem_addr(barriers + warp * C::kStages);
-    if (lane == 0) {
+    if (kBulkCopy) {
+        if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < C::kStages; ++s) mbar_init(bar_addr + 8 * s, 1);
-        fence_proxy_async();
+            for (int s = 0; s < C::kStages; ++s) mbar_init(bar_addr + 8 * s, 1);
+            fence_proxy_async();
+        }
+        __syncwarp();
     }
-    __syncwarp();
 
     const int64_t page_bytes = static_cast<int64_t>(P) * p.page_width;
     const uint8_t* head_base = p.cache + head * page_bytes;
     const int64_t block_bytes = heads * page_bytes;
     const int anchor_at = P * p.anchor_offset, residual_at = P * p.residual_offset;
-    auto issue = [&](int block, int stage) {  // lane 0 only
+    auto issue = [&](int block, int stage) {
         const uint8_t* k_page = head_base + block * block_bytes;
         const uint8_t* v_page = k_page + p.plane_stride;
-        const uint32_t dst = ring_addr + stage * C::kStageBytes, bar = bar_addr + 8 * stage;
-        mbar_expect_tx(bar, C::kStageBytes);
-        bulk_load(dst, k_page + anchor_at, C::kAnchorBytes, bar);
-        if (C::kResidual) bulk_load(dst + C::kAnchorBytes, k_page + residual_at, C::kResidualBytes, bar);
-        bulk_load(dst + C::kPlaneBytes, v_page + anchor_at, C::kAnchorBytes, bar);
-        if (C::kResidual)
-            bulk_load(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, C::kResidualBytes, bar);
+        const uint32_t dst = ring_addr + stage * C::kStageBytes;
+        if (kBulkCopy) {
+            if (lane == 0) {
+                const uint32_t bar = bar_addr + 8 * stage;
+                fence_proxy_async();
+                mbar_expect_tx(bar, C::kStageBytes);
+                bulk_load(dst, k_page + anchor_at, C::kAnchorBytes, bar);
+                if (C::kResidual) bulk_load(dst + C::kAnchorBytes, k_page + residual_at, C::kResidualBytes, bar);
+                bulk_load(dst + C::kPlaneBytes, v_page + anchor_at, C::kAnchorBytes, bar);
+                if (C::kResidual)
+                    bulk_load(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, C::kResidualBytes, bar);
+            }
+        } else {
+            warp_copy<C::kAnchorBytes>(dst, k_page + anchor_at, lane);
+            if (C::kResidual) warp_copy<C::kResidualBytes>(dst + C::kAnchorBytes, k_page + residual_at, lane);
+            warp_copy<C::kAnchorBytes>(dst + C::kPlaneBytes, v_page + anchor_at, lane);
+            if (C::kResidual)
+                warp_copy<C::kResidualBytes>(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, lane);
+        }
     };
     // block ids of this warp's next 32 pages, one per lane
     int batch_base = 0;
@@ -358,10 +394,15 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     load_batch(0);
     int issued = 0;
     {
-        const int first = min(C::kStages, warp_pages);
-        for (; issued < first; ++issued) {
-            const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
-            if (lane == 0) issue(block, issued);
+        // commit-group bookkeeping wants exactly kStages groups here and one more per loop iteration
+#pragma unroll
+        for (int s = 0; s < C::kStages; ++s) {
+            if (s < warp_pages) {
+                const int block = __shfl_sync(kFullMask, my_block, s);
+                issue(block, s);
+                ++issued;
+            }
+            if (!kBulkCopy) cp_async_commit();
         }
     }
 
@@ -463,7 +504,12 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     uint32_t parity = 0;
     int it_done = 0;  // pages fully consumed
     for (int it = 0; it < warp_pages; ++it) {
-        if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
+        if (kBulkCopy) {
+            if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
+        } else {
+            cp_async_wait<C::kStages - 1>();
+            __syncwarp();  // the other lanes' chunks of this page have landed too
+        }
         const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
         const uint32_t k_residual = k_anchor + C::kAnchorBytes;
         const uint32_t v_anchor = k_anchor + C::kPlaneBytes;
@@ -606,12 +652,10 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
         if (issued < warp_pages) {
             if (issued - batch_base == 32) load_batch(issued);
             const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
-            if (lane == 0) {
-                fence_proxy_async();
-                issue(block, stage);
-            }
+            issue(block, stage);
             ++issued;
         }
+        if (!kBulkCopy) cp_async_commit();
         if (++stage == C::kStages) { stage = 0; parity ^= 1u; }
         it_done = it + 1;
     }
@@ -627,6 +671,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
             if (++s2 == C::kStages) { s2 = 0; par2 ^= 1u; }
         }
     }
+    if (!kBulkCopy) cp_async_wait<0>();
     flush();
 
     // ---- fold the 8 token slots of the warp ------------------------------------------------------------
