@@ -402,10 +402,21 @@ def run_gpu(args):
                                 qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
         return run
 
-    reps = max(1, 48 // layers)
-    ms_res = timed(attention_only(0), 1)                     # warm
-    ms_res = timed(attention_only(0), reps) / (reps * layers)
-    ms_anchor = timed(attention_only(3), reps) / (reps * layers)
+    def graph_timed(fn, replays):
+        """Capture `fn` once (after an eager warm-up) and time `replays` replays: per-kernel device time without
+        the Python launch overhead of eager calls."""
+        with torch.cuda.stream(stream):
+            fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        timed(g.replay, 1)
+        return timed(g.replay, replays)
+
+    reps = max(3, 48 // layers)
+    ms_res = graph_timed(attention_only(0), reps) / (reps * layers)
+    ms_anchor = graph_timed(attention_only(3), reps) / (reps * layers)
     bytes_res = attention_bytes(B, L, args.group, False)
     bytes_anchor = attention_bytes(B, L, args.group, True)
     peak, peak_kind = measured_peak()
@@ -415,7 +426,7 @@ def run_gpu(args):
         for layer in range(layers):
             _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
                            key_rot, None, None, records, "anchor", 3, "ls")
-    ms_quant = timed(quantize_only, reps) / (reps * layers)
+    ms_quant = graph_timed(quantize_only, reps) / (reps * layers)
     _cuda.attention_status(device)
 
     sweep = None
@@ -435,8 +446,7 @@ def run_gpu(args):
                             _cuda.attention(q[layer, loop, :batch], k_live[layer, loop, :batch], v_live[layer, loop, :batch],
                                             caches[layer], out[layer, loop, :batch], starts, lens, block_table[:batch],
                                             key_rot, None, None, records, "anchor", 3, loop)
-                    timed(run, 1)
-                    t = timed(run, reps) / (reps * layers)
+                    t = graph_timed(run, reps) / (reps * layers)
                     nbytes = attention_bytes(batch, context, args.group, loop == 3)
                     sweep.append({"batch": batch, "context": context, "loop": loop, "us": 1000 * t,
                                   "gbs": nbytes / (t * 1e-3) / 1e9, "frac": nbytes / (t * 1e-3) / 1e9 / peak})

@@ -597,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
                 acc_off0 += off;
                 acc_off1 += off;
                 const float weight = pa * so.x * kWeightUp;
-                const uint32_t w_low = half2_from(weight), w_high = half2_from(weight * 0.0625f);
+                const uint32_t w_low = half2_from(weight), w_high = hmul2_raw(w_low, 0x2C002C00u);  // w/16, exact
                 const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
