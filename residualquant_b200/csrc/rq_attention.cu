@@ -29,6 +29,7 @@
 // Every wait on an mbarrier is bounded; on expiry the kernel raises the workspace status word, drains what it
 // can and returns.
 #include <atomic>
+#include <type_traits>
 
 #include "rq_common.cuh"
 #include "rq_kernels.h"
@@ -46,6 +47,7 @@ constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kNever = -1e30f;  // exponent of a stream that has seen no token: exp2(kNever - anything real) == 0
 
 // P[i][j] == -1  <=>  bit j of kPaleyRow[i]  <=>  bit i of kPaleyCol[j]
 __constant__ uint32_t kPaleyRowA[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0xed0, 0xda2,
@@ -412,16 +414,17 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     __syncthreads();
 
     // The K side runs on integer dot products (dp2a: two s16 x u8 products per instruction): the query slice is
-    // quantized once per CTA to 12 bits (anchor) / 10 bits (residual) of its largest magnitude and pre-shifted so
+    // quantized once per CTA to 11 bits (anchor) / 10 bits (residual) of its largest magnitude and pre-shifted so
     // that codes can be used where they sit in the packed word, without shifting them down:
-    //   INT4 word & 0x0F0F0F0F -> bytes c, word & 0xF0F0F0F0 -> bytes 16c: even channels carry 16*q, odd ones q
+    //   INT4 word itself -> bytes c_even + 16 c_odd, word & 0xF0F0F0F0 -> bytes 16 c_odd: even channels carry 16*q,
+    //        odd ones q - 16*q_even (which cancels what the unmasked byte added)
     //   INT2 word & (0x03030303 << 2k) -> bytes 4^k c:                     channel position k carries 4^(3-k)*q
     const int j = lane & 3;              // slice: channels 32j .. 32j+31
     const bool slice_ok = 32 * j < D;
     const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
     const float qmax = misc[2];
-    const float to_anchor = qmax > 0.f ? 2047.f / qmax : 0.f, to_residual = qmax > 0.f ? 511.f / qmax : 0.f;
-    const float anchor_unit = qmax / 2047.f, residual_unit = qmax / 511.f;
+    const float to_anchor = qmax > 0.f ? 1900.f / qmax : 0.f, to_residual = qmax > 0.f ? 511.f / qmax : 0.f;
+    const float anchor_unit = qmax / 1900.f, residual_unit = qmax / 511.f;
     uint32_t qa[16];                     // anchor operands, 4 per code word
     uint32_t qr[C::kResidual ? 16 : 1];  // residual operands, 8 per code word
     float qsum_a = 0.f;                  // sum of the quantized query over the slice, anchor resolution
@@ -440,8 +443,9 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
         for (int w = 0; w < 4; ++w) {
             qa[4 * w + 0] = pack_s16(16 * ia[8 * w + 0], 16 * ia[8 * w + 2]);
             qa[4 * w + 1] = pack_s16(16 * ia[8 * w + 4], 16 * ia[8 * w + 6]);
-            qa[4 * w + 2] = pack_s16(ia[8 * w + 1], ia[8 * w + 3]);
-            qa[4 * w + 3] = pack_s16(ia[8 * w + 5], ia[8 * w + 7]);
+            // the even operands meet the UNMASKED byte c_even + 16*c_odd; the odd operands take that excess back
+            qa[4 * w + 2] = pack_s16(ia[8 * w + 1] - 16 * ia[8 * w + 0], ia[8 * w + 3] - 16 * ia[8 * w + 2]);
+            qa[4 * w + 3] = pack_s16(ia[8 * w + 5] - 16 * ia[8 * w + 4], ia[8 * w + 7] - 16 * ia[8 * w + 6]);
         }
         if (C::kResidual) {
             int ir[32];
@@ -472,10 +476,11 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     const float residual_dot_unit = residual_unit * 0.015625f;  // ... a factor 64
 
     // ---- page loop -----------------------------------------------------------------------------------
-    float m = -INFINITY, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
+    float m = kNever, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
     uint32_t acc_b[16];                  // half2 partial sums of V, pair 4b+i = (channel 8b+i, channel 8b+i+4)
     float acc[32];
-    float acc_off0 = 0.f, acc_off1 = 0.f;  // offset part of V for channels 0..15 / 16..31 of the slice
+    constexpr bool kTwoOffsets = C::kResidual && C::RG == 16;  // two residual groups per 32-channel slice
+    float acc_off0 = 0.f, acc_off1 = 0.f;  // offset part of V for channels 0..15 / 16..31 of the slice (one sum if equal)
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc_b[i] = 0u;
 #pragma unroll
@@ -516,12 +521,15 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
         const uint32_t v_residual = v_anchor + C::kAnchorBytes;
         constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
         const int first_token = (page_begin + warp + kWarps * it) * P;
-        const int valid = min(P, history - first_token);
+        const int valid = history - first_token;  // >= P for every page but the last one of the history
 
+        // Full pages run without any per-token predicate; only the last page of a sequence can be partial.
+        auto process_page = [&](auto partial_tag) {
+        constexpr bool kPartial = decltype(partial_tag)::value;
 #pragma unroll
         for (int sub = 0; sub < P / 8; ++sub) {
             const int t = sub * 8 + slot;
-            const bool live_token = t < valid;
+            const bool live_token = !kPartial || t < valid;
             // ---------------- K: score of token t against the query slice (integer dot products) ----------------
             float part;
             {
@@ -532,9 +540,9 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
                 int d0 = 0, d1 = 0;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    const uint32_t even = words[w] & 0x0F0F0F0Fu, odd = words[w] & 0xF0F0F0F0u;
-                    d0 = dp2a_lo(qa[4 * w + 0], even, d0);
-                    d1 = dp2a_hi(qa[4 * w + 1], even, d1);
+                    const uint32_t odd = words[w] & 0xF0F0F0F0u;
+                    d0 = dp2a_lo(qa[4 * w + 0], words[w], d0);
+                    d1 = dp2a_hi(qa[4 * w + 1], words[w], d1);
                     d0 = dp2a_lo(qa[4 * w + 2], odd, d0);
                     d1 = dp2a_hi(qa[4 * w + 3], odd, d1);
                 }
@@ -567,7 +575,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
             }
             part += __shfl_xor_sync(kFullMask, part, 1);
             part += __shfl_xor_sync(kFullMask, part, 2);
-            const float score = live_token ? part : -INFINITY;
+            const float score = live_token ? part : kNever;
 
             // ---------------- online softmax of the token slot ----------------
             // `m` is the stream's reference exponent, not its exact maximum: it only moves when a score exceeds it
@@ -576,7 +584,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
                 const float f = fast_exp2(m - score);  // m == -inf gives 0
                 l *= f;
                 acc_off0 *= f;
-                acc_off1 *= f;
+                if (kTwoOffsets) acc_off1 *= f;
                 carry *= f;
                 const uint32_t f2 = half2_from(f);
 #pragma unroll
@@ -595,7 +603,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
                 if (C::kResidual) pa *= bf16_bits_to_float(lds16(v_residual + kResidualAlphaAt + 2 * t));
                 const float off = pa * so.y;
                 acc_off0 += off;
-                acc_off1 += off;
+                if (kTwoOffsets) acc_off1 += off;
                 const float weight = pa * so.x * kWeightUp;
                 const uint32_t w_low = half2_from(weight), w_high = hmul2_raw(w_low, 0x2C002C00u);  // w/16, exact
                 const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
@@ -616,7 +624,6 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
                     const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * C::kResidualGroups + js) << 8));
                     s0 = s1 = so.x;
                     acc_off0 += prob * so.y;
-                    acc_off1 += prob * so.y;
                 } else {
                     const float2 s01 = fp8x2_to_float2(lds16(meta + 2 * js));
                     const float2 o01 = fp8x2_to_float2(lds16(meta + P * C::kResidualGroups + 2 * js));
@@ -646,6 +653,8 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
                 }
             }
         }
+        };
+        if (valid >= P) process_page(std::false_type{}); else process_page(std::true_type{});
 
         if ((it + 1) % kFlushPages == 0) flush();
         __syncwarp();  // every lane has finished reading this stage
@@ -679,7 +688,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 4));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 8));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 16));
-    const float f_slot = m == -INFINITY ? 0.f : fast_exp2(m - m_warp);
+    const float f_slot = fast_exp2(m - m_warp);  // untouched streams carry zero sums, so their factor is irrelevant
     float l_warp = l * f_slot;
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 4);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 8);
@@ -691,7 +700,7 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
         for (int e = 0; e < 32; ++e) {
             const int pair = e >> 1, b = pair >> 2, i = pair & 3;
             const int local = 8 * b + i + 4 * (e & 1);  // channel inside the slice
-            const float off = local < 16 ? acc_off0 : acc_off1;
+            const float off = (kTwoOffsets && local >= 16) ? acc_off1 : acc_off0;
             scratch[local] = (acc[e] * kSumDown + off) * f_slot;
         }
     }
@@ -714,14 +723,14 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     __syncthreads();
 
     // ---- fold the warps of the CTA: thread c owns channel c ---------------------------------------------
-    float part_m = -INFINITY;
+    float part_m = kNever;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) part_m = fmaxf(part_m, warp_stat[2 * w]);
     float part_l = 0.f, value = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
         const float mw = warp_stat[2 * w];
-        const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - part_m);
+        const float f = fast_exp2(mw - part_m);
         part_l += warp_stat[2 * w + 1] * f;
         if (tid < D) value += warp_acc[w * D + tid] * f;
     }
@@ -742,13 +751,13 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
         if (misc[0] == 0.f) return;
         __threadfence();
         const float* all = p.partials + (static_cast<int64_t>(row) * heads + head) * splits * (D + 2);
-        part_m = -INFINITY;
+        part_m = kNever;
         for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * (D + 2)));
         part_l = 0.f;
         value = 0.f;
         for (int s = 0; s < splits; ++s) {
             const float ms = __ldcg(all + s * (D + 2));
-            const float f = ms == -INFINITY ? 0.f : fast_exp2(ms - part_m);
+            const float f = fast_exp2(ms - part_m);
             part_l += __ldcg(all + s * (D + 2) + 1) * f;
             if (tid < D) value += __ldcg(all + s * (D + 2) + 2 + tid) * f;
         }
