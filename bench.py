@@ -264,7 +264,7 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
 
-    from residualquant_b200 import _cuda
+    from residualquant_b200 import _cuda, sharding
     from residualquant_b200 import build as kernel_build
 
     rank = int(os.environ.get("RANK", "0"))
@@ -347,12 +347,7 @@ def run_gpu(args):
             stop.record(stream)
         stop.synchronize()
         barrier()
-        ms = start.elapsed_time(stop)
-        if world > 1:
-            t = torch.tensor([ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return sharding.max_over_ranks(start.elapsed_time(stop), device)
 
     sampler = ClockSampler(local_rank)
     # ---------------- device-resident throughput ----------------

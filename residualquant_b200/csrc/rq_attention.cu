@@ -69,8 +69,8 @@ struct Config {
     static constexpr int kResidualBytes = kResidual ? P * (kResidualCode + 2 * kResidualGroups + 2) : 0;
     static constexpr int kPlaneBytes = kAnchorBytes + kResidualBytes;
     static constexpr int kStageBytes = 2 * kPlaneBytes;
-    static constexpr int kStagesRaw = 14336 / kStageBytes;
-    static constexpr int kStages = kStagesRaw < 2 ? 2 : (kStagesRaw > 6 ? 6 : kStagesRaw);
+    // pages in flight per warp; sized so that four CTAs (16 warps) fit in one SM's shared memory at block size 16
+    static constexpr int kStages = P == 16 ? (kResidual ? 3 : 4) : 2;
     static constexpr int kRingBytes = kStages * kStageBytes;
     static_assert(kAnchorBytes % 16 == 0 && kResidualBytes % 16 == 0, "bulk copies need 16-byte multiples");
     static_assert(kRingBytes >= 32 * 33 * 4, "the ring doubles as the warp's merge scratch");

@@ -1,0 +1,89 @@
+"""Host-side mirror of the reference's per-group state and of the decode branch of its attention hook.
+
+`DeferredKVGroup` follows plugins/residual_quantization/src/residual_quantization/install_model.py:17-52: the K/V of
+the loops of a KV group are held back (cloned) until the group's last loop arrives, then all records go to
+`quantize` in one call.  `PackedDecodeAttention` follows the decode path of `PackedImpl.forward` and `_store_kv`
+(packed_backend.py:28-137): attention over the packed cache plus the live token, then stage/quantize.  Neither
+touches vLLM; a vLLM attention backend only has to forward its `forward(...)` arguments here.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _cuda
+
+
+class DeferredKVGroup:
+    """Owns the packed format of one KV group and keeps raw K/V until every loop of the group has been seen."""
+
+    def __init__(self, records: Sequence[Sequence[int]], page_tokens: int, reference_mode: str = "anchor",
+                 anchor_index: Optional[int] = None, coefficient_method: str = "ls"):
+        self.records = tuple(tuple(int(v) for v in r) for r in records)
+        if not self.records:
+            raise ValueError("Every packed group must contain at least one record")
+        if reference_mode not in ("adjacent", "anchor"):
+            raise ValueError("Unsupported reference")
+        self.anchor_index = len(self.records) - 1 if anchor_index is None else int(anchor_index)
+        if reference_mode == "adjacent" and self.anchor_index != 0:
+            raise ValueError("Adjacent reference currently requires anchor_index=0")
+        if coefficient_method not in ("unit", "norm", "ls"):
+            raise ValueError("Unsupported coefficient method")
+        self.page_tokens = int(page_tokens)
+        self.reference_mode = reference_mode
+        self.coefficient_method = coefficient_method
+        self.pending: List[Tuple[torch.Tensor, torch.Tensor]] = []
+
+    def page_width(self, head_dim: int) -> int:
+        """Bytes per token of one (head, plane): codes + FP8 scale/offset per group + bf16 alpha, over all records
+        (install_model.py:34-38)."""
+        code_bytes = head_dim * sum(bits for bits, _ in self.records) // 8
+        metadata_bytes = 2 * sum(head_dim // group for _, group in self.records)
+        return code_bytes + metadata_bytes + 2 * len(self.records)
+
+    def cache_shape(self, num_blocks: int, num_kv_heads: int, head_dim: int) -> Tuple[int, int, int, int, int]:
+        """(2, blocks, heads, block_size, page_width), the reference's PackedBackend.get_kv_cache_shape
+        (packed_backend.py:222-223)."""
+        return (2, num_blocks, num_kv_heads, self.page_tokens, self.page_width(head_dim))
+
+    def stage(self, key: torch.Tensor, value: torch.Tensor):
+        """Non-final loops: keep a copy, return None.  Final loop: return every (K, V) pair in loop order and reset.
+        The completing call borrows its input, so a one-record group never copies."""
+        if len(self.pending) + 1 == len(self.records):
+            records = self.pending + [(key, value)]
+            self.pending = []
+            return records
+        self.pending.append((key.clone(), value.clone()))
+        return None
+
+
+class PackedDecodeAttention:
+    """One attention slot (loop `group_loop_index` of a group) of a looped decoder, decode path only."""
+
+    def __init__(self, group: DeferredKVGroup, group_loop_index: int, key_rotation=None, value_rotation=None,
+                 key_mean: Optional[torch.Tensor] = None):
+        if not 0 <= group_loop_index < len(group.records):
+            raise ValueError("loop index outside the group")
+        self.packed_group = group
+        self.group_loop_index = group_loop_index
+        self.key_rotation = key_rotation
+        self.value_rotation = value_rotation
+        self.key_mean = key_mean
+
+    def forward(self, query, key, value, kv_cache, query_start_loc, seq_lens, block_table, slot_mapping, output):
+        """query/key/value/output: bf16 [tokens, heads, head_dim]; writes `output` in place and returns it."""
+        if output is None:
+            raise ValueError("BF16 output required")
+        group = self.packed_group
+        records = [list(r) for r in group.records]
+        _cuda.attention(query, key, value, kv_cache, output, query_start_loc, seq_lens, block_table,
+                        self.key_rotation, self.value_rotation, self.key_mean, records, group.reference_mode,
+                        group.anchor_index, self.group_loop_index)
+        actual = slot_mapping.numel()
+        staged = group.stage(key[:actual], value[:actual])
+        if staged is not None:
+            _cuda.quantize(staged, kv_cache, slot_mapping, self.key_rotation, self.value_rotation, self.key_mean,
+                           records, group.reference_mode, group.anchor_index, group.coefficient_method)
+        return output

@@ -200,3 +200,59 @@ def test_argument_errors_raise_runtime_error():
     narrow = torch.zeros((2, case.num_blocks, case.heads, 16, 168), dtype=torch.uint8, device="cuda")
     with pytest.raises(RuntimeError, match="No compiled packed CUDA kernel"):
         call(records=[[2, 32]] * 4, loop_index=0, kv_cache=narrow)
+
+
+def test_large_value_magnitudes_stay_accurate_and_finite():
+    """V four times larger than the benchmark distribution (group ranges of ~100) stays inside the half2
+    accumulation range: the error scales with the data, so the absolute part of the tolerance is scaled by the same
+    factor.  Absurd magnitudes (FP8 parameters saturated) must at least give finite outputs."""
+    case = helpers.make_case(40, 128, 2, [260, 33], 32, 16)
+    for rows in case.values:
+        rows *= 4.0                                    # bf16-exact scaling; ranges of ~100 in outlier groups
+    cache = helpers.oracle_cache(case)
+    for loop in (0, 3):
+        cache_t = torch.from_numpy(cache).cuda()
+        got = G.gpu_attention(case, cache_t, loop).float().cpu().numpy()
+        want = helpers.oracle_attention(case, cache, loop)
+        assert np.all(np.abs(got - want) <= 4.0 * ATOL + RTOL * np.abs(want))
+    huge = helpers.make_case(41, 128, 2, [70], 32, 16)
+    for rows in huge.values:
+        rows *= 256.0
+    cache = helpers.oracle_cache(huge)
+    out = G.gpu_attention(huge, torch.from_numpy(cache).cuda(), 0).float()
+    assert torch.isfinite(out).all()
+
+
+def test_decode_step_through_the_group_mirror():
+    """Four loop slots of one group: attention per loop, K/V held back, one quantize on the last loop
+    (reference: packed_backend.py:28-137, install_model.py:40-52)."""
+    from oracle import rq_oracle as O
+    from residualquant_b200.group import DeferredKVGroup, PackedDecodeAttention
+
+    case = helpers.make_case(42, 128, 4, [150, 47], 32, 16)
+    L = case.layout
+    kr, vr = G.device_rotations(case)
+    group = DeferredKVGroup(L.records, L.page_tokens)
+    slots = [PackedDecodeAttention(group, i, kr, vr) for i in range(4)]
+    cache_np = helpers.oracle_cache(case)
+    cache = torch.from_numpy(cache_np).cuda()
+    r = len(case.seq_lens)
+    qsl = torch.arange(r + 1, dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    live_slots = torch.tensor(
+        [int(case.block_table[i, (case.seq_lens[i] - 1) // 16]) * 16 + (case.seq_lens[i] - 1) % 16 for i in range(r)],
+        dtype=torch.int64, device="cuda")
+    q = G.bf16(case.query)
+    for loop in range(4):
+        k = G.bf16(case.keys[loop][case.live_rows])
+        v = G.bf16(case.values[loop][case.live_rows])
+        out = slots[loop].forward(q, k, v, cache, qsl, seq, table, live_slots, torch.zeros_like(q))
+        torch.cuda.synchronize()
+        want = helpers.oracle_attention(case, cache_np, loop)
+        assert np.all(np.abs(out.float().cpu().numpy() - want) <= ATOL + RTOL * np.abs(want))
+        assert len(group.pending) == (loop + 1) % 4
+    okr, ovr = helpers.oracle_rotations(case)
+    O.quantize([(k[case.live_rows], v[case.live_rows]) for k, v in zip(case.keys, case.values)], cache_np,
+               live_slots.cpu().numpy(), L, okr, ovr, None)
+    assert np.array_equal(cache.cpu().numpy(), cache_np)
