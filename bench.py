@@ -55,24 +55,34 @@ def parse_args():
     p.add_argument("--context", type=int, default=8192)
     p.add_argument("--group", type=int, default=32, choices=[16, 32])
     p.add_argument("--layers", type=int, default=24)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--head-dim", type=int, default=128, choices=[128, 96])
+    p.add_argument("--page", type=int, default=16, choices=[16, 32], help="vLLM block size")
+    p.add_argument("--compare-bf16", action="store_true",
+                   help="also time a BF16-KV decode attention (torch SDPA, contiguous KV) of one layer's 4 loops")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--sweep", action="store_true", help="also time attention alone over the batch x context grid")
     return p.parse_args()
 
 
-def record_bytes(bits, group, dim=HEAD_DIM):
+def record_bytes(bits, group, dim=None):
+    dim = HEAD_DIM if dim is None else dim
     return dim * bits // 8 + 2 * dim // group + 2
 
 
-def attention_bytes(batch, context, group, loop_is_anchor, heads=HEADS, dim=HEAD_DIM):
+def attention_bytes(batch, context, group, loop_is_anchor, heads=None, dim=None):
     """Algorithmic bytes of one attention launch: every cached token's anchor record without its alpha column,
     plus the loop's own residual record, for K and V; plus q, live k, live v, out in bf16."""
+    heads = HEADS if heads is None else heads
+    dim = HEAD_DIM if dim is None else dim
     anchor = record_bytes(4, 32, dim) - 2
     per_token = anchor if loop_is_anchor else anchor + record_bytes(2, group, dim)
     return batch * (context - 1) * heads * 2 * per_token + batch * heads * dim * 8
 
 
-def quantize_bytes(tokens, group, heads=HEADS, dim=HEAD_DIM):
+def quantize_bytes(tokens, group, heads=None, dim=None):
+    heads = HEADS if heads is None else heads
+    dim = HEAD_DIM if dim is None else dim
     width = 3 * record_bytes(2, group, dim) + record_bytes(4, 32, dim)
     return 2 * 4 * tokens * heads * dim * 2 + 2 * tokens * heads * width
 
@@ -174,7 +184,7 @@ def run_reference(args):
 def workload_config(args):
     return {
         "workload": f"config1 kernel sweep point: batch {args.batch} x context {args.context}, INT2 g{args.group} "
-                    f"residuals + INT4 g32 anchor, {args.layers} layers x 4 loops, 16 heads x 128, block 16, "
+                    f"residuals + INT4 g32 anchor, {args.layers} layers x 4 loops, {args.heads} heads x {args.head_dim}, block {args.page}, "
                     "CUDA-graph decode step (4 attention + 1 quantize launch per layer)",
         "batch_per_gpu": args.batch,
         "context": args.context,
@@ -446,6 +456,27 @@ def run_gpu(args):
     ms_quant = graph_timed(quantize_only, reps) / (reps * layers)
     _cuda.attention_status(device)
 
+    bf16 = None
+    if args.compare_bf16 and rank == 0:
+        # One layer's four loop attentions over BF16 K/V of the same shape (contiguous [B, H, L, D], no paging, library
+        # kernel): the comparator the packed path has to beat.  4 loops x (K + V) = 8 tensors of B*H*L*D bf16.
+        import torch.nn.functional as F
+        kv = [torch.randn(B, HEADS, L, HEAD_DIM, device=device, dtype=torch.bfloat16) for _ in range(8)]
+        qb = torch.randn(4, B, HEADS, 1, HEAD_DIM, device=device, dtype=torch.bfloat16)
+        ob = torch.empty_like(qb)
+
+        def bf16_layer():
+            for loop in range(4):
+                ob[loop] = F.scaled_dot_product_attention(qb[loop], kv[2 * loop], kv[2 * loop + 1])
+        ms_bf16 = graph_timed(bf16_layer, 5) / 5
+        bytes_bf16 = 8 * B * HEADS * L * HEAD_DIM * 2
+        packed_layer_ms = 3 * ms_res + ms_anchor + ms_quant
+        bf16 = {"kernel": "torch.nn.functional.scaled_dot_product_attention, contiguous BF16 KV, 4 loops of one layer",
+                "ms_per_layer": ms_bf16, "gbs": bytes_bf16 / (ms_bf16 * 1e-3) / 1e9,
+                "packed_ms_per_layer": packed_layer_ms, "speedup": ms_bf16 / packed_layer_ms,
+                "bf16_kv_bytes_per_layer": bytes_bf16}
+        del kv
+
     sweep = None
     if args.sweep and rank == 0:
         sweep = []
@@ -503,6 +534,8 @@ def run_gpu(args):
     }
     if sweep is not None:
         line["sweep"] = sweep
+    if bf16 is not None:
+        line["bf16_kv_comparator"] = bf16
     if not args.no_cpu_baseline:
         cpu_value, description, _ = cpu_sample(L, args.group, layers, B)
         line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port", "sample": description}
@@ -512,7 +545,9 @@ def run_gpu(args):
 
 
 def main():
+    global HEADS, HEAD_DIM, PAGE
     args = parse_args()
+    HEADS, HEAD_DIM, PAGE = args.heads, args.head_dim, args.page
     if args.impl == "reference":
         run_reference(args)
     else:
