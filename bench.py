@@ -454,6 +454,18 @@ def run_gpu(args):
             _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
                            key_rot, None, None, records, "anchor", 3, "ls")
     ms_quant = graph_timed(quantize_only, reps) / (reps * layers)
+
+    # prefill-sized write: two full prompts (2 x context tokens) of layer 0 re-quantized in one call
+    prefill_tokens = min(2, B) * L
+    pk, pv = stack["rows"](prefill_tokens), stack["rows"](prefill_tokens)
+    positions = torch.arange(L, device=device)
+    prefill_slots = torch.cat([block_table[b, positions // PAGE].long() * PAGE + positions % PAGE
+                               for b in range(min(2, B))])
+
+    def quantize_prefill():
+        _cuda.quantize(list(zip(pk, pv)), caches[0], prefill_slots, key_rot, None, None, records, "anchor", 3, "ls")
+    ms_prefill = graph_timed(quantize_prefill, 5) / 5
+    del pk, pv
     _cuda.attention_status(device)
 
     bf16 = None
@@ -530,6 +542,9 @@ def run_gpu(args):
                             "frac": bytes_anchor / (ms_anchor * 1e-3) / 1e9 / peak},
             "quantize_decode_write": {"us_per_launch": 1000 * ms_quant,
                                       "achieved": quantize_bytes(B, args.group) / (ms_quant * 1e-3) / 1e9},
+            "quantize_prefill_write": {"tokens": prefill_tokens, "us_per_launch": 1000 * ms_prefill,
+                                       "achieved": quantize_bytes(prefill_tokens, args.group) / (ms_prefill * 1e-3) / 1e9,
+                                       "frac": quantize_bytes(prefill_tokens, args.group) / (ms_prefill * 1e-3) / 1e9 / peak},
         },
     }
     if sweep is not None:
