@@ -53,7 +53,7 @@ __device__ __forceinline__ void butterfly_across_lanes(float (&x)[N], int mask, 
 #pragma unroll
     for (int i = 0; i < N; ++i) {
         const float other = __shfl_xor_sync(kFullMask, x[i], mask);
-        x[i] = upper ? __fsub_rn(other, x[i]) : __fadd_rn(x[i], other);
+        x[i] = __fmaf_rn(upper ? -1.f : 1.f, x[i], other);  // other - x or x + other, one rounding either way
     }
 }
 

@@ -27,11 +27,7 @@ __constant__ uint32_t kPaleyCol[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0
 // `j` is the lane's slice (channels 16j .. 16j+15) inside its 8-lane row group.
 template <int D, bool INVERSE>
 __device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign16, float rscale) {
-    if (!INVERSE) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if ((sign16 >> i) & 1u) x[i] = -x[i];
-    }
+    // forward: the sign diagonal has already been applied when the row was loaded
     if (D == 128) {
         butterflies_in_lane<16>(x);
         butterfly_across_lanes<16>(x, 1, (j & 1) != 0);
@@ -123,14 +119,21 @@ __device__ __forceinline__ GroupCode group_quantize(const float (&z)[16], int bi
     out.offset8 = fp8_encode(__fadd_rn(__fsub_rn(center, radius), 0.0f));
     out.scale8 = fp8_encode(__fdiv_rn(__fmul_rn(2.f, radius), levels));
     const float offset = fp8_decode(out.offset8), scale = fp8_decode(out.scale8);
+    // n = (z - offset) / scale, correctly rounded, without a division per channel: with r = RN(1/scale),
+    // q0 = RN(d*r), e = d - q0*scale (exact in one fma), n = RN(q0 + e*r) is the IEEE quotient (the divisor has a
+    // 4-bit significand; checked against exact rational arithmetic for every FP8 scale).
+    // code = floor(n) + (n - floor(n) > 0.5)  ==  ceil(n - 0.5): a half rounds down, n - 0.5 is exact for n >= 0.5.
+    const float r = scale > 0.f ? __frcp_rn(scale) : 0.f;
+    const int top = bits == 2 ? 3 : 15;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         uint32_t code = 0;
         if (scale > 0.f) {
-            const float n = __fdiv_rn(__fsub_rn(z[i], offset), scale);
-            const float fl = floorf(n);
-            const float up = __fsub_rn(n, fl) > 0.5f ? 1.f : 0.f;  // a half rounds down
-            code = static_cast<uint32_t>(fminf(fmaxf(__fadd_rn(fl, up), 0.f), levels));
+            const float d = __fsub_rn(z[i], offset);
+            const float q0 = __fmul_rn(d, r);
+            const float e = __fmaf_rn(-q0, scale, d);
+            const float n = __fmaf_rn(e, r, q0);
+            code = static_cast<uint32_t>(min(max(__float2int_ru(__fsub_rn(n, 0.5f)), 0), top));
         }
         out.code[i] = code;
     }
@@ -167,6 +170,11 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
     uint32_t sign16 = 0;
     if (rotated && j < kSlices)
         sign16 = (p.sign[plane][head * (D / 32) + (j >> 1)] >> (16 * (j & 1))) & 0xffffu;
+    // bit 15 / bit 31 of word i flips channel 2i / 2i+1 of the lane (rows are loaded as pairs of bf16)
+    uint32_t sign_words[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        sign_words[i] = (((sign16 >> (2 * i)) & 1u) << 15) | (((sign16 >> (2 * i + 1)) & 1u) << 31);
     const bool centered = plane == 0 && p.mean != nullptr;
 
     const int P = p.page_tokens;
@@ -174,7 +182,8 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
     uint8_t* page = p.cache + plane * p.plane_stride +
                     (active ? (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width : 0);
 
-    auto load_row = [&](int r, float (&x)[16]) {
+    // flip = apply the rotation's sign diagonal while loading (rows that go straight into the forward rotation)
+    auto load_row = [&](int r, float (&x)[16], bool flip) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = 0.f;
         if (!active) return;
@@ -185,12 +194,16 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
             const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                x[2 * i] = bf16_bits_to_float(w[i] & 0xffffu);
-                x[2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+                const uint32_t flipped = flip ? w[i] ^ sign_words[i] : w[i];  // sign diagonal on the raw bf16 pair
+                x[2 * i] = __uint_as_float(flipped << 16);
+                x[2 * i + 1] = __uint_as_float(flipped & 0xffff0000u);
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) x[i] = __bfloat162float(src[i]);
+            for (int i = 0; i < 16; ++i) {
+                const float v = __bfloat162float(src[i]);
+                x[i] = (flip && ((sign16 >> i) & 1u)) ? -v : v;
+            }
         }
     };
     auto load_mean = [&](int r, float (&m)[16]) {
@@ -251,7 +264,7 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
     float ref[16];  // bf16-valued reconstruction that residuals predict from
     {
         float y[16], mean[16];
-        load_row(anchor, y);
+        load_row(anchor, y, true);
         if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
         load_mean(anchor, mean);
         if (centered) {
@@ -282,7 +295,7 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
     for (int r = 0; r < p.num_records; ++r) {
         if (r == anchor) continue;
         float y[16], mean[16];
-        load_row(r, y);
+        load_row(r, y, p.chain == RQ_CHAIN_KERNEL);
         load_mean(r, mean);
         uint16_t alpha_bits;
         if (p.chain == RQ_CHAIN_KERNEL) {
@@ -299,7 +312,8 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float prediction = bf16_round(__fmul_rn(ref[i], alpha));
-                y[i] = bf16_round(__fsub_rn(y[i], prediction));
+                const float target = bf16_round(__fsub_rn(y[i], prediction));
+                y[i] = ((sign16 >> i) & 1u) ? -target : target;  // sign diagonal of the forward rotation
             }
             if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
         }
