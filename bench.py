@@ -58,6 +58,9 @@ def parse_args():
     p.add_argument("--heads", type=int, default=16)
     p.add_argument("--head-dim", type=int, default=128, choices=[128, 96])
     p.add_argument("--page", type=int, default=16, choices=[16, 32], help="vLLM block size")
+    p.add_argument("--shard", default="sequences", choices=["sequences", "heads"],
+                   help="sequences: every rank owns its own batch (weak scaling, no collective); heads: every rank holds "
+                        "all sequences but only its KV heads and all-gathers the attention output (strong scaling)")
     p.add_argument("--compare-bf16", action="store_true",
                    help="also time a BF16-KV decode attention (torch SDPA, contiguous KV) of one layer's 4 loops")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -185,8 +188,11 @@ def workload_config(args):
     return {
         "workload": f"config1 kernel sweep point: batch {args.batch} x context {args.context}, INT2 g{args.group} "
                     f"residuals + INT4 g32 anchor, {args.layers} layers x 4 loops, {args.heads} heads x {args.head_dim}, block {args.page}, "
-                    "CUDA-graph decode step (4 attention + 1 quantize launch per layer)",
+                    "CUDA-graph decode step (4 attention + 1 quantize launch per layer)"
+                    + ("; KV heads sharded over the ranks, one NCCL all-gather of the output per attention call, eager step"
+                       if args.shard == "heads" else ""),
         "batch_per_gpu": args.batch,
+        "sharding": args.shard,
         "context": args.context,
         "layers": args.layers,
         "l2": "inputs larger than L2 (each layer's packed cache is read once per step)",
@@ -314,6 +320,14 @@ def run_gpu(args):
     else:
         kernel_build.build()
 
+    global HEADS
+    heads_total = args.heads
+    shard_heads = args.shard == "heads"
+    if shard_heads:
+        HEADS = sharding.shard_counts(heads_total, world)[rank]   # this rank's slice of every cache and of q/k/v
+        if HEADS == 0:
+            raise RuntimeError("more ranks than KV heads")
+    replicas = 1 if shard_heads else world                          # independent copies of the batch in the job
     B, L, layers = args.batch, args.context, args.layers
     stack = build_stack(args, device, torch)
     records, caches = stack["records"], stack["caches"]
@@ -339,11 +353,16 @@ def run_gpu(args):
         position = (seq_lens - 1).long()
         slot_mapping.copy_(block_table[batch_index, position // PAGE].long() * PAGE + position % PAGE)
 
+    gathered = [None]
+
     def hot_path():
         for layer in range(layers):
             for loop in range(4):
                 _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer], out[layer, loop],
                                 qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
+                if shard_heads:
+                    # the output projection needs every head: one all-gather of [B, local heads, D] per call
+                    gathered[0] = sharding.gather_heads(out[layer, loop], heads_total)
             _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
                            key_rot, None, None, records, "anchor", 3, "ls")
 
@@ -357,9 +376,17 @@ def run_gpu(args):
         step_body()                      # eager warm-up: workspace, per-variant attributes
     stream.synchronize()
     seq_lens.fill_(L)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        step_body()
+    if shard_heads and world > 1:
+        # The step contains NCCL all-gathers; it is replayed eagerly rather than from a captured graph.
+        class _Eager:
+            @staticmethod
+            def replay():
+                step_body()
+        graph = _Eager()
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step_body()
     seq_lens.fill_(L)
     torch.cuda.synchronize(device)
     launches_per_step = layers * 5
@@ -390,7 +417,7 @@ def run_gpu(args):
         sampler.start()
     ms = timed(graph.replay, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    value = world * B * args.steps / (ms * 1e-3)
+    value = replicas * B * args.steps / (ms * 1e-3)
 
     # ---------------- end to end: host rows in, outputs back ----------------
     seq_lens.fill_(L)
@@ -417,7 +444,7 @@ def run_gpu(args):
     stream.synchronize()
     host_lens.fill_(L)
     ms_e2e = timed(e2e_step, args.steps)
-    e2e_value = world * B * args.steps / (ms_e2e * 1e-3)
+    e2e_value = replicas * B * args.steps / (ms_e2e * 1e-3)
 
     # ---------------- dominant kernel alone: attention of a residual loop, one launch per layer ----------------
     seq_lens.fill_(L)
@@ -525,7 +552,7 @@ def run_gpu(args):
         "warmup": args.warmup,
         "ms_per_step": ms / args.steps,
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong" if shard_heads else "weak",
         "vs_baseline": None,
         "dtype": "f16 dot products and value sums with fp32 softmax/accumulation (attention); f32 (quantizer)",
         "data": "synthetic",
