@@ -61,7 +61,8 @@ typedef enum RqRotationKind {
      * set when sign[h][c] is -1.  H_128 is the Sylvester matrix, H_96 = Paley-12 (x) Sylvester-8
      * (scripts/calibration/rotation_math.py:6-32). */
     RQ_ROTATION_SIGNED_HADAMARD = 1,
-    /* dense fp16 [heads][head_dim][head_dim], y = x @ R (common/api.h:42-55). */
+    /* dense fp16 [heads][head_dim][head_dim], y = x @ R (common/api.h:42-55): any learned rotation.  Rotated by a
+     * separate tensor-core launch (TF32 products, fp32 accumulation) into caller-provided scratch. */
     RQ_ROTATION_DENSE_FP16 = 2
 } RqRotationKind;
 
@@ -109,9 +110,16 @@ typedef struct RqQuantizeArgs {
     int32_t coefficient;     /* RqCoefficient */
     int32_t chain;           /* RqChain */
     void* stream;
+    void* workspace;         /* only for RQ_ROTATION_DENSE_FP16: rq_quantize_workspace_bytes() bytes, 16-byte aligned */
+    size_t workspace_bytes;
 } RqQuantizeArgs;
 
-/* Rotate, quantize and bit-pack the K/V rows of every record of a group into their pages.  One launch. */
+/* Scratch a quantize call needs: fp32 copies of the rotated rows of every plane whose rotation is dense
+ * (num_records * num_tokens * heads * head_dim * 4 bytes per such plane), 0 otherwise. */
+size_t rq_quantize_workspace_bytes(const RqGroupSpec* spec, int64_t num_tokens, int32_t key_rotation_kind,
+                                   int32_t value_rotation_kind);
+/* Rotate, quantize and bit-pack the K/V rows of every record of a group into their pages.  One launch
+ * (plus one rotation launch per plane with a dense rotation). */
 int32_t rq_quantize(const RqQuantizeArgs* args);
 
 typedef struct RqAttentionArgs {
@@ -150,7 +158,7 @@ typedef struct RqAttentionArgs {
 int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32_t max_blocks_per_request,
                                     int32_t page_tokens);
 /* Bytes of scratch one rq_attention call needs: per-partition (max, denominator, value sums), one arrival
- * counter per (row, head) and a status word.  The reference allocates the equivalent per call
+ * counter per (row, head), a status word and room for the densely rotated query rows.  The reference allocates the equivalent per call
  * (attention/launch.cuh:85-98). */
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits);
 /* Zero the counters and the status word (asynchronous, on `stream`).  Needed once per workspace; every call

@@ -4,10 +4,10 @@ names, argument meaning and error behaviour (RuntimeError on a rejected argument
 kernels behind the C ABI of include/rq_b200.h.
 
 Differences a caller can see:
-  * `key_rotation` / `value_rotation` may be the dense fp16 `[heads, D, D]` tensor of the reference API -- it must
-    then have been passed once to `residualquant_b200.rotation.register_rotation`, which recognises
-    diag(+-1) @ Hadamard matrices -- or a `SignedHadamardRotation` directly.  Arbitrary dense matrices are
-    rejected (no kernel yet) instead of being computed slowly.
+  * `key_rotation` / `value_rotation` are the dense fp16 `[heads, D, D]` tensors of the reference API or a
+    `SignedHadamardRotation`.  A tensor that was passed once to `residualquant_b200.rotation.register_rotation` and
+    recognised as diag(+-1) @ Hadamard runs the fused Walsh-Hadamard path; any other matrix is rotated by a
+    tensor-core launch (TF32 products like the reference) in front of the quantizer / attention kernel.
   * scratch memory for the split-KV merge comes from one cached buffer per (device, size) instead of five
     allocations per call (attention/launch.cuh:85-98); under CUDA-graph capture the buffer is whatever was
     cached before capture began, so warm up once before capturing, as the reference does
@@ -71,11 +71,14 @@ def _rotation_arg(rotation, device, heads: int, head_dim: int, keep: list) -> _l
             "Contiguous FP16 [heads, channels, channels] rotation required",
         )
         structured = lookup(rotation)
-        _require(
-            structured is not None,
-            "this rotation matrix is not registered as a signed Hadamard rotation "
-            "(residualquant_b200.rotation.register_rotation); dense rotations have no kernel yet",
-        )
+        if structured is None:
+            # an arbitrary learned rotation: rotated by a tensor-core launch from the dense matrix
+            _require(rotation.data_ptr() % 16 == 0, "16-byte aligned rotation required")
+            keep.append(rotation)
+            out.kind = _lib.ROTATION_DENSE_FP16
+            out.scale = 1.0
+            out.data = rotation.data_ptr()
+            return out
     _require(
         structured.heads == heads and structured.head_dim == head_dim and structured.sign_masks.device == device,
         "rotation does not match the head count, channel count or device",
@@ -169,6 +172,13 @@ def quantize(
     args.key_mean = key_mean.data_ptr() if key_mean is not None else None
     args.coefficient = _lib.COEFFICIENTS[coefficient_method]
     args.chain = _lib.CHAINS[_chain]
+    scratch_bytes = lib.rq_quantize_workspace_bytes(ctypes.byref(args.spec), slot_mapping.numel(), args.key_rotation.kind,
+                                                    args.value_rotation.kind)
+    if scratch_bytes:
+        scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=kv_cache.device)  # caching allocator: graph safe
+        keep.append(scratch)
+        args.workspace = scratch.data_ptr()
+        args.workspace_bytes = scratch_bytes
     with torch.cuda.device(kv_cache.device):
         args.stream = torch.cuda.current_stream(kv_cache.device).cuda_stream
         _lib.check(lib.rq_quantize(ctypes.byref(args)))

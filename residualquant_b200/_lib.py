@@ -19,6 +19,7 @@ EXPORTS = (
     "rq_page_width",
     "rq_record_offset",
     "rq_quantize",
+    "rq_quantize_workspace_bytes",
     "rq_attention_default_splits",
     "rq_attention_workspace_bytes",
     "rq_attention_workspace_init",
@@ -65,6 +66,8 @@ class RqQuantizeArgs(ctypes.Structure):
         ("coefficient", ctypes.c_int32),
         ("chain", ctypes.c_int32),
         ("stream", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
     ]
 
 
@@ -118,6 +121,8 @@ def load() -> ctypes.CDLL:
     lib.rq_page_width.restype = ctypes.c_int32
     lib.rq_record_offset.argtypes = [ctypes.POINTER(RqGroupSpec), ctypes.c_int32]
     lib.rq_record_offset.restype = ctypes.c_int32
+    lib.rq_quantize_workspace_bytes.argtypes = [ctypes.POINTER(RqGroupSpec), ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
+    lib.rq_quantize_workspace_bytes.restype = ctypes.c_size_t
     lib.rq_quantize.argtypes = [ctypes.POINTER(RqQuantizeArgs)]
     lib.rq_quantize.restype = ctypes.c_int32
     lib.rq_attention_default_splits.argtypes = [ctypes.c_int32] * 4

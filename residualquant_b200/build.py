@@ -25,6 +25,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relax
 UNITS = {
     "rq_quantize.cu": ["-fmad=false"],
     "rq_attention.cu": [],
+    "rq_rotate.cu": [],
     "rq_capi.cu": [],
 }
 HEADERS = ["rq_common.cuh", "rq_kernels.h", os.path.join("..", "..", "include", "rq_b200.h")]

@@ -220,7 +220,14 @@ __device__ __forceinline__ void prepare_query(const AttentionParams& p, int row,
         x[3] = bf16_bits_to_float(raw.y >> 16);
     }
     float scale = rsqrtf(static_cast<float>(D)) * kLog2e;
-    if (p.key_sign != nullptr) {
+    if (p.rotated_query != nullptr) {
+        // dense learned rotation: q @ R was computed by rotate_rows_kernel
+        if (owner) {
+            const float4 v = *reinterpret_cast<const float4*>(
+                p.rotated_query + (static_cast<int64_t>(row) * p.heads + head) * D + 4 * lane);
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        }
+    } else if (p.key_sign != nullptr) {
         if (owner) {
             const uint32_t sign = p.key_sign[head * (D / 32) + (lane >> 3)] >> (4 * (lane & 7));
 #pragma unroll
@@ -792,7 +799,28 @@ __global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_con
     const float f_live = fast_exp2(live - total_m);
     const float denom = part_l * f_hist + f_live;
     float hist = tid < D ? value * f_hist / denom : 0.f;
-    if (p.value_sign != nullptr) {
+    if (p.value_matrix != nullptr) {
+        // dense explicit value rotation: history <- history @ R^T, one output channel per thread
+        float* buffer = warp_acc;  // free again
+        __syncthreads();
+        if (tid < D) buffer[tid] = hist;
+        __syncthreads();
+        if (tid < D) {
+            const uint4* matrix_row = reinterpret_cast<const uint4*>(p.value_matrix + (static_cast<int64_t>(head) * D + tid) * D);
+            float sum = 0.f;
+#pragma unroll 4
+            for (int k8 = 0; k8 < D / 8; ++k8) {
+                const uint4 packed = __ldg(matrix_row + k8);
+                const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 pair = __half22float2(as_half2(words[i]));
+                    sum += buffer[8 * k8 + 2 * i] * pair.x + buffer[8 * k8 + 2 * i + 1] * pair.y;
+                }
+            }
+            hist = sum;
+        }
+    } else if (p.value_sign != nullptr) {
         float* buffer = warp_acc;  // free again
         __syncthreads();
         if (tid < D) buffer[tid] = hist;

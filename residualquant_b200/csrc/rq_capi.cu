@@ -63,9 +63,11 @@ int check_rotation(const RqRotation& r, const char* name) {
         if (!(r.scale > 0.f)) return fail(RQ_ERR_INVALID_ARGUMENT, "%s: scale must be positive", name);
         return RQ_OK;
     }
-    if (r.kind == RQ_ROTATION_DENSE_FP16)
-        return fail(RQ_ERR_UNSUPPORTED, "%s: dense fp16 rotations have no kernel yet; register the matrix as a signed "
-                                        "Hadamard rotation", name);
+    if (r.kind == RQ_ROTATION_DENSE_FP16) {
+        if (r.data == nullptr || !aligned(r.data, 16))
+            return fail(RQ_ERR_INVALID_ARGUMENT, "%s: contiguous 16-byte aligned FP16 [heads, channels, channels] rotation required", name);
+        return RQ_OK;
+    }
     return fail(RQ_ERR_INVALID_ARGUMENT, "%s: unknown rotation kind %d", name, r.kind);
 }
 
@@ -88,6 +90,12 @@ int32_t rq_record_offset(const RqGroupSpec* spec, int32_t index) {
     int offset = 0;
     for (int r = 0; r < index; ++r) offset += record_bytes(spec, r);
     return offset;
+}
+
+size_t rq_quantize_workspace_bytes(const RqGroupSpec* spec, int64_t num_tokens, int32_t key_kind, int32_t value_kind) {
+    if (spec == nullptr || num_tokens <= 0 || spec->num_records < 1 || spec->heads < 1 || spec->head_dim < 1) return 0;
+    const size_t plane = static_cast<size_t>(spec->num_records) * num_tokens * spec->heads * spec->head_dim * sizeof(float);
+    return (key_kind == RQ_ROTATION_DENSE_FP16 ? plane : 0) + (value_kind == RQ_ROTATION_DENSE_FP16 ? plane : 0);
 }
 
 int32_t rq_quantize(const RqQuantizeArgs* a) {
@@ -157,6 +165,37 @@ int32_t rq_quantize(const RqQuantizeArgs* a) {
     p.coefficient = a->coefficient;
     p.chain = a->chain;
     p.vector_loads = vector_loads ? 1 : 0;
+    // Dense learned rotations: one tensor-core launch per plane writes the rotated rows to the caller's scratch.
+    const size_t need = rq_quantize_workspace_bytes(&s, a->num_tokens, a->key_rotation.kind, a->value_rotation.kind);
+    if (need > 0) {
+        if (a->chain == RQ_CHAIN_CALIBRATION)
+            return fail(RQ_ERR_UNSUPPORTED, "the calibration chain needs an invertible structured rotation");
+        if (a->workspace == nullptr || !aligned(a->workspace, 16) || a->workspace_bytes < need)
+            return fail(RQ_ERR_WORKSPACE, "dense rotations need %zu bytes of 16-byte aligned workspace, got %zu", need,
+                        a->workspace_bytes);
+        float* cursor = static_cast<float*>(a->workspace);
+        for (int plane = 0; plane < 2; ++plane) {
+            const RqRotation& rot = plane == 0 ? a->key_rotation : a->value_rotation;
+            if (rot.kind != RQ_ROTATION_DENSE_FP16) continue;
+            rq::RotateParams rp;
+            memset(&rp, 0, sizeof(rp));
+            for (int r = 0; r < s.num_records; ++r) {
+                rp.source[r] = plane == 0 ? p.key[r] : p.value[r];
+                rp.source_stride[r] = plane == 0 ? p.key_stride[r] : p.value_stride[r];
+            }
+            rp.num_sources = s.num_records;
+            rp.matrix = static_cast<const __half*>(rot.data);
+            rp.output = cursor;
+            rp.slots = a->slot_mapping;
+            rp.num_rows = p.num_tokens;
+            rp.heads = s.heads;
+            rp.scale = 1.f;
+            const cudaError_t rerr = rq::launch_rotate(rp, s.head_dim, static_cast<cudaStream_t>(a->stream));
+            if (rerr != cudaSuccess) return fail_cuda(rerr, "rotation launch");
+            p.rotated_rows[plane] = cursor;
+            cursor += static_cast<size_t>(s.num_records) * p.num_tokens * s.heads * s.head_dim;
+        }
+    }
     const cudaError_t err = rq::launch_quantize(p, s.head_dim, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "quantize launch");
     return RQ_OK;
@@ -193,7 +232,8 @@ size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32
     const size_t counters = round_up(static_cast<size_t>(num_query_rows) * heads * sizeof(int32_t), 256);
     const size_t partials =
         num_splits > 1 ? static_cast<size_t>(num_query_rows) * heads * num_splits * (head_dim + 2) * sizeof(float) : 0;
-    return kStatusBytes + counters + round_up(partials, 256);
+    const size_t rotated_query = round_up(static_cast<size_t>(num_query_rows) * heads * head_dim * sizeof(float), 256);
+    return kStatusBytes + counters + round_up(partials, 256) + rotated_query;
 }
 
 int32_t rq_attention_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -312,6 +352,27 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     p.counters = reinterpret_cast<int32_t*>(base + kStatusBytes);
     p.partials = reinterpret_cast<float*>(
         base + kStatusBytes + round_up(static_cast<size_t>(a->num_query_rows) * s.heads * sizeof(int32_t), 256));
+    if (a->key_rotation.kind == RQ_ROTATION_DENSE_FP16) {
+        // q @ R on the tensor cores, once per call, into the tail of the workspace
+        const size_t partial_bytes =
+            splits > 1 ? static_cast<size_t>(a->num_query_rows) * s.heads * splits * (s.head_dim + 2) * sizeof(float) : 0;
+        float* rotated = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.partials) + round_up(partial_bytes, 256));
+        rq::RotateParams rp;
+        memset(&rp, 0, sizeof(rp));
+        rp.source[0] = p.query;
+        rp.source_stride[0] = p.query_stride;
+        rp.num_sources = 1;
+        rp.matrix = static_cast<const __half*>(a->key_rotation.data);
+        rp.output = rotated;
+        rp.slots = nullptr;
+        rp.num_rows = a->num_query_rows;
+        rp.heads = s.heads;
+        rp.scale = 1.f;
+        const cudaError_t rerr = rq::launch_rotate(rp, s.head_dim, static_cast<cudaStream_t>(a->stream));
+        if (rerr != cudaSuccess) return fail_cuda(rerr, "query rotation launch");
+        p.rotated_query = rotated;
+    }
+    if (a->value_rotation.kind == RQ_ROTATION_DENSE_FP16) p.value_matrix = static_cast<const __half*>(a->value_rotation.data);
     const cudaError_t err = rq::launch_attention(v, p, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "attention launch");
     return RQ_OK;

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -27,7 +28,23 @@ struct QuantizeParams {
     int num_records, anchor, mode, coefficient, chain;
     int bits[RQ_MAX_RECORDS], group[RQ_MAX_RECORDS], record_offset[RQ_MAX_RECORDS];
     int vector_loads;         // rows are 16-byte aligned
+    // Dense learned rotation: rows already rotated by rotate_rows_kernel, fp32 [records][tokens][heads][head_dim]
+    // per plane (nullptr = read the bf16 inputs and rotate with the fused Walsh-Hadamard transform, or not at all).
+    const float* rotated_rows[2];
 };
+
+// y = x @ R for bf16 rows and a dense fp16 matrix per head (TF32 tensor-core products, fp32 accumulation).
+struct RotateParams {
+    const __nv_bfloat16* source[RQ_MAX_RECORDS];
+    int64_t source_stride[RQ_MAX_RECORDS];
+    int num_sources;
+    const __half* matrix;     // [heads][head_dim][head_dim]
+    float* output;            // [num_sources][num_rows][heads][head_dim]
+    const int64_t* slots;     // optional [num_rows]: rows with a negative slot are not read (output zeros)
+    int num_rows, heads;
+    float scale;
+};
+cudaError_t launch_rotate(const RotateParams& p, int head_dim, cudaStream_t stream);
 
 cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream);
 
@@ -50,6 +67,8 @@ struct AttentionParams {
     const uint32_t* key_sign;    // signed-Hadamard key rotation or nullptr
     const uint32_t* value_sign;  // explicit value rotation (undone on the history sum) or nullptr
     float key_rscale, value_rscale;
+    const float* rotated_query;  // dense key rotation: q @ R already computed, fp32 [rows][heads][head_dim]; else nullptr
+    const __half* value_matrix;  // dense explicit value rotation [heads][head_dim][head_dim]; else nullptr
     const float* mean;           // [records][heads][head_dim] or nullptr
     int heads, page_width;
     int anchor_offset;           // bytes per token before the anchor record

@@ -166,6 +166,7 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
     const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
     const int64_t* strides = plane == 0 ? p.key_stride : p.value_stride;
     const bool rotated = p.rotation[plane] == RQ_ROTATION_SIGNED_HADAMARD;
+    const float* pre_rotated = p.rotated_rows[plane];  // dense rotation already applied by rotate_rows_kernel
     const float rscale = p.rscale[plane];
     uint32_t sign16 = 0;
     if (rotated && j < kSlices)
@@ -187,6 +188,16 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = 0.f;
         if (!active) return;
+        if (pre_rotated != nullptr) {
+            const float4* src4 = reinterpret_cast<const float4*>(
+                pre_rotated + ((static_cast<int64_t>(r) * p.num_tokens + token) * p.heads + head) * D + 16 * j);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = __ldg(src4 + i);
+                x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+            }
+            return;
+        }
         const __nv_bfloat16* src = sources[r] + static_cast<int64_t>(token) * strides[r] + head * D + 16 * j;
         if (p.vector_loads) {
             const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src));

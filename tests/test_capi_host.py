@@ -58,9 +58,15 @@ def test_workspace_size_and_split_heuristic(built_library):
     lib = _lib.load()
     one = lib.rq_attention_workspace_bytes(64, 16, 128, 1)
     four = lib.rq_attention_workspace_bytes(64, 16, 128, 4)
-    assert one == 256 + 4096 and four == one + 64 * 16 * 4 * 130 * 4
+    rotated_query = 64 * 16 * 128 * 4
+    assert one == 256 + 4096 + rotated_query and four == one + 64 * 16 * 4 * 130 * 4
     assert four % 256 == 0
     assert lib.rq_attention_workspace_bytes(64, 16, 128, 0) == 0
     assert 1 <= lib.rq_attention_default_splits(1, 16, 512, 16) <= 64
     assert lib.rq_attention_default_splits(1, 16, 512, 16) >= lib.rq_attention_default_splits(64, 16, 512, 16)
     assert lib.rq_attention_default_splits(64, 16, 1, 16) == 1
+    spec = _lib.make_spec([[2, 32]] * 3 + [[4, 32]], "anchor", 3, 16, 128, 16)
+    plane = 4 * 100 * 16 * 128 * 4
+    assert lib.rq_quantize_workspace_bytes(ctypes.byref(spec), 100, 1, 1) == 0
+    assert lib.rq_quantize_workspace_bytes(ctypes.byref(spec), 100, 2, 0) == plane
+    assert lib.rq_quantize_workspace_bytes(ctypes.byref(spec), 100, 2, 2) == 2 * plane

@@ -139,9 +139,9 @@ def test_argument_errors_raise_runtime_error():
         _cuda.quantize(pairs, cache, slots, kr, vr, None, records, "sideways", 3, "ls")
     with pytest.raises(RuntimeError, match="BF16"):
         _cuda.quantize([(k.float(), v) for k, v in pairs], cache, slots, kr, vr, None, records, "anchor", 3, "ls")
-    dense = torch.eye(128, dtype=torch.float16, device="cuda").expand(2, 128, 128).contiguous()
-    with pytest.raises(RuntimeError, match="not registered"):
-        _cuda.quantize(pairs, cache, slots, dense, None, None, records, "anchor", 3, "ls")
+    with pytest.raises(RuntimeError, match="FP16"):
+        _cuda.quantize(pairs, cache, slots, torch.eye(128, device="cuda").expand(2, 128, 128).contiguous(), None, None,
+                       records, "anchor", 3, "ls")
 
 
 def test_dense_rotation_tensor_is_recognised_after_registration():
