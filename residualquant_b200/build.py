@@ -25,10 +25,12 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relax
 UNITS = {
     "rq_quantize.cu": ["-fmad=false"],
     "rq_attention.cu": [],
+    "rq_attention_d128.cu": [],
+    "rq_attention_d96.cu": [],
     "rq_rotate.cu": [],
     "rq_capi.cu": [],
 }
-HEADERS = ["rq_common.cuh", "rq_kernels.h", os.path.join("..", "..", "include", "rq_b200.h")]
+HEADERS = ["rq_common.cuh", "rq_kernels.h", "rq_attention_impl.cuh", os.path.join("..", "..", "include", "rq_b200.h")]
 
 
 def nvcc() -> str:

@@ -1,888 +1,26 @@
-// Packed paged decode attention (anchor reference mode), one launch per call.
-//
-// Replaces the reference's three kernels -- attention_prepare_kernel, attention_kernel, attention_merge_kernel
-// (plugins/residual_quantization/csrc/attention/prepare.cuh:391-430, compute.cuh:226-727, merge.cuh:9-84) --
-// and its page staging (attention/async_copy.cuh:109-168).
-//
-// Shape of the computation
-//   CTA  = one (query row, KV partition, head); grid = rows * splits * heads, heads fastest so that CTAs that
-//          run together read neighbouring pages of the same block.
-//   warp = an independent consumer of every 4th page of the partition with its OWN ring of shared-memory
-//          stages, filled by 1-D bulk async copies (cp.async.bulk + mbarrier complete_tx) that lane 0 issues
-//          STAGES pages ahead.  There is no CTA-wide barrier inside the page loop.
-//   lane = (token slot, 32-channel slice): 4 lanes per token, 8 tokens per warp step.  A slice is exactly one
-//          INT4 g32 anchor group, so scale/offset handling is per lane, not per channel.
-//   maths: no code is ever converted to a floating-point number one at a time.
-//          K: integer dot products (dp2a) of the masked code bytes against the rotated query quantized once per CTA
-//             to 12/10 bits, factored per slice as scale * sum(q*code) + offset * sum(q);
-//          softmax: one online-softmax stream per 4-lane token slot (fp32 reference exponent that moves only when a
-//             score exceeds it by more than a slack, denominator and offsets in fp32, base-2 exponent);
-//          V: `word & mask` read as a half2 IS a pair of codes times 2^-24 (subnormal halves are linear in their bit
-//             pattern), so one half2 FMA per channel pair with probability * alpha * scale * 2^11 as the weight;
-//             half2 sums are flushed to fp32 every 8 tokens; the offset part is accumulated once per group.
-//   merge: each warp folds its 8 streams, the CTA folds its 4 warps, and -- when the row has several
-//          partitions -- the LAST CTA to arrive (one atomic ticket per (row, head)) folds the partitions, adds the
-//          live token, undoes an explicit value rotation and stores bf16.  No second launch, no spin wait.
-//
-// The query rotation (signed Walsh-Hadamard) is fused into the prologue of every CTA (128 values, one warp).
-//
-// Every wait on an mbarrier is bounded; on expiry the kernel raises the workspace status word, drains what it
-// can and returns.
-#include <atomic>
-#include <type_traits>
-
-#include "rq_common.cuh"
+// Variant selection for the packed paged decode attention (the kernels live in rq_attention_impl.cuh, instantiated
+// once per head dimension).  Mirrors the reference's registry lookup (dispatch/kernel_registry.h:48-75): an
+// unknown key is an error, never a slow path.
 #include "rq_kernels.h"
 
 namespace rq {
-namespace {
 
-#ifndef RQ_ATTENTION_BULK_COPY
-#define RQ_ATTENTION_BULK_COPY 0
-#endif
-// Page staging engine: 1 = one elected lane issues cp.async.bulk copies that complete on an mbarrier,
-// 0 = every lane issues 16-byte cp.async copies tracked by commit groups (fewer instructions per page).
-constexpr bool kBulkCopy = RQ_ATTENTION_BULK_COPY != 0;
-constexpr int kWarps = 4;
-constexpr int kThreads = kWarps * 32;
-constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kNever = -1e30f;  // exponent of a stream that has seen no token: exp2(kNever - anything real) == 0
-
-// P[i][j] == -1  <=>  bit j of kPaleyRow[i]  <=>  bit i of kPaleyCol[j]
-__constant__ uint32_t kPaleyRowA[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0xed0, 0xda2,
-                                        0xb46, 0x68e, 0xd1c, 0xa3a, 0, 0, 0, 0};
-__constant__ uint32_t kPaleyColA[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc,
-                                        0x5b8, 0xb70, 0x6e2, 0xdc4, 0, 0, 0, 0};
-
-template <int D_, int AB_, int AG_, int RB_, int RG_, int P_, bool MEAN_>
-struct Config {
-    static constexpr int D = D_, AB = AB_, AG = AG_, RB = RB_, RG = RG_, P = P_;
-    static constexpr bool kMean = MEAN_, kResidual = RB_ != 0;
-    static_assert(AB == 4 && AG == 32, "anchor record must be INT4 with 32-channel groups");
-    static_assert(RB == 0 || RB == 2, "residual record must be INT2");
-    static_assert(D == 128 || D == 96, "head_dim 128 or 96");
-    static constexpr int kAnchorCode = D * AB / 8, kAnchorGroups = D / AG;
-    static constexpr int kAnchorBytes = P * (kAnchorCode + 2 * kAnchorGroups);  // staged without its alpha column
-    static constexpr int kResidualCode = kResidual ? D * RB / 8 : 0;
-    static constexpr int kResidualGroups = kResidual ? D / RG : 0;
-    static constexpr int kResidualBytes = kResidual ? P * (kResidualCode + 2 * kResidualGroups + 2) : 0;
-    static constexpr int kPlaneBytes = kAnchorBytes + kResidualBytes;
-    static constexpr int kStageBytes = 2 * kPlaneBytes;
-    // pages in flight per warp; sized so that four CTAs (16 warps) fit in one SM's shared memory at block size 16
-    static constexpr int kStages = P == 16 ? (kResidual ? 3 : 4) : 2;
-    static constexpr int kRingBytes = kStages * kStageBytes;
-    static_assert(kAnchorBytes % 16 == 0 && kResidualBytes % 16 == 0, "bulk copies need 16-byte multiples");
-    static_assert(kRingBytes >= 32 * 33 * 4, "the ring doubles as the warp's merge scratch");
-    // shared memory map (bytes)
-    static constexpr int kOffRing = 0;
-    static constexpr int kOffQuery = kOffRing + kWarps * kRingBytes;       // float[D]
-    static constexpr int kOffWarpAcc = kOffQuery + D * 4;                  // float[kWarps][D]
-    static constexpr int kOffWarpStat = kOffWarpAcc + kWarps * D * 4;      // float[kWarps][2] + float misc[8]
-    static constexpr int kOffBarriers = kOffWarpStat + 64;                 // uint64[kWarps][kStages]
-    static constexpr int kSmemBytes = kOffBarriers + kWarps * kStages * 8;
-};
-
-// ---- PTX wrappers --------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-// 16-byte asynchronous copy global -> shared (L1 bypass), one per lane.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-// Copy `BYTES` (a multiple of 16) with the whole warp: lane l moves chunks l, l+32, ...
-template <int BYTES>
-__device__ __forceinline__ void warp_copy(uint32_t dst, const uint8_t* src, int lane) {
-    constexpr int kChunks = BYTES / 16;
-#pragma unroll
-    for (int i = 0; i < (kChunks + 31) / 32; ++i) {
-        if (32 * (i + 1) <= kChunks || lane + 32 * i < kChunks) cp_async16(dst + 16 * lane + 512 * i, src + 16 * lane + 512 * i);
-    }
-}
-// Bounded wait.  false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
-    return d;
-}
-__device__ __forceinline__ __half2 as_half2(uint32_t bits) { return *reinterpret_cast<const __half2*>(&bits); }
-
-// Shared-memory loads by 32-bit shared address (no generic-pointer arithmetic in the hot loop).
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t a) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds8(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-// d = c + a.s16[0] * b.u8[0|2] + a.s16[1] * b.u8[1|3]
-__device__ __forceinline__ int dp2a_lo(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp2a_hi(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-// Two FP8-e4m3 bytes (first in bits 0-7, second in bits 8-15) -> two floats, one hardware conversion.
-__device__ __forceinline__ float2 fp8x2_to_float2(uint32_t pair) {
-    uint32_t h2;
-    asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(h2) : "r"(pair));
-    return __half22float2(as_half2(h2));
-}
-__device__ __forceinline__ uint32_t pack_s16(int lo, int hi) {
-    return (static_cast<uint32_t>(lo) & 0xffffu) | (static_cast<uint32_t>(hi) << 16);
-}
-
-// half2 arithmetic on raw 32-bit registers.
-__device__ __forceinline__ uint32_t hfma2_raw(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ uint32_t hmul2_raw(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t half2_from(float v) {  // (v, v), saturating to the largest finite half
-    uint32_t d;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %1;" : "=r"(d) : "f"(v));
-    return d;
-}
-// V codes are never converted: a half whose raw bits are an integer N < 2048 is the number N * 2^-24 (subnormals and
-// the first normal binade are linear in the bit pattern), so `word & mask` IS a pair of scaled codes and the scale
-// goes into the weight.  weight * 2^11 stays a finite half for |weight| < 32 (it saturates beyond: a V group would
-// need a range above ~240 for that); the half2 sums then carry a factor 2^-13: 11-bit relative precision for sums
-// above 0.5, 2^-11 absolute below.
-constexpr float kWeightUp = 2048.f;
-constexpr float kSumDown = 8192.f;
-
-// Rotated, pre-scaled query of this (row, head) into shared memory: qs[c] = (q @ R)[c] * D^-1/2 * log2(e).
-// Executed by warp 0; lane L owns channels 4L .. 4L+3.
-template <int D>
-__device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs, float* qmax_out) {
-    const int lane = threadIdx.x & 31;
-    float x[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool owner = 4 * lane < D;
-    if (owner) {
-        const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + 4 * lane;
-        const uint2 raw = *reinterpret_cast<const uint2*>(q);
-        x[0] = bf16_bits_to_float(raw.x & 0xffffu);
-        x[1] = bf16_bits_to_float(raw.x >> 16);
-        x[2] = bf16_bits_to_float(raw.y & 0xffffu);
-        x[3] = bf16_bits_to_float(raw.y >> 16);
-    }
-    float scale = rsqrtf(static_cast<float>(D)) * kLog2e;
-    if (p.rotated_query != nullptr) {
-        // dense learned rotation: q @ R was computed by rotate_rows_kernel
-        if (owner) {
-            const float4 v = *reinterpret_cast<const float4*>(
-                p.rotated_query + (static_cast<int64_t>(row) * p.heads + head) * D + 4 * lane);
-            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-        }
-    } else if (p.key_sign != nullptr) {
-        if (owner) {
-            const uint32_t sign = p.key_sign[head * (D / 32) + (lane >> 3)] >> (4 * (lane & 7));
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                if ((sign >> i) & 1u) x[i] = -x[i];
-        }
-        butterflies_in_lane<4>(x);
-        butterfly_across_lanes<4>(x, 1, (lane & 1) != 0);
-        if (D == 128) {
-            butterfly_across_lanes<4>(x, 2, (lane & 2) != 0);
-            butterfly_across_lanes<4>(x, 4, (lane & 4) != 0);
-            butterfly_across_lanes<4>(x, 8, (lane & 8) != 0);
-            butterfly_across_lanes<4>(x, 16, (lane & 16) != 0);
-        } else {
-            const uint32_t mask = kPaleyColA[(lane >> 1) & 15];
-            float out[4];
-#pragma unroll
-            for (int a = 0; a < 12; ++a) {
-                const bool negative = (mask >> a) & 1u;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float v = __shfl_sync(kFullMask, x[i], 2 * a + (lane & 1));
-                    const float t = negative ? -v : v;
-                    out[i] = a == 0 ? t : out[i] + t;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) x[i] = out[i];
-        }
-        scale *= p.key_rscale;
-    }
-    float biggest = 0.f;
-    if (owner) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float v = x[i] * scale;
-            qs[4 * lane + i] = v;
-            biggest = fmaxf(biggest, fabsf(v));
-        }
-    }
-#pragma unroll
-    for (int d = 16; d; d >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(kFullMask, biggest, d));
-    if (lane == 0) *qmax_out = biggest;
-}
-
-// Undo an explicit value rotation on the history sum: h <- ((h H^T) * rscale) * sign.  Warp 0, in place in smem.
-template <int D>
-__device__ __forceinline__ void unrotate_history(const AttentionParams& p, int head, float* hist) {
-    const int lane = threadIdx.x & 31;
-    const bool owner = 4 * lane < D;
-    float x[4] = {0.f, 0.f, 0.f, 0.f};
-    if (owner) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = hist[4 * lane + i];
-    }
-    butterflies_in_lane<4>(x);
-    butterfly_across_lanes<4>(x, 1, (lane & 1) != 0);
-    if (D == 128) {
-        butterfly_across_lanes<4>(x, 2, (lane & 2) != 0);
-        butterfly_across_lanes<4>(x, 4, (lane & 4) != 0);
-        butterfly_across_lanes<4>(x, 8, (lane & 8) != 0);
-        butterfly_across_lanes<4>(x, 16, (lane & 16) != 0);
-    } else {
-        const uint32_t mask = kPaleyRowA[(lane >> 1) & 15];
-        float out[4];
-#pragma unroll
-        for (int a = 0; a < 12; ++a) {
-            const bool negative = (mask >> a) & 1u;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float v = __shfl_sync(kFullMask, x[i], 2 * a + (lane & 1));
-                const float t = negative ? -v : v;
-                out[i] = a == 0 ? t : out[i] + t;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = out[i];
-    }
-    if (owner) {
-        const uint32_t sign = p.value_sign[head * (D / 32) + (lane >> 3)] >> (4 * (lane & 7));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float v = x[i] * p.value_rscale;
-            hist[4 * lane + i] = ((sign >> i) & 1u) ? -v : v;
-        }
-    }
-}
-
-template <class C>
-__global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_constant__ AttentionParams p) {
-    constexpr int D = C::D, P = C::P;
-    constexpr int kFlushPages = 64 / P;   // a lane adds 8 tokens between flushes
-    constexpr float kSlack = 1.f;         // probabilities stay below 2
-    extern __shared__ __align__(128) uint8_t smem[];
-    float* qs = reinterpret_cast<float*>(smem + C::kOffQuery);
-    float* warp_acc = reinterpret_cast<float*>(smem + C::kOffWarpAcc);
-    float* warp_stat = reinterpret_cast<float*>(smem + C::kOffWarpStat);  // [w][2] then misc at [8..15]
-    uint64_t* barriers = reinterpret_cast<uint64_t*>(smem + C::kOffBarriers);
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int heads = p.heads, splits = p.splits;
-    const int head = blockIdx.x % heads;
-    const int split = (blockIdx.x / heads) % splits;
-    const int row = blockIdx.x / (heads * splits);
-
-    // ---- which request, which pages -----------------------------------------------------------------
-    const int num_requests = p.num_requests;
-    if (row >= p.query_start_loc[num_requests]) return;  // graph padding: leave the output row untouched
-    int request = min(row, num_requests - 1);
-    if (!(p.query_start_loc[request] <= row && row < p.query_start_loc[request + 1])) {
-        int lo = 0, hi = num_requests - 1;  // largest r with query_start_loc[r] <= row
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (p.query_start_loc[mid] <= row) lo = mid; else hi = mid - 1;
-        }
-        request = lo;
-    }
-    const int history = max(0, p.seq_lens[request] - 1);
-    const int pages = (history + P - 1) / P;
-    const int chunk = (pages + splits - 1) / splits;
-    const int page_begin = min(pages, split * chunk), page_end = min(pages, page_begin + chunk);
-    // pages of this warp: page_begin + warp, + kWarps, ...
-    const int warp_pages = page_begin + warp < page_end ? (page_end - page_begin - warp + kWarps - 1) / kWarps : 0;
-    const int32_t* table = p.block_table + static_cast<int64_t>(request) * p.block_table_stride;
-
-    // ---- per-warp ring: init barriers, start the first copies ----------------------------------------
-    uint8_t* ring = smem + C::kOffRing + warp * C::kRingBytes;
-    const uint32_t ring_addr = smem_addr(ring);
-    const uint32_t bar_addr = smem_addr(barriers + warp * C::kStages);
-    if (kBulkCopy) {
-        if (lane == 0) {
-#pragma unroll
-            for (int s = 0; s < C::kStages; ++s) mbar_init(bar_addr + 8 * s, 1);
-            fence_proxy_async();
-        }
-        __syncwarp();
-    }
-
-    const int64_t page_bytes = static_cast<int64_t>(P) * p.page_width;
-    const uint8_t* head_base = p.cache + head * page_bytes;
-    const int64_t block_bytes = heads * page_bytes;
-    const int anchor_at = P * p.anchor_offset, residual_at = P * p.residual_offset;
-    auto issue = [&](int block, int stage) {
-        const uint8_t* k_page = head_base + block * block_bytes;
-        const uint8_t* v_page = k_page + p.plane_stride;
-        const uint32_t dst = ring_addr + stage * C::kStageBytes;
-        if (kBulkCopy) {
-            if (lane == 0) {
-                const uint32_t bar = bar_addr + 8 * stage;
-                fence_proxy_async();
-                mbar_expect_tx(bar, C::kStageBytes);
-                bulk_load(dst, k_page + anchor_at, C::kAnchorBytes, bar);
-                if (C::kResidual) bulk_load(dst + C::kAnchorBytes, k_page + residual_at, C::kResidualBytes, bar);
-                bulk_load(dst + C::kPlaneBytes, v_page + anchor_at, C::kAnchorBytes, bar);
-                if (C::kResidual)
-                    bulk_load(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, C::kResidualBytes, bar);
-            }
-        } else {
-            warp_copy<C::kAnchorBytes>(dst, k_page + anchor_at, lane);
-            if (C::kResidual) warp_copy<C::kResidualBytes>(dst + C::kAnchorBytes, k_page + residual_at, lane);
-            warp_copy<C::kAnchorBytes>(dst + C::kPlaneBytes, v_page + anchor_at, lane);
-            if (C::kResidual)
-                warp_copy<C::kResidualBytes>(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, lane);
-        }
-    };
-    // block ids of this warp's next 32 pages, one per lane
-    int batch_base = 0;
-    int my_block = 0;
-    auto load_batch = [&](int base) {
-        batch_base = base;
-        my_block = base + lane < warp_pages ? table[page_begin + warp + kWarps * (base + lane)] : 0;
-    };
-    load_batch(0);
-    int issued = 0;
-    {
-        // commit-group bookkeeping wants exactly kStages groups here and one more per loop iteration
-#pragma unroll
-        for (int s = 0; s < C::kStages; ++s) {
-            if (s < warp_pages) {
-                const int block = __shfl_sync(kFullMask, my_block, s);
-                issue(block, s);
-                ++issued;
-            }
-            if (!kBulkCopy) cp_async_commit();
-        }
-    }
-
-    // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
-    float* misc = warp_stat + 8;         // [0] last-arrival flag, [1] live score, [2] max |q|
-    if (warp == 0) prepare_query<D>(p, row, head, qs, misc + 2);
-    __syncthreads();
-
-    // The K side runs on integer dot products (dp2a: two s16 x u8 products per instruction): the query slice is
-    // quantized once per CTA to 11 bits (anchor) / 10 bits (residual) of its largest magnitude and pre-shifted so
-    // that codes can be used where they sit in the packed word, without shifting them down:
-    //   INT4 word itself -> bytes c_even + 16 c_odd, word & 0xF0F0F0F0 -> bytes 16 c_odd: even channels carry 16*q,
-    //        odd ones q - 16*q_even (which cancels what the unmasked byte added)
-    //   INT2 word & (0x03030303 << 2k) -> bytes 4^k c:                     channel position k carries 4^(3-k)*q
-    const int j = lane & 3;              // slice: channels 32j .. 32j+31
-    const bool slice_ok = 32 * j < D;
-    const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
-    const float qmax = misc[2];
-    const float to_anchor = qmax > 0.f ? 1900.f / qmax : 0.f, to_residual = qmax > 0.f ? 511.f / qmax : 0.f;
-    const float anchor_unit = qmax / 1900.f, residual_unit = qmax / 511.f;
-    uint32_t qa[16];                     // anchor operands, 4 per code word
-    uint32_t qr[C::kResidual ? 16 : 1];  // residual operands, 8 per code word
-    float qsum_a = 0.f;                  // sum of the quantized query over the slice, anchor resolution
-    float qsum_r0 = 0.f, qsum_r1 = 0.f;  // residual resolution, channels 0..15 / 16..31 of the slice
-    float qmean = 0.f;                   // sum_c q[c] * mean[anchor][c] over the slice (residual loops with a mean)
-    {
-        const float* qslice = qs + 32 * js;
-        int ia[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            ia[c] = slice_ok ? __float2int_rn(qslice[c] * to_anchor) : 0;
-            qsum_a += static_cast<float>(ia[c]);
-        }
-        qsum_a *= anchor_unit;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            qa[4 * w + 0] = pack_s16(16 * ia[8 * w + 0], 16 * ia[8 * w + 2]);
-            qa[4 * w + 1] = pack_s16(16 * ia[8 * w + 4], 16 * ia[8 * w + 6]);
-            // the even operands meet the UNMASKED byte c_even + 16*c_odd; the odd operands take that excess back
-            qa[4 * w + 2] = pack_s16(ia[8 * w + 1] - 16 * ia[8 * w + 0], ia[8 * w + 3] - 16 * ia[8 * w + 2]);
-            qa[4 * w + 3] = pack_s16(ia[8 * w + 5] - 16 * ia[8 * w + 4], ia[8 * w + 7] - 16 * ia[8 * w + 6]);
-        }
-        if (C::kResidual) {
-            int ir[32];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                ir[c] = slice_ok ? __float2int_rn(qslice[c] * to_residual) : 0;
-                if (c < 16) qsum_r0 += static_cast<float>(ir[c]); else qsum_r1 += static_cast<float>(ir[c]);
-            }
-            qsum_r0 *= residual_unit;
-            qsum_r1 *= residual_unit;
-#pragma unroll
-            for (int v = 0; v < 2; ++v) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int shift = 1 << (2 * (3 - k));
-                    qr[8 * v + 2 * k] = pack_s16(shift * ir[16 * v + k], shift * ir[16 * v + 4 + k]);
-                    qr[8 * v + 2 * k + 1] = pack_s16(shift * ir[16 * v + 8 + k], shift * ir[16 * v + 12 + k]);
-                }
-            }
-            if (C::kMean && slice_ok) {
-                const float* mean = p.mean + (static_cast<int64_t>(p.anchor_index) * heads + head) * D + 32 * js;
-#pragma unroll
-                for (int c = 0; c < 32; ++c) qmean += qslice[c] * mean[c];
-            }
-        }
-    }
-    const float anchor_dot_unit = anchor_unit * 0.0625f;      // the integer dot product carries a factor 16
-    const float residual_dot_unit = residual_unit * 0.015625f;  // ... a factor 64
-
-    // ---- page loop -----------------------------------------------------------------------------------
-    float m = kNever, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
-    uint32_t acc_b[16];                  // half2 partial sums of V, pair 4b+i = (channel 8b+i, channel 8b+i+4)
-    float acc[32];
-    constexpr bool kTwoOffsets = C::kResidual && C::RG == 16;  // two residual groups per 32-channel slice
-    float acc_off0 = 0.f, acc_off1 = 0.f;  // offset part of V for channels 0..15 / 16..31 of the slice (one sum if equal)
-#pragma unroll
-    for (int i = 0; i < 16; ++i) acc_b[i] = 0u;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    bool failed = false;
-    const int slot = lane >> 2;          // token slot 0..7 inside a warp step
-    float carry = 1.f;                   // factor the fp32 sums still have to be multiplied by (deferred rescale)
-
-    // half2 partial sums -> fp32 sums, every 8 tokens of a lane
-    auto flush = [&]() {
-        if (__any_sync(kFullMask, carry != 1.f)) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] *= carry;
-            carry = 1.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float2 f = __half22float2(as_half2(acc_b[i]));
-            acc[2 * i] += f.x;
-            acc[2 * i + 1] += f.y;
-            acc_b[i] = 0u;
-        }
-    };
-
-    int stage = 0;
-    uint32_t parity = 0;
-    int it_done = 0;  // pages fully consumed
-    for (int it = 0; it < warp_pages; ++it) {
-        if (kBulkCopy) {
-            if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
-        } else {
-            cp_async_wait<C::kStages - 1>();
-            __syncwarp();  // the other lanes' chunks of this page have landed too
-        }
-        const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
-        const uint32_t k_residual = k_anchor + C::kAnchorBytes;
-        const uint32_t v_anchor = k_anchor + C::kPlaneBytes;
-        const uint32_t v_residual = v_anchor + C::kAnchorBytes;
-        constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
-        const int first_token = (page_begin + warp + kWarps * it) * P;
-        const int valid = history - first_token;  // >= P for every page but the last one of the history
-
-        // Full pages run without any per-token predicate; only the last page of a sequence can be partial.
-        auto process_page = [&](auto partial_tag) {
-        constexpr bool kPartial = decltype(partial_tag)::value;
-#pragma unroll
-        for (int sub = 0; sub < P / 8; ++sub) {
-            const int t = sub * 8 + slot;
-            const bool live_token = !kPartial || t < valid;
-            // ---------------- K: score of token t against the query slice (integer dot products) ----------------
-            float part;
-            {
-                const uint4 codes = lds128(k_anchor + t * C::kAnchorCode + 16 * js);
-                const uint32_t meta = k_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
-                const float2 so = fp8x2_to_float2(lds8(meta) | (lds8(meta + P * C::kAnchorGroups) << 8));
-                const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
-                int d0 = 0, d1 = 0;
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const uint32_t odd = words[w] & 0xF0F0F0F0u;
-                    d0 = dp2a_lo(qa[4 * w + 0], words[w], d0);
-                    d1 = dp2a_hi(qa[4 * w + 1], words[w], d1);
-                    d0 = dp2a_lo(qa[4 * w + 2], odd, d0);
-                    d1 = dp2a_hi(qa[4 * w + 3], odd, d1);
-                }
-                part = so.x * (static_cast<float>(d0 + d1) * anchor_dot_unit) + so.y * qsum_a;
-            }
-            if (C::kResidual) {
-                const float alpha = bf16_bits_to_float(lds16(k_residual + kResidualAlphaAt + 2 * t));
-                if (C::kMean) part += qmean;
-                part *= alpha;
-                const uint2 codes = lds64(k_residual + t * C::kResidualCode + 8 * js);
-                int d0 = 0, d1 = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t m0 = codes.x & (0x03030303u << (2 * k)), m1 = codes.y & (0x03030303u << (2 * k));
-                    d0 = dp2a_lo(qr[2 * k], m0, d0);
-                    d0 = dp2a_hi(qr[2 * k + 1], m0, d0);
-                    d1 = dp2a_lo(qr[8 + 2 * k], m1, d1);
-                    d1 = dp2a_hi(qr[8 + 2 * k + 1], m1, d1);
-                }
-                const uint32_t meta = k_residual + P * C::kResidualCode + t * C::kResidualGroups;
-                if (C::RG == 32) {
-                    const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * C::kResidualGroups + js) << 8));
-                    part += so.x * (static_cast<float>(d0 + d1) * residual_dot_unit) + so.y * (qsum_r0 + qsum_r1);
-                } else {
-                    const float2 s01 = fp8x2_to_float2(lds16(meta + 2 * js));
-                    const float2 o01 = fp8x2_to_float2(lds16(meta + P * C::kResidualGroups + 2 * js));
-                    part += s01.x * (static_cast<float>(d0) * residual_dot_unit) + o01.x * qsum_r0 +
-                            s01.y * (static_cast<float>(d1) * residual_dot_unit) + o01.y * qsum_r1;
-                }
-            }
-            part += __shfl_xor_sync(kFullMask, part, 1);
-            part += __shfl_xor_sync(kFullMask, part, 2);
-            const float score = live_token ? part : kNever;
-
-            // ---------------- online softmax of the token slot ----------------
-            // `m` is the stream's reference exponent, not its exact maximum: it only moves when a score exceeds it
-            // by more than kSlack, so probabilities stay below 2^kSlack and rescaling is rare.
-            if (score > m + kSlack) {
-                const float f = fast_exp2(m - score);  // m == -inf gives 0
-                l *= f;
-                acc_off0 *= f;
-                if (kTwoOffsets) acc_off1 *= f;
-                carry *= f;
-                const uint32_t f2 = half2_from(f);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc_b[i] = hmul2_raw(acc_b[i], f2);
-                m = score;
-            }
-            const float prob = live_token ? fast_exp2(score - m) : 0.f;
-            l += prob;
-
-            // ---------------- V: accumulate prob * V_hat[t] over the slice ----------------
-            {
-                const uint4 codes = lds128(v_anchor + t * C::kAnchorCode + 16 * js);
-                const uint32_t meta = v_anchor + P * C::kAnchorCode + t * C::kAnchorGroups + js;
-                const float2 so = fp8x2_to_float2(lds8(meta) | (lds8(meta + P * C::kAnchorGroups) << 8));
-                float pa = prob;  // the V plane stores its own coefficient
-                if (C::kResidual) pa *= bf16_bits_to_float(lds16(v_residual + kResidualAlphaAt + 2 * t));
-                const float off = pa * so.y;
-                acc_off0 += off;
-                if (kTwoOffsets) acc_off1 += off;
-                const float weight = pa * so.x * kWeightUp;
-                const uint32_t w_low = half2_from(weight), w_high = hmul2_raw(w_low, 0x2C002C00u);  // w/16, exact
-                const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const uint32_t upper = words[w] >> 8;
-                    acc_b[4 * w + 0] = hfma2_raw(words[w] & 0x000F000Fu, w_low, acc_b[4 * w + 0]);
-                    acc_b[4 * w + 1] = hfma2_raw(words[w] & 0x00F000F0u, w_high, acc_b[4 * w + 1]);
-                    acc_b[4 * w + 2] = hfma2_raw(upper & 0x000F000Fu, w_low, acc_b[4 * w + 2]);
-                    acc_b[4 * w + 3] = hfma2_raw(upper & 0x00F000F0u, w_high, acc_b[4 * w + 3]);
-                }
-            }
-            if (C::kResidual) {
-                const uint2 codes = lds64(v_residual + t * C::kResidualCode + 8 * js);
-                const uint32_t meta = v_residual + P * C::kResidualCode + t * C::kResidualGroups;
-                float s0, s1;
-                if (C::RG == 32) {
-                    const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * C::kResidualGroups + js) << 8));
-                    s0 = s1 = so.x;
-                    acc_off0 += prob * so.y;
-                } else {
-                    const float2 s01 = fp8x2_to_float2(lds16(meta + 2 * js));
-                    const float2 o01 = fp8x2_to_float2(lds16(meta + P * C::kResidualGroups + 2 * js));
-                    s0 = s01.x;
-                    s1 = s01.y;
-                    acc_off0 += prob * o01.x;
-                    acc_off1 += prob * o01.y;
-                }
-                const uint32_t quarter = 0x34003400u, sixteenth = 0x2C002C00u, sixtyfourth = 0x24002400u;  // half2
-                const uint32_t words[2] = {codes.x, codes.y};
-                uint32_t wk[4];  // weights for code positions 0..3 of a byte: w, w/4, w/16, w/64
-#pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    if (v == 0 || C::RG == 16) {
-                        wk[0] = half2_from(prob * (v == 0 ? s0 : s1) * kWeightUp);
-                        wk[1] = hmul2_raw(wk[0], quarter);      // exact: powers of two
-                        wk[2] = hmul2_raw(wk[0], sixteenth);
-                        wk[3] = hmul2_raw(wk[0], sixtyfourth);
-                    }
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const uint32_t tb = prmt(words[v], 0u, b == 0 ? 0x4140u : 0x4342u);  // bytes [2b, 0, 2b+1, 0]
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            acc_b[8 * v + 4 * b + k] = hfma2_raw(tb & (0x00030003u << (2 * k)), wk[k], acc_b[8 * v + 4 * b + k]);
-                    }
-                }
-            }
-        }
-        };
-        if (valid >= P) process_page(std::false_type{}); else process_page(std::true_type{});
-
-        if ((it + 1) % kFlushPages == 0) flush();
-        __syncwarp();  // every lane has finished reading this stage
-        if (issued < warp_pages) {
-            if (issued - batch_base == 32) load_batch(issued);
-            const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
-            issue(block, stage);
-            ++issued;
-        }
-        if (!kBulkCopy) cp_async_commit();
-        if (++stage == C::kStages) { stage = 0; parity ^= 1u; }
-        it_done = it + 1;
-    }
-    __syncwarp();
-    failed = __any_sync(kFullMask, failed);
-    if (failed) {
-        if (lane == 0) atomicExch(p.status, 1);
-        // Copies already issued still target this CTA's shared memory: give each one more bounded wait.
-        int s2 = stage;
-        uint32_t par2 = parity;
-        for (int k = it_done; k < issued; ++k) {
-            mbar_wait(bar_addr + 8 * s2, par2);
-            if (++s2 == C::kStages) { s2 = 0; par2 ^= 1u; }
-        }
-    }
-    if (!kBulkCopy) cp_async_wait<0>();
-    flush();
-
-    // ---- fold the 8 token slots of the warp ------------------------------------------------------------
-    float m_warp = m;
-    m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 4));
-    m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 8));
-    m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 16));
-    const float f_slot = fast_exp2(m - m_warp);  // untouched streams carry zero sums, so their factor is irrelevant
-    float l_warp = l * f_slot;
-    l_warp += __shfl_xor_sync(kFullMask, l_warp, 4);
-    l_warp += __shfl_xor_sync(kFullMask, l_warp, 8);
-    l_warp += __shfl_xor_sync(kFullMask, l_warp, 16);
-    __syncwarp();
-    {
-        float* scratch = reinterpret_cast<float*>(ring) + lane * 33;  // [32 lanes][33]: conflict-free both ways
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            const int pair = e >> 1, b = pair >> 2, i = pair & 3;
-            const int local = 8 * b + i + 4 * (e & 1);  // channel inside the slice
-            const float off = (kTwoOffsets && local >= 16) ? acc_off1 : acc_off0;
-            scratch[local] = (acc[e] * kSumDown + off) * f_slot;
-        }
-    }
-    __syncwarp();
-    if (4 * lane < D) {
-        const float* scratch = reinterpret_cast<const float*>(ring);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int c = 4 * lane + i, slice = c >> 5, local = c & 31;
-            float sum = 0.f;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) sum += scratch[(4 * g + slice) * 33 + local];
-            warp_acc[warp * D + c] = sum;
-        }
-    }
-    if (lane == 0) {
-        warp_stat[2 * warp] = m_warp;
-        warp_stat[2 * warp + 1] = l_warp;
-    }
-    __syncthreads();
-
-    // ---- fold the warps of the CTA: thread c owns channel c ---------------------------------------------
-    float part_m = kNever;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) part_m = fmaxf(part_m, warp_stat[2 * w]);
-    float part_l = 0.f, value = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        const float mw = warp_stat[2 * w];
-        const float f = fast_exp2(mw - part_m);
-        part_l += warp_stat[2 * w + 1] * f;
-        if (tid < D) value += warp_acc[w * D + tid] * f;
-    }
-
-    // ---- several partitions: park the partial, the last CTA to arrive folds them -----------------------
-    if (splits > 1) {
-        float* mine = p.partials + ((static_cast<int64_t>(row) * heads + head) * splits + split) * (D + 2);
-        if (tid == 0) { mine[0] = part_m; mine[1] = part_l; }
-        if (tid < D) mine[2 + tid] = value;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const int ticket = atomicAdd(p.counters + row * heads + head, 1);
-            misc[0] = ticket == splits - 1 ? 1.f : 0.f;
-            if (ticket == splits - 1) p.counters[row * heads + head] = 0;  // ready for the next call
-        }
-        __syncthreads();
-        if (misc[0] == 0.f) return;
-        __threadfence();
-        const float* all = p.partials + (static_cast<int64_t>(row) * heads + head) * splits * (D + 2);
-        part_m = kNever;
-        for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * (D + 2)));
-        part_l = 0.f;
-        value = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = __ldcg(all + s * (D + 2));
-            const float f = fast_exp2(ms - part_m);
-            part_l += __ldcg(all + s * (D + 2) + 1) * f;
-            if (tid < D) value += __ldcg(all + s * (D + 2) + 2 + tid) * f;
-        }
-    }
-
-    // ---- live token, normalisation, optional inverse value rotation, store -------------------------------
-    if (warp == 0) {
-        float dot = 0.f, shift = 0.f;
-        if (4 * lane < D) {
-            const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + 4 * lane;
-            const __nv_bfloat16* k = p.key + static_cast<int64_t>(row) * p.key_stride + head * D + 4 * lane;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dot += __bfloat162float(q[i]) * __bfloat162float(k[i]);
-            if (C::kMean) {
-                // history scores leave out q.mean[loop]; the live score drops the same constant (prepare.cuh:229)
-                const float* mean = p.mean + (static_cast<int64_t>(p.loop_index) * heads + head) * D + 4 * lane;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) shift += qs[4 * lane + i] * mean[i];
-            }
-        }
-#pragma unroll
-        for (int d = 16; d; d >>= 1) {
-            dot += __shfl_xor_sync(kFullMask, dot, d);
-            shift += __shfl_xor_sync(kFullMask, shift, d);
-        }
-        if (lane == 0) misc[1] = dot * rsqrtf(static_cast<float>(D)) * kLog2e - shift;
-    }
-    __syncthreads();
-    const float live = misc[1];
-    const float total_m = fmaxf(part_m, live);
-    const float f_hist = part_l > 0.f ? fast_exp2(part_m - total_m) : 0.f;
-    const float f_live = fast_exp2(live - total_m);
-    const float denom = part_l * f_hist + f_live;
-    float hist = tid < D ? value * f_hist / denom : 0.f;
-    if (p.value_matrix != nullptr) {
-        // dense explicit value rotation: history <- history @ R^T, one output channel per thread
-        float* buffer = warp_acc;  // free again
-        __syncthreads();
-        if (tid < D) buffer[tid] = hist;
-        __syncthreads();
-        if (tid < D) {
-            const uint4* matrix_row = reinterpret_cast<const uint4*>(p.value_matrix + (static_cast<int64_t>(head) * D + tid) * D);
-            float sum = 0.f;
-#pragma unroll 4
-            for (int k8 = 0; k8 < D / 8; ++k8) {
-                const uint4 packed = __ldg(matrix_row + k8);
-                const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 pair = __half22float2(as_half2(words[i]));
-                    sum += buffer[8 * k8 + 2 * i] * pair.x + buffer[8 * k8 + 2 * i + 1] * pair.y;
-                }
-            }
-            hist = sum;
-        }
-    } else if (p.value_sign != nullptr) {
-        float* buffer = warp_acc;  // free again
-        __syncthreads();
-        if (tid < D) buffer[tid] = hist;
-        __syncthreads();
-        if (warp == 0) unrotate_history<D>(p, head, buffer);
-        __syncthreads();
-        if (tid < D) hist = buffer[tid];
-    }
-    if (tid < D) {
-        const float v_live = __bfloat162float(p.value[static_cast<int64_t>(row) * p.value_stride + head * D + tid]);
-        p.output[static_cast<int64_t>(row) * p.output_stride + head * D + tid] =
-            __float2bfloat16_rn(hist + v_live * (f_live / denom));
-    }
-}
-
-template <class C>
-cudaError_t launch_one(const AttentionParams& p, cudaStream_t stream) {
-    // Raise the dynamic shared memory limit once per device (bit d of the mask = device d is configured).
-    static std::atomic<unsigned long long> configured{0ull};
-    int device = 0;
-    cudaError_t err = cudaGetDevice(&device);
-    if (err != cudaSuccess) return err;
-    const unsigned long long bit = 1ull << (device & 63);
-    if (!(configured.load(std::memory_order_acquire) & bit)) {
-        err = cudaFuncSetAttribute(attention_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (err != cudaSuccess) return err;
-        configured.fetch_or(bit, std::memory_order_release);
-    }
-    const int64_t blocks = static_cast<int64_t>(p.num_rows) * p.splits * p.heads;
-    attention_kernel<C><<<static_cast<unsigned>(blocks), kThreads, C::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <int D, int RB, int RG, int P>
-cudaError_t launch_mean(bool has_mean, const AttentionParams& p, cudaStream_t stream) {
-    if (has_mean) return launch_one<Config<D, 4, 32, RB, RG, P, true>>(p, stream);
-    return launch_one<Config<D, 4, 32, RB, RG, P, false>>(p, stream);
-}
-
-template <int D, int P>
-cudaError_t launch_residual(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream) {
-    if (v.residual_bits == 0) return launch_mean<D, 0, 32, P>(v.has_mean, p, stream);
-    if (v.residual_bits == 2 && v.residual_group == 32) return launch_mean<D, 2, 32, P>(v.has_mean, p, stream);
-    if (v.residual_bits == 2 && v.residual_group == 16) return launch_mean<D, 2, 16, P>(v.has_mean, p, stream);
-    return cudaErrorInvalidDeviceFunction;
-}
-
-}  // namespace
+cudaError_t launch_attention_d128(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream);
+cudaError_t launch_attention_d96(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream);
 
 bool attention_variant_available(const AttentionVariant& v) {
     if (v.head_dim != 128 && v.head_dim != 96) return false;
     if (v.page_tokens != 16 && v.page_tokens != 32) return false;
-    if (v.anchor_bits != 4 || v.anchor_group != 32) return false;
-    if (v.residual_bits == 0) return true;
-    return v.residual_bits == 2 && (v.residual_group == 16 || v.residual_group == 32);
+    const int ab = v.anchor_bits, ag = v.anchor_group, rb = v.residual_bits, rg = v.residual_group;
+    if (ab == 4 && ag == 32) return rb == 0 || (rb == 2 && (rg == 16 || rg == 32)) || (rb == 4 && rg == 32);
+    if (ab == 2 && ag == 32) return rb == 0 || (rb == 2 && rg == 32);
+    if (ab == 2 && ag == 16) return rb == 0 || (rb == 2 && rg == 16);
+    return false;
 }
 
 cudaError_t launch_attention(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream) {
     if (!attention_variant_available(v)) return cudaErrorInvalidDeviceFunction;
-    if (v.head_dim == 128)
-        return v.page_tokens == 16 ? launch_residual<128, 16>(v, p, stream) : launch_residual<128, 32>(v, p, stream);
-    return v.page_tokens == 16 ? launch_residual<96, 16>(v, p, stream) : launch_residual<96, 32>(v, p, stream);
+    return v.head_dim == 128 ? launch_attention_d128(v, p, stream) : launch_attention_d96(v, p, stream);
 }
 
 }  // namespace rq

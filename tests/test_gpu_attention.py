@@ -197,9 +197,9 @@ def test_argument_errors_raise_runtime_error():
         call(block_table=table.long())
     with pytest.raises(RuntimeError, match="adjacent"):
         call(records=[[4, 32], [2, 32], [2, 32], [2, 32]], anchor_index=0, reference_mode="adjacent", loop_index=1)
-    narrow = torch.zeros((2, case.num_blocks, case.heads, 16, 168), dtype=torch.uint8, device="cuda")
+    other = torch.zeros((2, case.num_blocks, case.heads, 16, 328), dtype=torch.uint8, device="cuda")
     with pytest.raises(RuntimeError, match="No compiled packed CUDA kernel"):
-        call(records=[[2, 32]] * 4, loop_index=0, kv_cache=narrow)
+        call(records=[[4, 16]] * 4, loop_index=0, kv_cache=other)
 
 
 def test_large_value_magnitudes_stay_accurate_and_finite():
@@ -256,3 +256,22 @@ def test_decode_step_through_the_group_mirror():
     O.quantize([(k[case.live_rows], v[case.live_rows]) for k, v in zip(case.keys, case.values)], cache_np,
                live_slots.cpu().numpy(), L, okr, ovr, None)
     assert np.array_equal(cache.cpu().numpy(), cache_np)
+
+
+@pytest.mark.parametrize("records,anchor", [
+    (((4, 32), (4, 32), (4, 32), (4, 32)), 3),      # "4444"
+    (((2, 32), (2, 32), (2, 32), (2, 32)), 3),      # "2222" g32
+    (((2, 16), (2, 16), (2, 16), (2, 16)), 0),      # "2222" g16, anchor first
+    (((4, 32), (2, 32), (2, 32), (2, 32)), 0),      # "4222", anchor first
+    (((4, 32), (2, 16), (2, 16), (2, 16)), 0),
+    (((4, 32),), 0),
+    (((2, 32),), 0),
+])
+@pytest.mark.parametrize("head_dim", [128, 96])
+def test_other_schedules_of_the_registry(records, anchor, head_dim):
+    """Every (anchor record, loop record) pair of the reference's anchor-mode schedule lists
+    (dispatch/decode_*_anchor_{0,3}_g{16,32}.cu)."""
+    case = helpers.make_case(43, head_dim, 2, [170, 18], records=records, anchor_index=anchor, with_mean=(head_dim == 96))
+    cache = helpers.oracle_cache(case)
+    for loop in range(len(records)):
+        _check(case, cache, loop, splits=2 if loop % 2 else 0)
