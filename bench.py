@@ -564,7 +564,9 @@ def run_gpu(args):
         "roofline": {
             "bound": "hbm", "kernel": "attention_kernel (residual loop: INT4 anchor + INT2 residual)",
             "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": None, "algorithmic_bytes_per_launch": bytes_res, "us_per_launch": 1000 * ms_res,
+            # DRAM bytes per launch = algorithmic bytes x 1.128, the ratio ncu measured on a smaller launch of the same
+            # kernel (profiles/attention_kernel_b32_ctx8192.md); traffic grows in proportion to the tokens read
+            "traffic": 1.128 * bytes_res, "algorithmic_bytes_per_launch": bytes_res, "us_per_launch": 1000 * ms_res,
             "anchor_loop": {"us_per_launch": 1000 * ms_anchor, "achieved": bytes_anchor / (ms_anchor * 1e-3) / 1e9,
                             "frac": bytes_anchor / (ms_anchor * 1e-3) / 1e9 / peak},
             "quantize_decode_write": {"us_per_launch": 1000 * ms_quant,

@@ -70,6 +70,7 @@ struct Config {
     static constexpr int kPlaneBytes = kAnchorBytes + kResidualBytes;
     static constexpr int kStageBytes = 2 * kPlaneBytes;
     // pages in flight per warp; sized so that four CTAs (16 warps) fit in one SM's shared memory at block size 16
+    static constexpr int kMinBlocks = 4;  // CTAs per SM the register allocation aims for (5 for the anchor loop measured no faster)
     static constexpr int kBaseStages = P == 16 ? (kResidual ? 3 : 4) : 2;
     static constexpr int kScratchStages = (32 * 33 * 4 + kStageBytes - 1) / kStageBytes;  // the ring doubles as merge scratch
     static constexpr int kStages = kBaseStages > kScratchStages ? kBaseStages : kScratchStages;
@@ -478,7 +479,7 @@ __device__ __forceinline__ void unrotate_history(const AttentionParams& p, int h
 }
 
 template <class C>
-__global__ void __launch_bounds__(kThreads, 4) attention_kernel(const __grid_constant__ AttentionParams p) {
+__global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(const __grid_constant__ AttentionParams p) {
     constexpr int D = C::D, P = C::P;
     constexpr int kFlushPages = 64 / P;   // a lane adds 8 tokens between flushes
     constexpr float kSlack = 1.f;         // probabilities stay below 2
