@@ -55,10 +55,13 @@ __constant__ uint32_t kPaleyRowA[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 
 __constant__ uint32_t kPaleyColA[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc,
                                         0x5b8, 0xb70, 0x6e2, 0xdc4, 0, 0, 0, 0};
 
-template <int D_, int AB_, int AG_, int RB_, int RG_, int P_, bool MEAN_>
+template <int D_, int AB_, int AG_, int RB_, int RG_, int P_, bool MEAN_, bool ADJ_ = false>
 struct Config {
     static constexpr int D = D_, AB = AB_, AG = AG_, RB = RB_, RG = RG_, P = P_;
     static constexpr bool kMean = MEAN_, kResidual = RB_ != 0;
+    // Adjacent mode stages the whole prefix of records 0..loop (run-time size, at most four INT4 g32 records).
+    static constexpr bool kAdjacent = ADJ_;
+    static constexpr int kMaxPrefixBytes = P * 4 * (D / 2 + 2 * (D / 32) + 2);
     static_assert(AB == 2 || AB == 4, "anchor record must be INT2 or INT4");
     static_assert(RB == 0 || RB == 2 || RB == 4, "residual record must be absent, INT2 or INT4");
     static_assert(D == 128 || D == 96, "head_dim 128 or 96");
@@ -68,10 +71,10 @@ struct Config {
     static constexpr int kResidualGroups = kResidual ? D / RG : 0;
     static constexpr int kResidualBytes = kResidual ? P * (kResidualCode + 2 * kResidualGroups + 2) : 0;
     static constexpr int kPlaneBytes = kAnchorBytes + kResidualBytes;
-    static constexpr int kStageBytes = 2 * kPlaneBytes;
+    static constexpr int kStageBytes = kAdjacent ? 2 * kMaxPrefixBytes : 2 * kPlaneBytes;
     // pages in flight per warp; sized so that four CTAs (16 warps) fit in one SM's shared memory at block size 16
     static constexpr int kMinBlocks = 4;  // CTAs per SM the register allocation aims for (5 for the anchor loop measured no faster)
-    static constexpr int kBaseStages = P == 16 ? (kResidual ? 3 : 4) : 2;
+    static constexpr int kBaseStages = kAdjacent ? 2 : (P == 16 ? (kResidual ? 3 : 4) : 2);
     static constexpr int kScratchStages = (32 * 33 * 4 + kStageBytes - 1) / kStageBytes;  // the ring doubles as merge scratch
     static constexpr int kStages = kBaseStages > kScratchStages ? kBaseStages : kScratchStages;
     static constexpr int kRingBytes = kStages * kStageBytes;
@@ -115,6 +118,10 @@ __device__ __forceinline__ void warp_copy(uint32_t dst, const uint8_t* src, int 
     for (int i = 0; i < (kChunks + 31) / 32; ++i) {
         if (32 * (i + 1) <= kChunks || lane + 32 * i < kChunks) cp_async16(dst + 16 * lane + 512 * i, src + 16 * lane + 512 * i);
     }
+}
+// Same with a run-time size.
+__device__ __forceinline__ void warp_copy_bytes(uint32_t dst, const uint8_t* src, int bytes, int lane) {
+    for (int at = 16 * lane; at < bytes; at += 512) cp_async16(dst + at, src + at);
 }
 // Bounded wait.  false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -211,7 +218,8 @@ constexpr float kSumDown = 8192.f;
 // Query operands for the integer dot products of one code width, built once per CTA from the rotated query slice.
 //   INT4: the word itself carries bytes c_even + 16 c_odd, word & 0xF0F0F0F0 carries 16 c_odd: even channels get
 //         16*q, odd ones q - 16*q_even (which takes back what the unmasked byte added); 11-bit query.
-//   INT2: word & (0x03030303 << 2k) carries 4^k c: channel position k gets 4^(3-k)*q; 10-bit query.
+//   INT2: word & (0x03030303 << 2k) carries 4^k c: positions 0,1 get 4q, q and feed one sum, positions 2,3 get 4q, q
+//         and feed a second sum that carries an extra factor 16 (shifted out exactly); 13-bit query.
 template <int BITS>
 struct QueryOperands {
     uint32_t op[16];
@@ -221,7 +229,7 @@ struct QueryOperands {
 
 template <int BITS>
 __device__ __forceinline__ void build_operands(const float* qslice, bool slice_ok, float qmax, QueryOperands<BITS>& out) {
-    constexpr float kLevels = BITS == 4 ? 1900.f : 511.f;
+    constexpr float kLevels = BITS == 4 ? 1900.f : 8191.f;
     const float to_int = qmax > 0.f ? kLevels / qmax : 0.f, unit = qmax / kLevels;
     int iq[32];
     float s0 = 0.f, s1 = 0.f;
@@ -242,12 +250,12 @@ __device__ __forceinline__ void build_operands(const float* qslice, bool slice_o
             out.op[4 * w + 3] = pack_s16(iq[8 * w + 5] - 16 * iq[8 * w + 4], iq[8 * w + 7] - 16 * iq[8 * w + 6]);
         }
     } else {
-        out.dot_unit = unit * 0.015625f;  // ... a factor 64
+        out.dot_unit = unit * 0.25f;  // ... a factor 4
 #pragma unroll
         for (int v = 0; v < 2; ++v) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int shift = 1 << (2 * (3 - k));
+                const int shift = (k & 1) ? 1 : 4;
                 out.op[8 * v + 2 * k] = pack_s16(shift * iq[16 * v + k], shift * iq[16 * v + 4 + k]);
                 out.op[8 * v + 2 * k + 1] = pack_s16(shift * iq[16 * v + 8 + k], shift * iq[16 * v + 12 + k]);
             }
@@ -299,13 +307,22 @@ __device__ __forceinline__ float score_record(uint32_t base, int t, int js, cons
         }
     } else {
         const uint2 codes = lds64(base + t * R::kCode + 8 * js);
+        int h0 = 0, h1 = 0;  // sums of code positions 2 and 3: they carry an extra factor 16
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const uint32_t m0 = codes.x & (0x03030303u << (2 * k)), m1 = codes.y & (0x03030303u << (2 * k));
-            d0 = dp2a_lo(q.op[2 * k], m0, d0);
-            d0 = dp2a_hi(q.op[2 * k + 1], m0, d0);
-            d1 = dp2a_lo(q.op[8 + 2 * k], m1, d1);
-            d1 = dp2a_hi(q.op[8 + 2 * k + 1], m1, d1);
+            int& s0 = k < 2 ? d0 : h0;
+            int& s1 = k < 2 ? d1 : h1;
+            s0 = dp2a_lo(q.op[2 * k], m0, s0);
+            s0 = dp2a_hi(q.op[2 * k + 1], m0, s0);
+            s1 = dp2a_lo(q.op[8 + 2 * k], m1, s1);
+            s1 = dp2a_hi(q.op[8 + 2 * k + 1], m1, s1);
+        }
+        if (GROUP == 32) {
+            d0 += (h0 + h1) >> 4;  // exact: a multiple of 16
+        } else {
+            d0 += h0 >> 4;
+            d1 += h1 >> 4;
         }
     }
     float2 scales, offsets;
@@ -536,7 +553,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         const uint8_t* k_page = head_base + block * block_bytes;
         const uint8_t* v_page = k_page + p.plane_stride;
         const uint32_t dst = ring_addr + stage * C::kStageBytes;
-        if (kBulkCopy) {
+        if (C::kAdjacent) {
+            const int prefix = P * p.chain_offset[p.chain_count];
+            warp_copy_bytes(dst, k_page, prefix, lane);
+            warp_copy_bytes(dst + C::kMaxPrefixBytes, v_page, prefix, lane);
+        } else if (kBulkCopy) {
             if (lane == 0) {
                 const uint32_t bar = bar_addr + 8 * stage;
                 fence_proxy_async();
@@ -588,7 +609,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     const bool slice_ok = 32 * j < D;
     const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
     const float qmax = misc[2];
-    constexpr bool kUse4 = C::AB == 4 || C::RB == 4, kUse2 = C::AB == 2 || C::RB == 2;
+    constexpr bool kUse4 = C::kAdjacent || C::AB == 4 || C::RB == 4, kUse2 = C::kAdjacent || C::AB == 2 || C::RB == 2;
     QueryOperands<4> q4;
     QueryOperands<2> q2;
     if (kUse4) build_operands<4>(qs + 32 * js, slice_ok, qmax, q4);
@@ -596,8 +617,19 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     auto operands = [&](auto bits_tag) -> const auto& {
         if constexpr (decltype(bits_tag)::value == 4) return q4; else return q2;
     };
+    float chain_qmean[4] = {0.f, 0.f, 0.f, 0.f};  // adjacent mode: sum_c q[c] * mean[r][c] for the records before the loop's own
+    if (C::kAdjacent && C::kMean && slice_ok) {
+        const float* qslice = qs + 32 * js;
+        for (int r = 0; r + 1 < p.chain_count; ++r) {
+            const float* mean = p.mean + (static_cast<int64_t>(r) * heads + head) * D + 32 * js;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) sum += qslice[c] * mean[c];
+            chain_qmean[r] = sum;
+        }
+    }
     float qmean = 0.f;                   // sum_c q[c] * mean[anchor][c] over the slice (residual loops with a mean)
-    if (C::kMean && C::kResidual && slice_ok) {
+    if (!C::kAdjacent && C::kMean && C::kResidual && slice_ok) {
         const float* qslice = qs + 32 * js;
         const float* mean = p.mean + (static_cast<int64_t>(p.anchor_index) * heads + head) * D + 32 * js;
 #pragma unroll
@@ -608,7 +640,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     float m = kNever, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
     uint32_t acc_b[16];                  // half2 partial sums of V, pair 4b+i = (channel 8b+i, channel 8b+i+4)
     float acc[32];
-    constexpr bool kTwoOffsets = C::AG == 16 || (C::kResidual && C::RG == 16);  // a record with two groups per slice
+    constexpr bool kTwoOffsets = C::kAdjacent || C::AG == 16 || (C::kResidual && C::RG == 16);  // a record with two groups per slice
     float acc_off0 = 0.f, acc_off1 = 0.f;  // offset part of V for channels 0..15 / 16..31 of the slice (one sum if equal)
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc_b[i] = 0u;
@@ -646,7 +678,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         }
         const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
         const uint32_t k_residual = k_anchor + C::kAnchorBytes;
-        const uint32_t v_anchor = k_anchor + C::kPlaneBytes;
+        const uint32_t v_anchor = k_anchor + (C::kAdjacent ? C::kMaxPrefixBytes : C::kPlaneBytes);
         const uint32_t v_residual = v_anchor + C::kAnchorBytes;
         constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
         const int first_token = (page_begin + warp + kWarps * it) * P;
@@ -660,8 +692,26 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             const int t = sub * 8 + slot;
             const bool live_token = !kPartial || t < valid;
             // ---------------- K: score of token t against the query slice (integer dot products) ----------------
-            float part = score_record<C::AB, C::AG, P, D>(k_anchor, t, js, operands(std::integral_constant<int, C::AB>{}));
-            if constexpr (C::kResidual) {
+            float part = 0.f;
+            if constexpr (C::kAdjacent) {
+                // K_hat[loop] = alpha_loop * K_hat[loop-1] + R_loop (+ means of the earlier loops): Horner over the records
+                for (int r = 0; r < p.chain_count; ++r) {
+                    const uint32_t base = k_anchor + P * p.chain_offset[r];
+                    const int bits = p.chain_bits[r], group = p.chain_group[r];
+                    float one;
+                    if (bits == 4) one = score_record<4, 32, P, D>(base, t, js, q4);
+                    else if (group == 32) one = score_record<2, 32, P, D>(base, t, js, q2);
+                    else one = score_record<2, 16, P, D>(base, t, js, q2);
+                    if (r > 0) {
+                        const int alpha_at = P * (D * bits / 8 + 2 * (D / group));
+                        part *= bf16_bits_to_float(lds16(base + alpha_at + 2 * t));
+                    }
+                    part += one + chain_qmean[r];
+                }
+            } else {
+            part = score_record<C::AB, C::AG, P, D>(k_anchor, t, js, operands(std::integral_constant<int, C::AB>{}));
+            }
+            if constexpr (C::kResidual && !C::kAdjacent) {
                 const float alpha = bf16_bits_to_float(lds16(k_residual + kResidualAlphaAt + 2 * t));
                 if (C::kMean) part += qmean;
                 part = part * alpha +
@@ -689,11 +739,27 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             l += prob;
 
             // ---------------- V: accumulate prob * V_hat[t] over the slice ----------------
+            if constexpr (C::kAdjacent) {
+                // record r enters with weight prob * alpha_{r+1} * ... * alpha_loop (the V plane's own coefficients)
+                float weight = prob;
+                for (int r = p.chain_count - 1; r >= 0; --r) {
+                    const uint32_t base = v_anchor + P * p.chain_offset[r];
+                    const int bits = p.chain_bits[r], group = p.chain_group[r];
+                    if (bits == 4) accumulate_record<4, 32, P, D, true>(base, t, js, weight, acc_b, acc_off0, acc_off1);
+                    else if (group == 32) accumulate_record<2, 32, P, D, true>(base, t, js, weight, acc_b, acc_off0, acc_off1);
+                    else accumulate_record<2, 16, P, D, true>(base, t, js, weight, acc_b, acc_off0, acc_off1);
+                    if (r > 0) {
+                        const int alpha_at = P * (D * bits / 8 + 2 * (D / group));
+                        weight *= bf16_bits_to_float(lds16(base + alpha_at + 2 * t));
+                    }
+                }
+            } else {
             float pa = prob;  // the V plane stores its own coefficient
             if constexpr (C::kResidual) pa *= bf16_bits_to_float(lds16(v_residual + kResidualAlphaAt + 2 * t));
             accumulate_record<C::AB, C::AG, P, D, kTwoOffsets>(v_anchor, t, js, pa, acc_b, acc_off0, acc_off1);
             if constexpr (C::kResidual)
                 accumulate_record<C::RB, C::RG, P, D, kTwoOffsets>(v_residual, t, js, prob, acc_b, acc_off0, acc_off1);
+            }
         }
         };
         if (valid >= P) process_page(std::false_type{}); else process_page(std::true_type{});
@@ -899,6 +965,10 @@ cudaError_t launch_mean(bool has_mean, const AttentionParams& p, cudaStream_t st
 // (plugins/residual_quantization/csrc/dispatch/decode_*_anchor_*.cu): 2224 / 4222 / 4444 / 2222 and single-record groups.
 template <int D, int P>
 cudaError_t launch_records(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream) {
+    if (v.adjacent) {
+        if (v.has_mean) return launch_one<Config<D, 4, 32, 0, 32, P, true, true>>(p, stream);
+        return launch_one<Config<D, 4, 32, 0, 32, P, false, true>>(p, stream);
+    }
     const int ab = v.anchor_bits, ag = v.anchor_group, rb = v.residual_bits, rg = v.residual_group;
     if (ab == 4 && ag == 32) {
         if (rb == 0) return launch_mean<D, 4, 32, 0, 32, P>(v.has_mean, p, stream);

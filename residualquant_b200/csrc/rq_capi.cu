@@ -287,8 +287,15 @@ int32_t rq_attention(const RqAttentionArgs* a) {
         return fail(RQ_ERR_INVALID_ARGUMENT, "16-byte aligned contiguous fp32 key mean required");
     if ((status = check_rotation(a->key_rotation, "key_rotation")) != RQ_OK) return status;
     if ((status = check_rotation(a->value_rotation, "value_rotation")) != RQ_OK) return status;
-    if (s.reference_mode != RQ_REFERENCE_ANCHOR && s.num_records > 1)
-        return fail(RQ_ERR_UNSUPPORTED, "no compiled packed attention kernel for reference_mode=adjacent");
+    const bool adjacent = s.reference_mode == RQ_REFERENCE_ADJACENT && s.num_records > 1;
+    if (adjacent) {
+        if (s.num_records > 4)
+            return fail(RQ_ERR_UNSUPPORTED, "No compiled packed CUDA kernel for adjacent groups of more than 4 records");
+        for (int r = 0; r <= a->loop_index; ++r)
+            if (s.bits[r] == 4 && s.group_size[r] != 32)
+                return fail(RQ_ERR_UNSUPPORTED, "No compiled packed CUDA kernel for an INT4 record with groups of %d",
+                            s.group_size[r]);
+    }
 
     rq::AttentionVariant v;
     v.head_dim = s.head_dim;
@@ -299,6 +306,7 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     v.residual_group = anchor_loop ? 32 : s.group_size[a->loop_index];
     v.page_tokens = s.page_tokens;
     v.has_mean = a->key_mean != nullptr;
+    v.adjacent = adjacent;
     if (!rq::attention_variant_available(v))
         return fail(RQ_ERR_UNSUPPORTED,
                     "No compiled packed CUDA kernel for heads=%d, head_dim=%d, anchor=(%d,%d), loop record=(%d,%d), "
@@ -346,6 +354,14 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     p.residual_offset = rq_record_offset(&s, a->loop_index);
     p.anchor_index = s.anchor_index;
     p.loop_index = a->loop_index;
+    if (adjacent) {
+        p.chain_count = a->loop_index + 1;
+        for (int r = 0; r < p.chain_count; ++r) {
+            p.chain_bits[r] = s.bits[r];
+            p.chain_group[r] = s.group_size[r];
+        }
+        for (int r = 0; r <= p.chain_count; ++r) p.chain_offset[r] = rq_record_offset(&s, r);
+    }
     p.splits = splits;
     uint8_t* base = static_cast<uint8_t*>(a->workspace);
     p.status = reinterpret_cast<int32_t*>(base);

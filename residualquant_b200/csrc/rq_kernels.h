@@ -74,6 +74,10 @@ struct AttentionParams {
     int anchor_offset;           // bytes per token before the anchor record
     int residual_offset;         // bytes per token before the current loop's record (unused on the anchor loop)
     int anchor_index, loop_index;
+    // Adjacent reference mode: the loop's value is a chain over records 0..loop_index, all of which are read.
+    int chain_count;             // loop_index + 1 (0 in anchor mode)
+    int chain_bits[4], chain_group[4];
+    int chain_offset[5];         // bytes per token before record r; [chain_count] = bytes of the staged prefix
     int splits;
     int32_t* status;
     int32_t* counters;
@@ -89,6 +93,7 @@ struct AttentionVariant {
     int residual_group; // 16 | 32 (ignored on the anchor loop)
     int page_tokens;    // 16 | 32
     bool has_mean;
+    bool adjacent;      // adjacent reference mode: record types are run-time data (AttentionParams::chain_*)
 };
 
 // Returns cudaErrorInvalidDeviceFunction when the variant is not compiled in.

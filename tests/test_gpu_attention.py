@@ -195,8 +195,9 @@ def test_argument_errors_raise_runtime_error():
         call(query_start_loc=qsl[:1])
     with pytest.raises(RuntimeError, match="page table"):
         call(block_table=table.long())
-    with pytest.raises(RuntimeError, match="adjacent"):
-        call(records=[[4, 32], [2, 32], [2, 32], [2, 32]], anchor_index=0, reference_mode="adjacent", loop_index=1)
+    five = torch.zeros((2, case.num_blocks, case.heads, 16, 5 * 42), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="more than 4 records"):
+        call(records=[[2, 32]] * 5, anchor_index=0, reference_mode="adjacent", loop_index=1, kv_cache=five)
     other = torch.zeros((2, case.num_blocks, case.heads, 16, 328), dtype=torch.uint8, device="cuda")
     with pytest.raises(RuntimeError, match="No compiled packed CUDA kernel"):
         call(records=[[4, 16]] * 4, loop_index=0, kv_cache=other)
@@ -275,3 +276,20 @@ def test_other_schedules_of_the_registry(records, anchor, head_dim):
     cache = helpers.oracle_cache(case)
     for loop in range(len(records)):
         _check(case, cache, loop, splits=2 if loop % 2 else 0)
+
+
+@pytest.mark.parametrize("records", [
+    ((2, 32), (2, 32), (2, 32), (2, 32)),
+    ((4, 32), (2, 16), (2, 16), (2, 16)),
+    ((2, 32), (2, 32), (2, 32), (4, 32)),
+    ((4, 32), (4, 32), (4, 32), (4, 32)),
+])
+@pytest.mark.parametrize("head_dim,page", [(128, 16), (96, 32)])
+def test_adjacent_reference_mode(records, head_dim, page):
+    """Adjacent mode: loop r is restored as alpha_r * (loop r-1) + residual_r, a chain over records 0..r
+    (reference: attention/compute.cuh:123-197, dispatch/decode_*_adjacent_0_g{16,32}.cu)."""
+    case = helpers.make_case(44, head_dim, 2, [140, 35, 1], page_tokens=page, records=records, anchor_index=0,
+                             reference_mode="adjacent", with_mean=(head_dim == 128))
+    cache = helpers.oracle_cache(case)
+    for loop in range(4):
+        _check(case, cache, loop, splits=3 if loop == 2 else 0)
