@@ -61,6 +61,7 @@ def parse_args():
     p.add_argument("--shard", default="sequences", choices=["sequences", "heads"],
                    help="sequences: every rank owns its own batch (weak scaling, no collective); heads: every rank holds "
                         "all sequences but only its KV heads and all-gathers the attention output (strong scaling)")
+    p.add_argument("--splits", type=int, default=0, help="force the number of KV partitions per row (0 = library default)")
     p.add_argument("--compare-bf16", action="store_true",
                    help="also time a BF16-KV decode attention (torch SDPA, contiguous KV) of one layer's 4 loops")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -329,6 +330,7 @@ def run_gpu(args):
             raise RuntimeError("more ranks than KV heads")
     replicas = 1 if shard_heads else world                          # independent copies of the batch in the job
     B, L, layers = args.batch, args.context, args.layers
+    _cuda.set_attention_splits(args.splits)
     stack = build_stack(args, device, torch)
     records, caches = stack["records"], stack["caches"]
     # The model's weights absorb the value rotation in the served configuration (weights.py:9-37 of the reference),

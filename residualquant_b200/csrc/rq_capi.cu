@@ -215,14 +215,16 @@ int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32
         }
         if (sm_count_cache[device] > 0) sms = sm_count_cache[device];
     }
-    // Aim for about eight CTAs per SM overall (a few resident waves) while keeping at least sixteen pages
-    // (four per warp) in a partition.
+    // Measured on B200 (batch 1..64, context 8192): the step is fastest with about seven CTAs per SM in the whole
+    // grid (1.75 resident waves at 4 CTAs/SM), a power-of-two partition count, and at least 32 pages per partition;
+    // every extra partition costs a prologue (query rotation, first page fetch) and a merge.
     const int64_t base = static_cast<int64_t>(num_query_rows) * heads;
-    int64_t want = (8LL * sms + base - 1) / base;
-    const int64_t by_length = max_blocks_per_request > 0 ? (max_blocks_per_request + 15) / 16 : 1;
+    int64_t want = (7LL * sms) / base;
+    const int64_t by_length = max_blocks_per_request > 0 ? max_blocks_per_request / 32 : 1;
     if (want > by_length) want = by_length;
     if (want > 64) want = 64;
     if (want < 1) want = 1;
+    while (want & (want - 1)) want &= want - 1;  // largest power of two not above
     (void)page_tokens;
     return static_cast<int32_t>(want);
 }
