@@ -11,6 +11,8 @@
 // Work split: a row = one (token, head, plane); 8 lanes own a row, each lane 16 consecutive channels, so a
 // warp owns 4 consecutive tokens of one head and a 128-thread CTA 16 consecutive tokens (one vLLM block when
 // the slots are contiguous).  Grid = (ceil(tokens/16), heads, 2 planes).
+#include <type_traits>
+
 #include "rq_common.cuh"
 #include "rq_kernels.h"
 
@@ -93,13 +95,35 @@ __device__ __forceinline__ float row_dot(const float (&a)[16], const float (&b)[
     return acc;
 }
 
+// A quantized 16-channel slice.  magic[i] = bit pattern of the float 2^23 + code[i], i.e. 0x4B000000 + code[i]:
+// the form the codes come out of the rounding step in, cheap to pack and to turn back into a float.
 struct GroupCode {
-    uint32_t code[16];
+    uint32_t magic[16];
     uint8_t scale8, offset8;
 };
+constexpr uint32_t kMagicBits = 0x4B000000u;  // 8388608.0f
+__device__ __forceinline__ float code_value(uint32_t magic) { return __fsub_rn(__uint_as_float(magic), 8388608.f); }
+
+// sum_i magic[i] << (BITS * i) (mod 2^32) carries this constant on top of the packed codes.
+template <int BITS, int COUNT>
+__host__ __device__ constexpr uint32_t packed_magic_bias() {
+    uint32_t bias = 0;
+    for (int i = 0; i < COUNT; ++i) bias += kMagicBits << (BITS * i);
+    return bias;
+}
+// COUNT codes of BITS bits each, code i at bit BITS*i: one shift-add per code.
+template <int BITS, int COUNT>
+__device__ __forceinline__ uint32_t pack_codes(const uint32_t* magic) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = COUNT - 1; i >= 0; --i) word = (word << BITS) + magic[i];
+    constexpr uint32_t kBias = packed_magic_bias<BITS, COUNT>();
+    return word - kBias;
+}
 
 // Asymmetric group quantizer (reference: quantize/kernel.cuh:111-158; scripts/calibration/quantization.py:40-53).
-__device__ __forceinline__ GroupCode group_quantize(const float (&z)[16], int bits, int group) {
+template <int BITS>
+__device__ __forceinline__ GroupCode group_quantize(const float (&z)[16], int group) {
     GroupCode out;
     float low = z[0], high = z[0];
 #pragma unroll
@@ -111,38 +135,37 @@ __device__ __forceinline__ GroupCode group_quantize(const float (&z)[16], int bi
         low = fminf(low, __shfl_xor_sync(kFullMask, low, 1));
         high = fmaxf(high, __shfl_xor_sync(kFullMask, high, 1));
     }
-    const float levels = bits == 2 ? 3.f : 15.f;
+    constexpr float kLevels = BITS == 2 ? 3.f : 15.f;
     const float center = __fmul_rn(__fadd_rn(low, high), 0.5f);
     const float width = __fsub_rn(high, low);
-    const float radius = bits == 2 ? __fmul_rn(__fmul_rn(width, 0.9f), 0.5f) : __fmul_rn(width, 0.5f);
+    const float radius = BITS == 2 ? __fmul_rn(__fmul_rn(width, 0.9f), 0.5f) : __fmul_rn(width, 0.5f);
     // "+ 0.0f" turns a -0.0 lower bound into +0.0 so the stored byte never depends on which signed zero won a min/max.
     out.offset8 = fp8_encode(__fadd_rn(__fsub_rn(center, radius), 0.0f));
-    out.scale8 = fp8_encode(__fdiv_rn(__fmul_rn(2.f, radius), levels));
+    out.scale8 = fp8_encode(__fdiv_rn(__fmul_rn(2.f, radius), kLevels));
     const float offset = fp8_decode(out.offset8), scale = fp8_decode(out.scale8);
     // n = (z - offset) / scale, correctly rounded, without a division per channel: with r = RN(1/scale),
     // q0 = RN(d*r), e = d - q0*scale (exact in one fma), n = RN(q0 + e*r) is the IEEE quotient (the divisor has a
     // 4-bit significand; checked against exact rational arithmetic for every FP8 scale).
     // code = floor(n) + (n - floor(n) > 0.5)  ==  ceil(n - 0.5): a half rounds down, n - 0.5 is exact for n >= 0.5.
+    // The clamp to [0, levels] commutes with the ceiling (integer bounds), so it is done first, in floating point;
+    // adding 2^23 rounding upwards then leaves ceil(t) in the low significand bits.  A zero scale gives r = 0,
+    // n = 0 and code 0, as the reference stores; a NaN loses the first max() and also becomes code 0.
     const float r = scale > 0.f ? __frcp_rn(scale) : 0.f;
-    const int top = bits == 2 ? 3 : 15;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        uint32_t code = 0;
-        if (scale > 0.f) {
-            const float d = __fsub_rn(z[i], offset);
-            const float q0 = __fmul_rn(d, r);
-            const float e = __fmaf_rn(-q0, scale, d);
-            const float n = __fmaf_rn(e, r, q0);
-            code = static_cast<uint32_t>(min(max(__float2int_ru(__fsub_rn(n, 0.5f)), 0), top));
-        }
-        out.code[i] = code;
+        const float d = __fsub_rn(z[i], offset);
+        const float q0 = __fmul_rn(d, r);
+        const float e = __fmaf_rn(-q0, scale, d);
+        const float n = __fmaf_rn(e, r, q0);
+        const float t = fminf(fmaxf(__fsub_rn(n, 0.5f), 0.f), kLevels);
+        out.magic[i] = __float_as_uint(__fadd_ru(t, 8388608.f));
     }
     return out;
 }
 
 // bf16( code * bf16(scale) + bf16(offset) ) with a single rounding (reference: kernel.cuh:161-186).
-__device__ __forceinline__ float restore_bf16(uint32_t code, float scale, float offset) {
-    return __bfloat162float(__hfma(__ushort2bfloat16_rn(static_cast<unsigned short>(code)),
+__device__ __forceinline__ float restore_bf16(uint32_t magic, float scale, float offset) {
+    return __bfloat162float(__hfma(__float2bfloat16_rn(code_value(magic)),
                                    __float2bfloat16_rn(scale), __float2bfloat16_rn(offset)));
 }
 __device__ __forceinline__ float bf16_add(float a, float b) {
@@ -151,7 +174,7 @@ __device__ __forceinline__ float bf16_add(float a, float b) {
 __device__ __forceinline__ float bf16_round(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
 
 template <int D>
-__global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ QuantizeParams p) {
+__global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant__ QuantizeParams p) {
     constexpr int kSlices = D / 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = lane & 7;
@@ -183,8 +206,30 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
     uint8_t* page = p.cache + plane * p.plane_stride +
                     (active ? (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width : 0);
 
-    // flip = apply the rotation's sign diagonal while loading (rows that go straight into the forward rotation)
-    auto load_row = [&](int r, float (&x)[16], bool flip) {
+    // Rows of 16-byte aligned bf16 tensors are fetched as two 16-byte words per lane, one record ahead of their use.
+    const bool packed_rows = p.vector_loads && pre_rotated == nullptr;
+    auto fetch_packed = [&](int r, uint32_t (&w)[8]) {
+        uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+        if (active) {
+            const uint4* src = reinterpret_cast<const uint4*>(sources[r] + static_cast<int64_t>(token) * strides[r] +
+                                                              head * D + 16 * j);
+            lo = __ldg(src);
+            hi = __ldg(src + 1);
+        }
+        w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w;
+        w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+    };
+    // flip = apply the rotation's sign diagonal (rows that go straight into the forward rotation)
+    auto unpack = [&](const uint32_t (&w)[8], float (&x)[16], bool flip) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t flipped = flip ? w[i] ^ sign_words[i] : w[i];  // sign diagonal on the raw bf16 pair
+            x[2 * i] = __uint_as_float(flipped << 16);
+            x[2 * i + 1] = __uint_as_float(flipped & 0xffff0000u);
+        }
+    };
+    // the other two sources: fp32 rows already rotated by the dense path, and bf16 rows without 16-byte alignment
+    auto load_unpacked = [&](int r, float (&x)[16], bool flip) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = 0.f;
         if (!active) return;
@@ -199,55 +244,40 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
             return;
         }
         const __nv_bfloat16* src = sources[r] + static_cast<int64_t>(token) * strides[r] + head * D + 16 * j;
-        if (p.vector_loads) {
-            const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src));
-            const uint4 hi = __ldg(reinterpret_cast<const uint4*>(src) + 1);
-            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t flipped = flip ? w[i] ^ sign_words[i] : w[i];  // sign diagonal on the raw bf16 pair
-                x[2 * i] = __uint_as_float(flipped << 16);
-                x[2 * i + 1] = __uint_as_float(flipped & 0xffff0000u);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float v = __bfloat162float(src[i]);
-                x[i] = (flip && ((sign16 >> i) & 1u)) ? -v : v;
-            }
+        for (int i = 0; i < 16; ++i) {
+            const float v = __bfloat162float(src[i]);
+            x[i] = (flip && ((sign16 >> i) & 1u)) ? -v : v;
         }
     };
     auto load_mean = [&](int r, float (&m)[16]) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) m[i] = 0.f;
         if (centered && j < kSlices) {
-            const float* src = p.mean + (static_cast<int64_t>(r) * p.heads + head) * D + 16 * j;
+            const float4* src = reinterpret_cast<const float4*>(p.mean + (static_cast<int64_t>(r) * p.heads + head) * D + 16 * j);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) m[i] = src[i];
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = __ldg(src + i);
+                m[4 * i] = v.x; m[4 * i + 1] = v.y; m[4 * i + 2] = v.z; m[4 * i + 3] = v.w;
+            }
         }
     };
     // Quantize z (already centered) as record r, store it, return the codes and parameters.
-    auto commit = [&](int r, const float (&z)[16], uint16_t alpha_bits) -> GroupCode {
-        const int bits = p.bits[r], group = p.group[r];
-        const GroupCode q = group_quantize(z, bits, group);
+    auto commit_as = [&](auto bits_tag, int r, const float (&z)[16], uint16_t alpha_bits) -> GroupCode {
+        constexpr int kBits = decltype(bits_tag)::value;
+        const int group = p.group[r];
+        const GroupCode q = group_quantize<kBits>(z, group);
         if (active) {
-            const int code_bytes = D * bits / 8, groups = D / group;
+            constexpr int kCodeBytes = D * kBits / 8;
+            const int groups = D / group;
             uint8_t* record = page + static_cast<int64_t>(P) * p.record_offset[r];
-            if (bits == 2) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) word |= q.code[i] << (2 * i);
-                *reinterpret_cast<uint32_t*>(record + tok * code_bytes + 4 * j) = word;
+            if (kBits == 2) {
+                *reinterpret_cast<uint32_t*>(record + tok * kCodeBytes + 4 * j) = pack_codes<2, 16>(q.magic);
             } else {
-                uint32_t lo = 0, hi = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    lo |= q.code[i] << (4 * i);
-                    hi |= q.code[8 + i] << (4 * i);
-                }
-                *reinterpret_cast<uint2*>(record + tok * code_bytes + 8 * j) = make_uint2(lo, hi);
+                *reinterpret_cast<uint2*>(record + tok * kCodeBytes + 8 * j) =
+                    make_uint2(pack_codes<4, 8>(q.magic), pack_codes<4, 8>(q.magic + 8));
             }
-            uint8_t* scales = record + P * code_bytes;
+            uint8_t* scales = record + P * kCodeBytes;
             uint8_t* offsets = scales + P * groups;
             if (group == 16) {
                 scales[tok * groups + j] = q.scale8;
@@ -257,28 +287,40 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
                 offsets[tok * groups + (j >> 1)] = q.offset8;
             }
             if (j == 0)
-                *reinterpret_cast<uint16_t*>(record + P * (code_bytes + 2 * groups) + tok * 2) = alpha_bits;
+                *reinterpret_cast<uint16_t*>(record + P * (kCodeBytes + 2 * groups) + tok * 2) = alpha_bits;
         }
         return q;
     };
-    auto coefficient = [&](const float (&x)[16], const float (&ref)[16]) -> float {
+    auto commit = [&](int r, const float (&z)[16], uint16_t alpha_bits) -> GroupCode {
+        if (p.bits[r] == 2) return commit_as(std::integral_constant<int, 2>{}, r, z, alpha_bits);
+        return commit_as(std::integral_constant<int, 4>{}, r, z, alpha_bits);
+    };
+    // den = row_dot(ref, ref) is passed in: in anchor mode every residual record divides by the same sum.
+    auto coefficient = [&](const float (&x)[16], const float (&ref)[16], float den) -> float {
         if (p.coefficient == RQ_COEFF_UNIT) return 1.f;
         if (p.coefficient == RQ_COEFF_NORM) {
-            const float num = row_dot(x, x), den = row_dot(ref, ref);
+            const float num = row_dot(x, x);
             return den > 0.f ? __fdiv_rn(__fsqrt_rn(num), fmaxf(__fsqrt_rn(den), 1e-6f)) : 0.f;
         }
-        const float num = row_dot(x, ref), den = row_dot(ref, ref);
-        return __fdiv_rn(num, fmaxf(den, 1e-12f));
+        return __fdiv_rn(row_dot(x, ref), fmaxf(den, 1e-12f));
     };
-
+    // records in processing order: the anchor, then the others in loop order
     const int anchor = p.anchor;
+    auto record_at = [&](int k) { return k == 0 ? anchor : (k - 1 < anchor ? k - 1 : k); };
+
+    uint32_t words[8], ahead[8];
+    if (packed_rows) {
+        fetch_packed(anchor, words);
+        if (p.num_records > 1) fetch_packed(record_at(1), ahead);
+    }
+
     float ref[16];  // bf16-valued reconstruction that residuals predict from
     {
         float y[16], mean[16];
-        load_row(anchor, y, true);
+        if (packed_rows) unpack(words, y, true); else load_unpacked(anchor, y, true);
         if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
-        load_mean(anchor, mean);
         if (centered) {
+            load_mean(anchor, mean);
 #pragma unroll
             for (int i = 0; i < 16; ++i) y[i] = __fsub_rn(y[i], mean[i]);
         }
@@ -287,14 +329,14 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
         if (p.chain == RQ_CHAIN_KERNEL) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                ref[i] = restore_bf16(q.code[i], scale, offset);
+                ref[i] = restore_bf16(q.magic[i], scale, offset);
                 if (centered) ref[i] = bf16_add(ref[i], bf16_round(mean[i]));
             }
         } else {
             // decoded value (+ mean) back in original coordinates, rounded to bf16 there
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                ref[i] = __fmaf_rn(static_cast<float>(q.code[i]), scale, offset);
+                ref[i] = __fmaf_rn(code_value(q.magic[i]), scale, offset);
                 if (centered) ref[i] = __fadd_rn(ref[i], mean[i]);
             }
             if (rotated) rotate_row<D, true>(ref, j, sign16, rscale);
@@ -302,22 +344,30 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
             for (int i = 0; i < 16; ++i) ref[i] = bf16_round(ref[i]);
         }
     }
+    float den = 0.f;
+    if (p.coefficient != RQ_COEFF_UNIT && p.num_records > 1) den = row_dot(ref, ref);
 
-    for (int r = 0; r < p.num_records; ++r) {
-        if (r == anchor) continue;
+    for (int k = 1; k < p.num_records; ++k) {
+        const int r = record_at(k);
         float y[16], mean[16];
-        load_row(r, y, p.chain == RQ_CHAIN_KERNEL);
-        load_mean(r, mean);
+        if (packed_rows) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) words[i] = ahead[i];
+            if (k + 1 < p.num_records) fetch_packed(record_at(k + 1), ahead);
+            unpack(words, y, p.chain == RQ_CHAIN_KERNEL);
+        } else {
+            load_unpacked(r, y, p.chain == RQ_CHAIN_KERNEL);
+        }
         uint16_t alpha_bits;
         if (p.chain == RQ_CHAIN_KERNEL) {
             if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
-            const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref));
+            const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref, den));
             alpha_bits = __bfloat16_as_ushort(stored);
             const float alpha = __bfloat162float(stored);
 #pragma unroll
             for (int i = 0; i < 16; ++i) y[i] = __fmaf_rn(-ref[i], alpha, y[i]);
         } else {
-            const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref));
+            const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref, den));
             alpha_bits = __bfloat16_as_ushort(stored);
             const float alpha = __bfloat162float(stored);
 #pragma unroll
@@ -329,6 +379,7 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
             if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
         }
         if (centered) {
+            load_mean(r, mean);
 #pragma unroll
             for (int i = 0; i < 16; ++i) y[i] = __fsub_rn(y[i], mean[i]);
         }
@@ -339,11 +390,12 @@ __global__ void __launch_bounds__(128) quantize_kernel(const __grid_constant__ Q
             const __nv_bfloat16 alpha_bf = __ushort_as_bfloat16(alpha_bits);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                float restored = restore_bf16(q.code[i], scale, offset);
+                float restored = restore_bf16(q.magic[i], scale, offset);
                 if (centered) restored = bf16_add(restored, bf16_round(mean[i]));
                 ref[i] = __bfloat162float(
                     __hfma(__float2bfloat16_rn(ref[i]), alpha_bf, __float2bfloat16_rn(restored)));
             }
+            if (p.coefficient != RQ_COEFF_UNIT && k + 1 < p.num_records) den = row_dot(ref, ref);
         }
     }
 }
