@@ -61,6 +61,9 @@ def parse_args():
     p.add_argument("--shard", default="sequences", choices=["sequences", "heads"],
                    help="sequences: every rank owns its own batch (weak scaling, no collective); heads: every rank holds "
                         "all sequences but only its KV heads and all-gathers the attention output (strong scaling)")
+    p.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                   help="with --shard heads: fused = the attention kernel stores into every GPU's gathered output over "
+                        "NVLink and a barrier kernel follows (captured in the graph); nccl = one all-gather per call, eager")
     p.add_argument("--splits", type=int, default=0, help="force the number of KV partitions per row (0 = library default)")
     p.add_argument("--compare-bf16", action="store_true",
                    help="also time a BF16-KV decode attention (torch SDPA, contiguous KV) of one layer's 4 loops")
@@ -190,8 +193,10 @@ def workload_config(args):
         "workload": f"config1 kernel sweep point: batch {args.batch} x context {args.context}, INT2 g{args.group} "
                     f"residuals + INT4 g32 anchor, {args.layers} layers x 4 loops, {args.heads} heads x {args.head_dim}, block {args.page}, "
                     "CUDA-graph decode step (4 attention + 1 quantize launch per layer)"
-                    + ("; KV heads sharded over the ranks, one NCCL all-gather of the output per attention call, eager step"
-                       if args.shard == "heads" else ""),
+                    + ("" if args.shard != "heads" else
+                       "; KV heads sharded over the ranks, output rows stored into every GPU's gathered buffer by the attention "
+                       "kernel + one barrier kernel per call, captured in the graph" if args.gather == "fused" else
+                       "; KV heads sharded over the ranks, one NCCL all-gather of the output per attention call, eager step"),
         "batch_per_gpu": args.batch,
         "sharding": args.shard,
         "context": args.context,
@@ -356,14 +361,22 @@ def run_gpu(args):
         slot_mapping.copy_(block_table[batch_index, position // PAGE].long() * PAGE + position % PAGE)
 
     gathered = [None]
+    # Head sharding: the output projection needs every head.  "fused": the attention kernel stores its rows into every
+    # GPU's gathered buffer over NVLink and a barrier kernel follows (graph capturable); "nccl": one all-gather per call.
+    fused_gather = sharding.HeadGather(B, heads_total, HEAD_DIM, device) if shard_heads and args.gather == "fused" else None
 
     def hot_path():
         for layer in range(layers):
             for loop in range(4):
+                if fused_gather is not None:
+                    _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer],
+                                    out[layer, loop], qsl, seq_lens, block_table, key_rot, None, None, records,
+                                    "anchor", 3, loop, gather=fused_gather, gather_buffer=loop % 2)
+                    fused_gather.barrier()
+                    continue
                 _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer], out[layer, loop],
                                 qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
                 if shard_heads:
-                    # the output projection needs every head: one all-gather of [B, local heads, D] per call
                     gathered[0] = sharding.gather_heads(out[layer, loop], heads_total)
             _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
                            key_rot, None, None, records, "anchor", 3, "ls")
@@ -378,7 +391,7 @@ def run_gpu(args):
         step_body()                      # eager warm-up: workspace, per-variant attributes
     stream.synchronize()
     seq_lens.fill_(L)
-    if shard_heads and world > 1:
+    if shard_heads and world > 1 and fused_gather is None:
         # The step contains NCCL all-gathers; it is replayed eagerly rather than from a captured graph.
         class _Eager:
             @staticmethod
@@ -391,7 +404,7 @@ def run_gpu(args):
             step_body()
     seq_lens.fill_(L)
     torch.cuda.synchronize(device)
-    launches_per_step = layers * 5
+    launches_per_step = layers * (9 if fused_gather is not None else 5)
 
     def barrier():
         if world > 1:
@@ -419,6 +432,13 @@ def run_gpu(args):
         sampler.start()
     ms = timed(graph.replay, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    if fused_gather is not None:
+        # the gathered rows of the last call must equal an NCCL all-gather of every rank's own output
+        fused_gather.check()
+        last = out[layers - 1, 3]
+        expected = sharding.gather_heads(last, heads_total)
+        if not torch.equal(fused_gather.gathered(3 % 2), expected):
+            raise RuntimeError("fused head gather differs from the all-gathered outputs")
     value = replicas * B * args.steps / (ms * 1e-3)
 
     # ---------------- end to end: host rows in, outputs back ----------------

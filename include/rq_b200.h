@@ -33,6 +33,7 @@ extern "C" {
 #endif
 
 #define RQ_MAX_RECORDS 8
+#define RQ_MAX_PEERS 8 /* GPUs of one node that a head-sharded output can be stored to */
 
 typedef enum RqStatus {
     RQ_OK = 0,
@@ -151,6 +152,16 @@ typedef struct RqAttentionArgs {
                                        rq_attention_workspace_init() before its first use */
     size_t workspace_bytes;
     void* stream;
+    /* Head-sharded serving (each GPU holds a slice of the KV heads, the output projection needs all of them): when
+     * num_peers > 0 the kernel's epilogue ALSO stores every finished output row into the gathered buffer
+     * bf16 [rows][gather_stride] of each of the num_peers GPUs (its own included), at head gather_head_offset, with plain
+     * stores over NVLink -- the all-gather that would follow the kernel is fused into its epilogue (the reference is single-GPU).
+     * peer_output[i] is GPU i's buffer as mapped into THIS process (cudaIpcOpenMemHandle or equivalent).  The stores
+     * are complete on the peers after rq_peer_barrier.  Zero-initialised fields (num_peers = 0) switch this off. */
+    int32_t num_peers;
+    int32_t gather_head_offset;      /* first head of this rank inside a gathered row */
+    int64_t gather_stride;           /* ELEMENTS between rows of the gathered buffers (>= total heads * head_dim) */
+    void* peer_output[RQ_MAX_PEERS];
 } RqAttentionArgs;
 
 /* Partition count the library would pick for this shape on the current device (a pure host function of its
@@ -185,6 +196,36 @@ int32_t rq_attention_status(const void* workspace, void* stream);
  * calls on a device share the one buffer: two calls whose kernels overlap on the GPU (different streams) race;
  * keep them on one stream or order them with events. */
 int32_t rq_attention_noalloc(const RqAttentionArgs* args);
+
+/* Barrier between the GPUs of one node, for the fused output gather above: a one-CTA kernel on `stream` that publishes
+ * this rank's arrival in every peer's flag array (system-scope release store over NVLink) and then waits until every
+ * peer has published the same epoch in this rank's own array.  When it completes, all peer stores issued by earlier
+ * work of every rank's stream are visible here.  CUDA-graph capturable: the epoch lives in device memory and advances
+ * by one per launch.  The wait is bounded (timeout_ns of the GPU's global timer, 0 = 2 s): on expiry the kernel records
+ * RQ_ERR_DEVICE_TIMEOUT in `state` and returns, it never spins forever.
+ *   flags[i]  rank i's flag array, uint32 [RQ_MAX_PEERS], as mapped into this process; zeroed once before first use
+ *   state     this rank's own 256 bytes of device memory (epoch counter, status), zeroed once before first use */
+typedef struct RqPeerBarrierArgs {
+    int32_t world, rank;
+    void* flags[RQ_MAX_PEERS];
+    void* state;
+    uint64_t timeout_ns;
+    void* stream;
+} RqPeerBarrierArgs;
+int32_t rq_peer_barrier(const RqPeerBarrierArgs* args);
+/* Device memory that other processes of the node can map: a plain cudaMalloc (zero-filled), exported and opened
+ * with CUDA IPC handles of RQ_PEER_HANDLE_BYTES bytes that the host side exchanges however it likes
+ * (torch.distributed in this repository).  rq_peer_open maps a peer's allocation into the calling process with
+ * peer access from the current device; the pointer is what RqAttentionArgs.peer_output and
+ * RqPeerBarrierArgs.flags take.  Setup-time calls: they allocate and synchronize. */
+#define RQ_PEER_HANDLE_BYTES 64
+int32_t rq_peer_alloc(size_t bytes, void** pointer);
+int32_t rq_peer_free(void* pointer);
+int32_t rq_peer_export(const void* pointer, unsigned char* handle /* [RQ_PEER_HANDLE_BYTES] */);
+int32_t rq_peer_open(const unsigned char* handle, void** mapped);
+int32_t rq_peer_close(void* mapped);
+/* Synchronizes `stream` and returns the status recorded in `state`: RQ_OK or RQ_ERR_DEVICE_TIMEOUT. */
+int32_t rq_peer_barrier_status(const void* state, void* stream);
 
 const char* rq_last_error(void);
 const char* rq_version(void);

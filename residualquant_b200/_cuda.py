@@ -200,9 +200,16 @@ def attention(
     reference_mode: str,
     anchor_index: int,
     loop_index: int,
+    *,
+    gather=None,
+    gather_buffer: int = 0,
 ) -> None:
     """Decode attention of one loop over the packed pages plus the live token; writes `output` in place
-    (reference: plugins/residual_quantization/csrc/common/api.h:11-20, attention/api.cpp:8-115)."""
+    (reference: plugins/residual_quantization/csrc/common/api.h:11-20, attention/api.cpp:8-115).
+
+    `gather` (not part of the reference signature) is a `sharding.HeadGather`: when the KV heads are sharded over the
+    GPUs of a node, the kernel also stores every finished row into buffer `gather_buffer` of every GPU's gathered
+    output; call `gather.barrier()` afterwards, before anything reads the gathered rows."""
     lib = _lib.load()
     records = [list(r) for r in records]
     _validate_bf16_token_tensor(query)
@@ -265,6 +272,15 @@ def attention(
     args.value_rotation = _rotation_arg(value_rotation, query.device, heads, head_dim, keep)
     args.key_mean = key_mean.data_ptr() if key_mean is not None else None
     args.loop_index = loop_index
+    if gather is not None:
+        _require(gather.rows >= rows and gather.local_heads == heads and gather.head_dim == head_dim,
+                 "gathered output buffers do not match the query shape")
+        pointers = gather.peer_pointers(gather_buffer)
+        args.num_peers = len(pointers)
+        for i, pointer in enumerate(pointers):
+            args.peer_output[i] = pointer
+        args.gather_head_offset = gather.head_offset
+        args.gather_stride = gather.heads * head_dim
     with torch.cuda.device(query.device):
         splits = _forced_splits or lib.rq_attention_default_splits(rows, heads, block_table.size(1), kv_cache.size(3))
         args.num_splits = splits

@@ -9,6 +9,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.path.join(HERE, "librq_b200.so")
 
 RQ_MAX_RECORDS = 8
+RQ_MAX_PEERS = 8
+RQ_PEER_HANDLE_BYTES = 64
 RQ_OK = 0
 REFERENCE_MODES = {"anchor": 0, "adjacent": 1}
 COEFFICIENTS = {"unit": 0, "norm": 1, "ls": 2}
@@ -26,6 +28,13 @@ EXPORTS = (
     "rq_attention",
     "rq_attention_status",
     "rq_attention_noalloc",
+    "rq_peer_barrier",
+    "rq_peer_barrier_status",
+    "rq_peer_alloc",
+    "rq_peer_free",
+    "rq_peer_export",
+    "rq_peer_open",
+    "rq_peer_close",
     "rq_last_error",
     "rq_version",
 )
@@ -100,6 +109,21 @@ class RqAttentionArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
+        ("num_peers", ctypes.c_int32),
+        ("gather_head_offset", ctypes.c_int32),
+        ("gather_stride", ctypes.c_int64),
+        ("peer_output", ctypes.c_void_p * RQ_MAX_PEERS),
+    ]
+
+
+class RqPeerBarrierArgs(ctypes.Structure):
+    _fields_ = [
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("flags", ctypes.c_void_p * RQ_MAX_PEERS),
+        ("state", ctypes.c_void_p),
+        ("timeout_ns", ctypes.c_uint64),
+        ("stream", ctypes.c_void_p),
     ]
 
 
@@ -137,6 +161,20 @@ def load() -> ctypes.CDLL:
     lib.rq_attention_noalloc.restype = ctypes.c_int32
     lib.rq_attention_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.rq_attention_status.restype = ctypes.c_int32
+    lib.rq_peer_barrier.argtypes = [ctypes.POINTER(RqPeerBarrierArgs)]
+    lib.rq_peer_barrier.restype = ctypes.c_int32
+    lib.rq_peer_barrier_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.rq_peer_barrier_status.restype = ctypes.c_int32
+    lib.rq_peer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)]
+    lib.rq_peer_alloc.restype = ctypes.c_int32
+    lib.rq_peer_free.argtypes = [ctypes.c_void_p]
+    lib.rq_peer_free.restype = ctypes.c_int32
+    lib.rq_peer_export.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
+    lib.rq_peer_export.restype = ctypes.c_int32
+    lib.rq_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.rq_peer_open.restype = ctypes.c_int32
+    lib.rq_peer_close.argtypes = [ctypes.c_void_p]
+    lib.rq_peer_close.restype = ctypes.c_int32
     lib.rq_last_error.argtypes = []
     lib.rq_last_error.restype = ctypes.c_char_p
     lib.rq_version.argtypes = []

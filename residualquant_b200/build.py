@@ -28,6 +28,7 @@ UNITS = {
     "rq_attention_d128.cu": [],
     "rq_attention_d96.cu": [],
     "rq_rotate.cu": [],
+    "rq_peer.cu": [],
     "rq_capi.cu": [],
 }
 HEADERS = ["rq_common.cuh", "rq_kernels.h", "rq_attention_impl.cuh", os.path.join("..", "..", "include", "rq_b200.h")]

@@ -932,8 +932,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
     if (tid < D) {
         const float v_live = __bfloat162float(p.value[static_cast<int64_t>(row) * p.value_stride + head * D + tid]);
-        p.output[static_cast<int64_t>(row) * p.output_stride + head * D + tid] =
-            __float2bfloat16_rn(hist + v_live * (f_live / denom));
+        const __nv_bfloat16 result = __float2bfloat16_rn(hist + v_live * (f_live / denom));
+        p.output[static_cast<int64_t>(row) * p.output_stride + head * D + tid] = result;
+        // head-sharded serving: the same row goes straight into every GPU's gathered buffer (plain stores, own
+        // memory or a peer's over NVLink); a warp writes 64 contiguous bytes per peer
+        const int64_t gathered = static_cast<int64_t>(row) * p.gather_stride + (p.gather_head_offset + head) * D + tid;
+        for (int peer = 0; peer < p.num_peers; ++peer) p.peer_output[peer][gathered] = result;
     }
 }
 

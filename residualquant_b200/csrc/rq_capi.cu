@@ -391,6 +391,21 @@ int32_t rq_attention(const RqAttentionArgs* a) {
         p.rotated_query = rotated;
     }
     if (a->value_rotation.kind == RQ_ROTATION_DENSE_FP16) p.value_matrix = static_cast<const __half*>(a->value_rotation.data);
+    if (a->num_peers != 0) {
+        if (a->num_peers < 0 || a->num_peers > RQ_MAX_PEERS)
+            return fail(RQ_ERR_INVALID_ARGUMENT, "num_peers %d outside 0..%d", a->num_peers, RQ_MAX_PEERS);
+        if (a->gather_head_offset < 0 || a->gather_stride < (static_cast<int64_t>(a->gather_head_offset) + s.heads) * s.head_dim)
+            return fail(RQ_ERR_INVALID_ARGUMENT, "gathered rows of %lld elements cannot hold heads %d..%d",
+                        static_cast<long long>(a->gather_stride), a->gather_head_offset, a->gather_head_offset + s.heads);
+        for (int i = 0; i < a->num_peers; ++i) {
+            if (a->peer_output[i] == nullptr || !aligned(a->peer_output[i], 2))
+                return fail(RQ_ERR_INVALID_ARGUMENT, "peer_output[%d] must be a mapped bf16 buffer", i);
+            p.peer_output[i] = static_cast<__nv_bfloat16*>(a->peer_output[i]);
+        }
+        p.num_peers = a->num_peers;
+        p.gather_head_offset = a->gather_head_offset;
+        p.gather_stride = a->gather_stride;
+    }
     const cudaError_t err = rq::launch_attention(v, p, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "attention launch");
     return RQ_OK;
@@ -433,6 +448,83 @@ int32_t rq_attention_noalloc(const RqAttentionArgs* a) {
     copy.workspace = addresses[device];
     copy.workspace_bytes = RQ_STATIC_SCRATCH_BYTES;
     return rq_attention(&copy);
+}
+
+// ---- node-level barrier for the fused head gather ------------------------------------------------------------
+int32_t rq_peer_barrier(const RqPeerBarrierArgs* a) {
+    if (a == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null arguments");
+    if (a->world < 1 || a->world > RQ_MAX_PEERS || a->rank < 0 || a->rank >= a->world)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "rank %d of %d: at most %d GPUs of one node", a->rank, a->world, RQ_MAX_PEERS);
+    if (a->state == nullptr || !aligned(a->state, 8)) return fail(RQ_ERR_INVALID_ARGUMENT, "barrier state must be device memory");
+    rq::PeerBarrierParams p;
+    memset(&p, 0, sizeof(p));
+    for (int i = 0; i < a->world; ++i) {
+        if (a->flags[i] == nullptr || !aligned(a->flags[i], 4))
+            return fail(RQ_ERR_INVALID_ARGUMENT, "flags[%d] must be a mapped uint32 array", i);
+        p.flags[i] = static_cast<uint32_t*>(a->flags[i]);
+    }
+    p.state = static_cast<uint32_t*>(a->state);
+    p.world = a->world;
+    p.rank = a->rank;
+    p.timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
+    const cudaError_t err = rq::launch_peer_barrier(p, static_cast<cudaStream_t>(a->stream));
+    if (err != cudaSuccess) return fail_cuda(err, "peer barrier launch");
+    return RQ_OK;
+}
+
+int32_t rq_peer_alloc(size_t bytes, void** pointer) {
+    if (pointer == nullptr || bytes == 0) return fail(RQ_ERR_INVALID_ARGUMENT, "a size and a place for the pointer required");
+    static_assert(RQ_PEER_HANDLE_BYTES == sizeof(cudaIpcMemHandle_t), "handle size");
+    void* p = nullptr;
+    cudaError_t err = cudaMalloc(&p, bytes);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaMalloc(peer buffer)");
+    err = cudaMemset(p, 0, bytes);
+    if (err != cudaSuccess) {
+        cudaFree(p);
+        return fail_cuda(err, "clearing the peer buffer");
+    }
+    *pointer = p;
+    return RQ_OK;
+}
+
+int32_t rq_peer_free(void* pointer) {
+    const cudaError_t err = cudaFree(pointer);
+    return err == cudaSuccess ? RQ_OK : fail_cuda(err, "cudaFree(peer buffer)");
+}
+
+int32_t rq_peer_export(const void* pointer, unsigned char* handle) {
+    if (pointer == nullptr || handle == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null pointer");
+    cudaIpcMemHandle_t h;
+    const cudaError_t err = cudaIpcGetMemHandle(&h, const_cast<void*>(pointer));
+    if (err != cudaSuccess) return fail_cuda(err, "cudaIpcGetMemHandle");
+    memcpy(handle, &h, sizeof(h));
+    return RQ_OK;
+}
+
+int32_t rq_peer_open(const unsigned char* handle, void** mapped) {
+    if (handle == nullptr || mapped == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    const cudaError_t err = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaIpcOpenMemHandle");
+    *mapped = p;
+    return RQ_OK;
+}
+
+int32_t rq_peer_close(void* mapped) {
+    const cudaError_t err = cudaIpcCloseMemHandle(mapped);
+    return err == cudaSuccess ? RQ_OK : fail_cuda(err, "cudaIpcCloseMemHandle");
+}
+
+int32_t rq_peer_barrier_status(const void* state, void* stream) {
+    if (state == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null barrier state");
+    uint32_t words[2] = {0u, 0u};
+    cudaError_t err = cudaMemcpyAsync(words, state, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+    if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail_cuda(err, "reading the barrier state");
+    if (words[1] != 0u) return fail(static_cast<int32_t>(words[1]), "a peer did not reach barrier %u in time", words[0]);
+    return RQ_OK;
 }
 
 }  // extern "C"

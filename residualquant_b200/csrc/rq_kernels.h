@@ -82,7 +82,20 @@ struct AttentionParams {
     int32_t* status;
     int32_t* counters;
     float* partials;
+    // Fused head gather: finished rows also go to [rows][gather_stride] buffers of num_peers GPUs at gather_head_offset.
+    int num_peers, gather_head_offset;
+    int64_t gather_stride;
+    __nv_bfloat16* peer_output[RQ_MAX_PEERS];
 };
+
+// Node-level barrier kernel behind rq_peer_barrier.
+struct PeerBarrierParams {
+    uint32_t* flags[RQ_MAX_PEERS];
+    uint32_t* state;  // [0] epoch, [1] status
+    int world, rank;
+    unsigned long long timeout_ns;
+};
+cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream);
 
 // Kernel variant selector: which residual record (if any) is read next to the INT4/INT2 anchor.
 struct AttentionVariant {

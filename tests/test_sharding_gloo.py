@@ -26,6 +26,14 @@ def test_shard_counts_cover_everything():
     assert sharding.max_over_ranks(3.5, "cpu") == 3.5
 
 
+def test_gather_layout_is_aligned_and_disjoint():
+    one, flags, total = sharding.gather_layout(rows=16, heads=55, head_dim=96, buffers=2)
+    assert one % 256 == 0 and one >= 16 * 55 * 96 * 2
+    assert flags == 2 * one and total == flags + 256
+    one, flags, total = sharding.gather_layout(rows=1, heads=1, head_dim=96, buffers=1)
+    assert (one, flags, total) == (256, 256, 512)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
