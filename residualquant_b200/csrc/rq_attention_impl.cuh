@@ -385,18 +385,27 @@ __device__ __forceinline__ void accumulate_record(uint32_t base, int t, int js, 
 
 // Rotated, pre-scaled query of this (row, head) into shared memory: qs[c] = (q @ R)[c] * D^-1/2 * log2(e).
 // Executed by warp 0; lane L owns channels 4L .. 4L+3.
-template <int D>
-__device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs, float* qmax_out) {
+// Also computes the score of the live token (its K row is the raw bf16 input, original coordinates):
+// live = q.k * D^-1/2 * log2(e) - sum_c qs[c] * mean[loop][c]; the history scores leave out the same q.mean[loop]
+// constant (reference: prepare.cuh:229).
+template <int D, bool MEAN>
+__device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs, float* qmax_out,
+                                              float* live_out) {
     const int lane = threadIdx.x & 31;
     float x[4] = {0.f, 0.f, 0.f, 0.f};
+    float live_dot = 0.f;
     const bool owner = 4 * lane < D;
     if (owner) {
         const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + 4 * lane;
+        const __nv_bfloat16* k = p.key + static_cast<int64_t>(row) * p.key_stride + head * D + 4 * lane;
         const uint2 raw = *reinterpret_cast<const uint2*>(q);
+        const uint2 live = *reinterpret_cast<const uint2*>(k);
         x[0] = bf16_bits_to_float(raw.x & 0xffffu);
         x[1] = bf16_bits_to_float(raw.x >> 16);
         x[2] = bf16_bits_to_float(raw.y & 0xffffu);
         x[3] = bf16_bits_to_float(raw.y >> 16);
+        live_dot = x[0] * bf16_bits_to_float(live.x & 0xffffu) + x[1] * bf16_bits_to_float(live.x >> 16) +
+                   x[2] * bf16_bits_to_float(live.y & 0xffffu) + x[3] * bf16_bits_to_float(live.y >> 16);
     }
     float scale = rsqrtf(static_cast<float>(D)) * kLog2e;
     if (p.rotated_query != nullptr) {
@@ -438,18 +447,32 @@ __device__ __forceinline__ void prepare_query(const AttentionParams& p, int row,
         }
         scale *= p.key_rscale;
     }
-    float biggest = 0.f;
+    float biggest = 0.f, shift = 0.f;
     if (owner) {
+        float mean[4] = {0.f, 0.f, 0.f, 0.f};
+        if (MEAN) {
+            const float4 v = *reinterpret_cast<const float4*>(
+                p.mean + (static_cast<int64_t>(p.loop_index) * p.heads + head) * D + 4 * lane);
+            mean[0] = v.x; mean[1] = v.y; mean[2] = v.z; mean[3] = v.w;
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float v = x[i] * scale;
             qs[4 * lane + i] = v;
             biggest = fmaxf(biggest, fabsf(v));
+            shift += v * mean[i];
         }
     }
 #pragma unroll
-    for (int d = 16; d; d >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(kFullMask, biggest, d));
-    if (lane == 0) *qmax_out = biggest;
+    for (int d = 16; d; d >>= 1) {
+        biggest = fmaxf(biggest, __shfl_xor_sync(kFullMask, biggest, d));
+        live_dot += __shfl_xor_sync(kFullMask, live_dot, d);
+        if (MEAN) shift += __shfl_xor_sync(kFullMask, shift, d);
+    }
+    if (lane == 0) {
+        *qmax_out = biggest;
+        *live_out = live_dot * rsqrtf(static_cast<float>(D)) * kLog2e - shift;
+    }
 }
 
 // Undo an explicit value rotation on the history sum: h <- ((h H^T) * rscale) * sign.  Warp 0, in place in smem.
@@ -513,18 +536,24 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     const int row = blockIdx.x / (heads * splits);
 
     // ---- which request, which pages -----------------------------------------------------------------
+    // Decode batches have one row per request, so request == row is the guess; everything that only needs the guess
+    // is loaded in one go (independent loads, one memory latency) and re-read only if the guess was wrong.
     const int num_requests = p.num_requests;
-    if (row >= p.query_start_loc[num_requests]) return;  // graph padding: leave the output row untouched
     int request = min(row, num_requests - 1);
-    if (!(p.query_start_loc[request] <= row && row < p.query_start_loc[request + 1])) {
+    const int total_rows = __ldg(p.query_start_loc + num_requests);
+    const int guess_begin = __ldg(p.query_start_loc + request), guess_end = __ldg(p.query_start_loc + request + 1);
+    int seq_len = __ldg(p.seq_lens + request);
+    if (row >= total_rows) return;  // graph padding: leave the output row untouched
+    if (!(guess_begin <= row && row < guess_end)) {
         int lo = 0, hi = num_requests - 1;  // largest r with query_start_loc[r] <= row
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
             if (p.query_start_loc[mid] <= row) lo = mid; else hi = mid - 1;
         }
         request = lo;
+        seq_len = p.seq_lens[request];
     }
-    const int history = max(0, p.seq_lens[request] - 1);
+    const int history = max(0, seq_len - 1);
     const int pages = (history + P - 1) / P;
     const int chunk = (pages + splits - 1) / splits;
     const int page_begin = min(pages, split * chunk), page_end = min(pages, page_begin + chunk);
@@ -600,7 +629,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
     float* misc = warp_stat + 8;         // [0] last-arrival flag, [1] live score, [2] max |q|
-    if (warp == 0) prepare_query<D>(p, row, head, qs, misc + 2);
+    if (warp == 0) prepare_query<D, C::kMean>(p, row, head, qs, misc + 2, misc + 1);
+    if (warp == 1 && lane < D / 64) {
+        // the live token's V row is read at the very end of the CTA: have it in L2 by then
+        const __nv_bfloat16* v_row = p.value + static_cast<int64_t>(row) * p.value_stride + head * D + 64 * lane;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(v_row));
+    }
     __syncthreads();
 
     // The K side runs on integer dot products (dp2a: two s16 x u8 products per instruction) against a query slice
@@ -860,9 +894,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         __threadfence();
         const float* all = p.partials + (static_cast<int64_t>(row) * heads + head) * splits * (D + 2);
         part_m = kNever;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * (D + 2)));
         part_l = 0.f;
         value = 0.f;
+#pragma unroll 4
         for (int s = 0; s < splits; ++s) {
             const float ms = __ldcg(all + s * (D + 2));
             const float f = fast_exp2(ms - part_m);
@@ -871,29 +907,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         }
     }
 
-    // ---- live token, normalisation, optional inverse value rotation, store -------------------------------
-    if (warp == 0) {
-        float dot = 0.f, shift = 0.f;
-        if (4 * lane < D) {
-            const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + 4 * lane;
-            const __nv_bfloat16* k = p.key + static_cast<int64_t>(row) * p.key_stride + head * D + 4 * lane;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dot += __bfloat162float(q[i]) * __bfloat162float(k[i]);
-            if (C::kMean) {
-                // history scores leave out q.mean[loop]; the live score drops the same constant (prepare.cuh:229)
-                const float* mean = p.mean + (static_cast<int64_t>(p.loop_index) * heads + head) * D + 4 * lane;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) shift += qs[4 * lane + i] * mean[i];
-            }
-        }
-#pragma unroll
-        for (int d = 16; d; d >>= 1) {
-            dot += __shfl_xor_sync(kFullMask, dot, d);
-            shift += __shfl_xor_sync(kFullMask, shift, d);
-        }
-        if (lane == 0) misc[1] = dot * rsqrtf(static_cast<float>(D)) * kLog2e - shift;
-    }
-    __syncthreads();
+    // ---- live token (its score was computed in the prologue), normalisation, optional inverse value rotation, store ---
     const float live = misc[1];
     const float total_m = fmaxf(part_m, live);
     const float f_hist = part_l > 0.f ? fast_exp2(part_m - total_m) : 0.f;
