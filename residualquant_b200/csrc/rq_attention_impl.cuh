@@ -335,12 +335,19 @@ __device__ __forceinline__ float score_record(uint32_t base, int t, int js, cons
 
 // acc += weight * (code * scale + offset) over the slice for token t of one record: the code part goes into the half2
 // sums (pair 4b+i = channels 8b+i and 8b+i+4 of the slice), the offset part into one fp32 sum per 16 channels.
-template <int BITS, int GROUP, int P, int D, bool TWO_OFFSETS>
+// GUARDED (the last, partial page of a sequence): a token beyond the history has weight zero, but its bytes were never
+// written and may decode to NaN or infinity, so its parameters are replaced by zeros instead of being multiplied by zero.
+template <int BITS, int GROUP, int P, int D, bool TWO_OFFSETS, bool GUARDED = false>
 __device__ __forceinline__ void accumulate_record(uint32_t base, int t, int js, float weight, uint32_t (&acc_b)[16],
-                                                  float& acc_off0, float& acc_off1) {
+                                                  float& acc_off0, float& acc_off1, bool live = true) {
     using R = StagedRecord<BITS, GROUP, P, D>;
     float2 scales, offsets;
     load_parameters<BITS, GROUP, P, D>(base, t, js, scales, offsets);
+    if (GUARDED && !live) {
+        scales = make_float2(0.f, 0.f);
+        offsets = make_float2(0.f, 0.f);
+        weight = 0.f;
+    }
     acc_off0 += weight * offsets.x;
     if (TWO_OFFSETS) acc_off1 += weight * offsets.y;
     if (BITS == 4) {
@@ -639,8 +646,14 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // The K side runs on integer dot products (dp2a: two s16 x u8 products per instruction) against a query slice
     // quantized once per CTA; see QueryOperands.
-    const int j = lane & 3;              // slice: channels 32j .. 32j+31
-    const bool slice_ok = 32 * j < D;
+    // head_dim 128: 4 lanes per token, 8 tokens per warp step, a page is P/8 steps.
+    // head_dim  96: 3 lanes per token, 10 tokens per warp step (lanes 30 and 31 idle); steps run over the warp's tokens
+    //               as one stream across page boundaries, so that no step is left partly filled ("streamed").
+    constexpr bool kStream = D == 96;
+    constexpr int kStepTokens = kStream ? 10 : 8;
+    static_assert(!(kStream && kBulkCopy), "the streamed token loop tracks pages by commit groups");
+    const int j = kStream ? lane % 3 : lane & 3;  // slice: channels 32j .. 32j+31
+    const bool slice_ok = kStream ? lane < 30 : 32 * j < D;
     const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
     const float qmax = misc[2];
     constexpr bool kUse4 = C::kAdjacent || C::AB == 4 || C::RB == 4, kUse2 = C::kAdjacent || C::AB == 2 || C::RB == 2;
@@ -681,7 +694,9 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     bool failed = false;
-    const int slot = lane >> 2;          // token slot 0..7 inside a warp step
+    const int slot = kStream ? lane / 3 : lane >> 2;  // token slot inside a warp step
+    // streamed: the two other lanes of this lane's token (idle lanes point at themselves)
+    const int peer1 = slice_ok ? lane - j + (j + 1) % 3 : lane, peer2 = slice_ok ? lane - j + (j + 2) % 3 : lane;
     float carry = 1.f;                   // factor the fp32 sums still have to be multiplied by (deferred rescale)
 
     // half2 partial sums -> fp32 sums, every 8 tokens of a lane
@@ -700,31 +715,15 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         }
     };
 
-    int stage = 0;
-    uint32_t parity = 0;
-    int it_done = 0;  // pages fully consumed
-    for (int it = 0; it < warp_pages; ++it) {
-        if (kBulkCopy) {
-            if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
-        } else {
-            cp_async_wait<C::kStages - 1>();
-            __syncwarp();  // the other lanes' chunks of this page have landed too
-        }
-        const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
-        const uint32_t k_residual = k_anchor + C::kAnchorBytes;
-        const uint32_t v_anchor = k_anchor + (C::kAdjacent ? C::kMaxPrefixBytes : C::kPlaneBytes);
-        const uint32_t v_residual = v_anchor + C::kAnchorBytes;
-        constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
-        const int first_token = (page_begin + warp + kWarps * it) * P;
-        const int valid = history - first_token;  // >= P for every page but the last one of the history
-
-        // Full pages run without any per-token predicate; only the last page of a sequence can be partial.
-        auto process_page = [&](auto partial_tag) {
+    // One token of the lane's slot: score against the query slice, online softmax, value accumulation.
+    // `k_anchor` = shared address of the staged page (stage) the token lives in, `t` = its index inside the page.
+    auto process_token = [&](auto partial_tag, uint32_t k_anchor, int t, bool live_token) {
         constexpr bool kPartial = decltype(partial_tag)::value;
-#pragma unroll
-        for (int sub = 0; sub < P / 8; ++sub) {
-            const int t = sub * 8 + slot;
-            const bool live_token = !kPartial || t < valid;
+        [[maybe_unused]] const uint32_t k_residual = k_anchor + C::kAnchorBytes;
+        const uint32_t v_anchor = k_anchor + (C::kAdjacent ? C::kMaxPrefixBytes : C::kPlaneBytes);
+        [[maybe_unused]] const uint32_t v_residual = v_anchor + C::kAnchorBytes;
+        [[maybe_unused]] constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
+        {
             // ---------------- K: score of token t against the query slice (integer dot products) ----------------
             float part = 0.f;
             if constexpr (C::kAdjacent) {
@@ -751,8 +750,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                 part = part * alpha +
                        score_record<C::RB, C::RG, P, D>(k_residual, t, js, operands(std::integral_constant<int, C::RB>{}));
             }
-            part += __shfl_xor_sync(kFullMask, part, 1);
-            part += __shfl_xor_sync(kFullMask, part, 2);
+            if constexpr (kStream) {
+                part += __shfl_sync(kFullMask, part, peer1) + __shfl_sync(kFullMask, part, peer2);
+            } else {
+                part += __shfl_xor_sync(kFullMask, part, 1);
+                part += __shfl_xor_sync(kFullMask, part, 2);
+            }
             const float score = live_token ? part : kNever;
 
             // ---------------- online softmax of the token slot ----------------
@@ -779,9 +782,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                 for (int r = p.chain_count - 1; r >= 0; --r) {
                     const uint32_t base = v_anchor + P * p.chain_offset[r];
                     const int bits = p.chain_bits[r], group = p.chain_group[r];
-                    if (bits == 4) accumulate_record<4, 32, P, D, true>(base, t, js, weight, acc_b, acc_off0, acc_off1);
-                    else if (group == 32) accumulate_record<2, 32, P, D, true>(base, t, js, weight, acc_b, acc_off0, acc_off1);
-                    else accumulate_record<2, 16, P, D, true>(base, t, js, weight, acc_b, acc_off0, acc_off1);
+                    if (bits == 4)
+                        accumulate_record<4, 32, P, D, true, kPartial>(base, t, js, weight, acc_b, acc_off0, acc_off1, live_token);
+                    else if (group == 32)
+                        accumulate_record<2, 32, P, D, true, kPartial>(base, t, js, weight, acc_b, acc_off0, acc_off1, live_token);
+                    else
+                        accumulate_record<2, 16, P, D, true, kPartial>(base, t, js, weight, acc_b, acc_off0, acc_off1, live_token);
                     if (r > 0) {
                         const int alpha_at = P * (D * bits / 8 + 2 * (D / group));
                         weight *= bf16_bits_to_float(lds16(base + alpha_at + 2 * t));
@@ -790,13 +796,37 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             } else {
             float pa = prob;  // the V plane stores its own coefficient
             if constexpr (C::kResidual) pa *= bf16_bits_to_float(lds16(v_residual + kResidualAlphaAt + 2 * t));
-            accumulate_record<C::AB, C::AG, P, D, kTwoOffsets>(v_anchor, t, js, pa, acc_b, acc_off0, acc_off1);
+            accumulate_record<C::AB, C::AG, P, D, kTwoOffsets, kPartial>(v_anchor, t, js, pa, acc_b, acc_off0, acc_off1, live_token);
             if constexpr (C::kResidual)
-                accumulate_record<C::RB, C::RG, P, D, kTwoOffsets>(v_residual, t, js, prob, acc_b, acc_off0, acc_off1);
+                accumulate_record<C::RB, C::RG, P, D, kTwoOffsets, kPartial>(v_residual, t, js, prob, acc_b, acc_off0, acc_off1,
+                                                                             live_token);
             }
         }
-        };
-        if (valid >= P) process_page(std::false_type{}); else process_page(std::true_type{});
+    };
+
+    int stage = 0;
+    uint32_t parity = 0;
+    int it_done = 0;  // pages fully consumed
+    if constexpr (!kStream) {
+    for (int it = 0; it < warp_pages; ++it) {
+        if (kBulkCopy) {
+            if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
+        } else {
+            cp_async_wait<C::kStages - 1>();
+            __syncwarp();  // the other lanes' chunks of this page have landed too
+        }
+        const uint32_t k_anchor = ring_addr + stage * C::kStageBytes;
+        const int first_token = (page_begin + warp + kWarps * it) * P;
+        const int valid = history - first_token;  // >= P for every page but the last one of the history
+
+        // Full pages run without any per-token predicate; only the last page of a sequence can be partial.
+        if (valid >= P) {
+#pragma unroll
+            for (int sub = 0; sub < P / 8; ++sub) process_token(std::false_type{}, k_anchor, sub * 8 + slot, true);
+        } else {
+#pragma unroll
+            for (int sub = 0; sub < P / 8; ++sub) process_token(std::true_type{}, k_anchor, sub * 8 + slot, sub * 8 + slot < valid);
+        }
 
         if ((it + 1) % kFlushPages == 0) flush();
         __syncwarp();  // every lane has finished reading this stage
@@ -809,6 +839,43 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         if (!kBulkCopy) cp_async_commit();
         if (++stage == C::kStages) { stage = 0; parity ^= 1u; }
         it_done = it + 1;
+    }
+    } else {
+        // Streamed token loop.  Commit groups: kStages before the loop, one more per released page, so page q is group q
+        // and, with `released` pages handed back, at most kStages + released - 1 - q groups may still be pending when
+        // page q is needed.  A step touches at most two pages (kStepTokens < P) and `released` equals the first of them.
+        const int total = warp_pages * P;
+        const int steps = (total + kStepTokens - 1) / kStepTokens;
+        int released = 0, landed = 0;
+        for (int step = 0; step < steps; ++step) {
+            const int first = step * kStepTokens;
+            const int last_page = min((first + kStepTokens - 1) / P, warp_pages - 1);
+            if (last_page >= landed) {
+                if (last_page == released) cp_async_wait<C::kStages - 1>(); else cp_async_wait<C::kStages - 2>();
+                __syncwarp();
+                landed = last_page + 1;
+            }
+            const int n = first + (slice_ok ? slot : 0);      // this lane's token in the warp's stream
+            const int page = min(n / P, warp_pages - 1), t = n % P;
+            const uint32_t k_anchor = ring_addr + (page % C::kStages) * C::kStageBytes;
+            const int position = (page_begin + warp + kWarps * page) * P + t;   // in the sequence
+            const bool step_full = first + kStepTokens <= total && (page_begin + warp + kWarps * last_page + 1) * P <= history;
+            if (step_full) process_token(std::false_type{}, k_anchor, t, true);
+            else process_token(std::true_type{}, k_anchor, t, slice_ok && n < total && position < history);
+            if ((step + 1) % 8 == 0) flush();
+            if (min((first + kStepTokens) / P, warp_pages) > released) {  // the oldest page is used up: refill its stage
+                __syncwarp();
+                if (issued < warp_pages) {
+                    if (issued - batch_base == 32) load_batch(issued);
+                    const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
+                    issue(block, released % C::kStages);
+                    ++issued;
+                }
+                cp_async_commit();
+                ++released;
+            }
+        }
+        if (!slice_ok) m = kNever;  // idle lanes saw real tokens through zero operands: keep them out of the fold
     }
     __syncwarp();
     failed = __any_sync(kFullMask, failed);
@@ -827,11 +894,20 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // ---- fold the 8 token slots of the warp ------------------------------------------------------------
     float m_warp = m;
+    if (kStream) {
+        m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 1));
+        m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 2));
+    }
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 4));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 8));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 16));
     const float f_slot = fast_exp2(m - m_warp);  // untouched streams carry zero sums, so their factor is irrelevant
-    float l_warp = l * f_slot;
+    // the denominator of a token slot is counted once: every lane of the slot holds a copy
+    float l_warp = kStream ? (slice_ok && j == 0 ? l * f_slot : 0.f) : l * f_slot;
+    if (kStream) {
+        l_warp += __shfl_xor_sync(kFullMask, l_warp, 1);
+        l_warp += __shfl_xor_sync(kFullMask, l_warp, 2);
+    }
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 4);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 8);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 16);
@@ -854,7 +930,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             const int c = 4 * lane + i, slice = c >> 5, local = c & 31;
             float sum = 0.f;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) sum += scratch[(4 * g + slice) * 33 + local];
+            for (int g = 0; g < kStepTokens; ++g) sum += scratch[((kStream ? 3 : 4) * g + slice) * 33 + local];
             warp_acc[warp * D + c] = sum;
         }
     }

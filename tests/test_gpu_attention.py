@@ -293,3 +293,18 @@ def test_adjacent_reference_mode(records, head_dim, page):
     cache = helpers.oracle_cache(case)
     for loop in range(4):
         _check(case, cache, loop, splits=3 if loop == 2 else 0)
+
+
+@pytest.mark.parametrize("fill", [0xFF, 0x7F, 0xA5])
+@pytest.mark.parametrize("head_dim,page,mode", [(128, 16, "anchor"), (96, 32, "anchor"), (128, 16, "adjacent"), (96, 16, "adjacent")])
+def test_unwritten_bytes_of_the_last_page_are_ignored(fill, head_dim, page, mode):
+    """Tokens beyond the history share the last page with real ones; their bytes were never written and may decode to
+    NaN (FP8 0x7F / 0xFF, bf16 0xFFFF) or huge values.  They must not reach the output."""
+    if mode == "anchor":
+        case = helpers.make_case(51, head_dim, 2, [45, 3, 130, 1], 32, page)
+    else:
+        case = helpers.make_case(52, head_dim, 2, [45, 3, 130, 1], page_tokens=page, anchor_index=0,
+                                 records=((4, 32), (2, 16), (2, 32), (2, 32)), reference_mode="adjacent")
+    cache = helpers.oracle_cache(case, fill=fill)
+    for loop in range(4):
+        _check(case, cache, loop, splits=2 if loop == 1 else 0)
