@@ -646,14 +646,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // The K side runs on integer dot products (dp2a: two s16 x u8 products per instruction) against a query slice
     // quantized once per CTA; see QueryOperands.
-    // head_dim 128: 4 lanes per token, 8 tokens per warp step, a page is P/8 steps.
-    // head_dim  96: 3 lanes per token, 10 tokens per warp step (lanes 30 and 31 idle); steps run over the warp's tokens
-    //               as one stream across page boundaries, so that no step is left partly filled ("streamed").
-    constexpr bool kStream = D == 96;
-    constexpr int kStepTokens = kStream ? 10 : 8;
-    static_assert(!(kStream && kBulkCopy), "the streamed token loop tracks pages by commit groups");
-    const int j = kStream ? lane % 3 : lane & 3;  // slice: channels 32j .. 32j+31
-    const bool slice_ok = kStream ? lane < 30 : 32 * j < D;
+    // 4 lanes per token, 8 tokens per warp step.  At head_dim 96 the fourth lane of a token has no slice: it runs along
+    // with zero operands.  (A 3-lanes-per-token variant that streams 10 tokens per step across page boundaries was
+    // measured at the same speed: what it saves in idle lanes it spends on per-step address arithmetic that the
+    // fixed token positions of this layout fold into immediate offsets.)
+    const int j = lane & 3;              // slice: channels 32j .. 32j+31
+    const bool slice_ok = 32 * j < D;
     const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
     const float qmax = misc[2];
     constexpr bool kUse4 = C::kAdjacent || C::AB == 4 || C::RB == 4, kUse2 = C::kAdjacent || C::AB == 2 || C::RB == 2;
@@ -694,9 +692,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     bool failed = false;
-    const int slot = kStream ? lane / 3 : lane >> 2;  // token slot inside a warp step
-    // streamed: the two other lanes of this lane's token (idle lanes point at themselves)
-    const int peer1 = slice_ok ? lane - j + (j + 1) % 3 : lane, peer2 = slice_ok ? lane - j + (j + 2) % 3 : lane;
+    const int slot = lane >> 2;          // token slot 0..7 inside a warp step
     float carry = 1.f;                   // factor the fp32 sums still have to be multiplied by (deferred rescale)
 
     // half2 partial sums -> fp32 sums, every 8 tokens of a lane
@@ -750,12 +746,8 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                 part = part * alpha +
                        score_record<C::RB, C::RG, P, D>(k_residual, t, js, operands(std::integral_constant<int, C::RB>{}));
             }
-            if constexpr (kStream) {
-                part += __shfl_sync(kFullMask, part, peer1) + __shfl_sync(kFullMask, part, peer2);
-            } else {
-                part += __shfl_xor_sync(kFullMask, part, 1);
-                part += __shfl_xor_sync(kFullMask, part, 2);
-            }
+            part += __shfl_xor_sync(kFullMask, part, 1);
+            part += __shfl_xor_sync(kFullMask, part, 2);
             const float score = live_token ? part : kNever;
 
             // ---------------- online softmax of the token slot ----------------
@@ -807,7 +799,6 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     int stage = 0;
     uint32_t parity = 0;
     int it_done = 0;  // pages fully consumed
-    if constexpr (!kStream) {
     for (int it = 0; it < warp_pages; ++it) {
         if (kBulkCopy) {
             if (!mbar_wait(bar_addr + 8 * stage, parity)) { failed = true; break; }
@@ -840,43 +831,6 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         if (++stage == C::kStages) { stage = 0; parity ^= 1u; }
         it_done = it + 1;
     }
-    } else {
-        // Streamed token loop.  Commit groups: kStages before the loop, one more per released page, so page q is group q
-        // and, with `released` pages handed back, at most kStages + released - 1 - q groups may still be pending when
-        // page q is needed.  A step touches at most two pages (kStepTokens < P) and `released` equals the first of them.
-        const int total = warp_pages * P;
-        const int steps = (total + kStepTokens - 1) / kStepTokens;
-        int released = 0, landed = 0;
-        for (int step = 0; step < steps; ++step) {
-            const int first = step * kStepTokens;
-            const int last_page = min((first + kStepTokens - 1) / P, warp_pages - 1);
-            if (last_page >= landed) {
-                if (last_page == released) cp_async_wait<C::kStages - 1>(); else cp_async_wait<C::kStages - 2>();
-                __syncwarp();
-                landed = last_page + 1;
-            }
-            const int n = first + (slice_ok ? slot : 0);      // this lane's token in the warp's stream
-            const int page = min(n / P, warp_pages - 1), t = n % P;
-            const uint32_t k_anchor = ring_addr + (page % C::kStages) * C::kStageBytes;
-            const int position = (page_begin + warp + kWarps * page) * P + t;   // in the sequence
-            const bool step_full = first + kStepTokens <= total && (page_begin + warp + kWarps * last_page + 1) * P <= history;
-            if (step_full) process_token(std::false_type{}, k_anchor, t, true);
-            else process_token(std::true_type{}, k_anchor, t, slice_ok && n < total && position < history);
-            if ((step + 1) % 8 == 0) flush();
-            if (min((first + kStepTokens) / P, warp_pages) > released) {  // the oldest page is used up: refill its stage
-                __syncwarp();
-                if (issued < warp_pages) {
-                    if (issued - batch_base == 32) load_batch(issued);
-                    const int block = __shfl_sync(kFullMask, my_block, issued - batch_base);
-                    issue(block, released % C::kStages);
-                    ++issued;
-                }
-                cp_async_commit();
-                ++released;
-            }
-        }
-        if (!slice_ok) m = kNever;  // idle lanes saw real tokens through zero operands: keep them out of the fold
-    }
     __syncwarp();
     failed = __any_sync(kFullMask, failed);
     if (failed) {
@@ -894,20 +848,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // ---- fold the 8 token slots of the warp ------------------------------------------------------------
     float m_warp = m;
-    if (kStream) {
-        m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 1));
-        m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 2));
-    }
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 4));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 8));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 16));
     const float f_slot = fast_exp2(m - m_warp);  // untouched streams carry zero sums, so their factor is irrelevant
-    // the denominator of a token slot is counted once: every lane of the slot holds a copy
-    float l_warp = kStream ? (slice_ok && j == 0 ? l * f_slot : 0.f) : l * f_slot;
-    if (kStream) {
-        l_warp += __shfl_xor_sync(kFullMask, l_warp, 1);
-        l_warp += __shfl_xor_sync(kFullMask, l_warp, 2);
-    }
+    float l_warp = l * f_slot;
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 4);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 8);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 16);
@@ -930,7 +875,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             const int c = 4 * lane + i, slice = c >> 5, local = c & 31;
             float sum = 0.f;
 #pragma unroll
-            for (int g = 0; g < kStepTokens; ++g) sum += scratch[((kStream ? 3 : 4) * g + slice) * 33 + local];
+            for (int g = 0; g < 8; ++g) sum += scratch[(4 * g + slice) * 33 + local];
             warp_acc[warp * D + c] = sum;
         }
     }

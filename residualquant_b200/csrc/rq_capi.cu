@@ -215,18 +215,31 @@ int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32
         }
         if (sm_count_cache[device] > 0) sms = sm_count_cache[device];
     }
-    // Measured on B200 (batch 1..64, context 8192): the step is fastest with about seven CTAs per SM in the whole
-    // grid (1.75 resident waves at 4 CTAs/SM), a power-of-two partition count, and at least 32 pages per partition;
-    // every extra partition costs a prologue (query rotation, first page fetch) and a merge.
+    // Cost model fitted to measurements on B200 (batch 1..64 x 16 heads and 16 x 55 heads, contexts 2k..8k).  A CTA
+    // costs its pages plus a fixed overhead worth about 16 pages (prologue, first fetch, merge).  Four CTAs fit on an
+    // SM; the grid runs as full waves of 4 per SM plus a tail wave of c = ceil(rest / SMs) per SM, and an SM holding c
+    // CTAs delivers 0.45 / 0.85 / 0.92 / 1 of its throughput for c = 1..4 (the kernel is bound by instruction issue, so
+    // a tail wave that leaves SMs half empty is what hurts).  Partition counts are powers of two with at least four
+    // pages (one per warp) each; ties go to fewer partitions.
     const int64_t base = static_cast<int64_t>(num_query_rows) * heads;
-    int64_t want = (7LL * sms) / base;
-    const int64_t by_length = max_blocks_per_request > 0 ? max_blocks_per_request / 32 : 1;
-    if (want > by_length) want = by_length;
-    if (want > 64) want = 64;
-    if (want < 1) want = 1;
-    while (want & (want - 1)) want &= want - 1;  // largest power of two not above
+    const int64_t pages = max_blocks_per_request > 0 ? max_blocks_per_request : 1;
+    const double tail_cost[5] = {0.0, 1.0 / 0.45, 2.0 / 0.85, 3.0 / 0.92, 4.0};
+    int32_t best = 1;
+    double best_cost = 0.0;
+    for (int32_t candidate = 1; candidate <= 64 && (candidate == 1 || candidate * 4 <= pages); candidate *= 2) {
+        const int64_t ctas = base * candidate;
+        const int64_t full_waves = ctas / (4LL * sms);
+        const int64_t rest = ctas - full_waves * 4LL * sms;
+        const int64_t per_sm = (rest + sms - 1) / sms;
+        const double waves = 4.0 * static_cast<double>(full_waves) + tail_cost[per_sm];
+        const double cost = waves * (static_cast<double>(pages) / candidate + 16.0);
+        if (candidate == 1 || cost < best_cost * 0.99) {
+            best = candidate;
+            best_cost = cost;
+        }
+    }
     (void)page_tokens;
-    return static_cast<int32_t>(want);
+    return best;
 }
 
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits) {
