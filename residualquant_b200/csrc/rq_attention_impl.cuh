@@ -110,13 +110,14 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-// Copy `BYTES` (a multiple of 16) with the whole warp: lane l moves chunks l, l+32, ...
+// Copy `BYTES` (a multiple of 16) with the whole warp: lane l moves chunks l, l+32, ...  `dst` and `src` already
+// point at the lane's first chunk, so every copy differs from them by a compile-time constant only.
 template <int BYTES>
 __device__ __forceinline__ void warp_copy(uint32_t dst, const uint8_t* src, int lane) {
     constexpr int kChunks = BYTES / 16;
 #pragma unroll
     for (int i = 0; i < (kChunks + 31) / 32; ++i) {
-        if (32 * (i + 1) <= kChunks || lane + 32 * i < kChunks) cp_async16(dst + 16 * lane + 512 * i, src + 16 * lane + 512 * i);
+        if (32 * (i + 1) <= kChunks || lane + 32 * i < kChunks) cp_async16(dst + 512 * i, src + 512 * i);
     }
 }
 // Same with a run-time size.
@@ -201,6 +202,12 @@ __device__ __forceinline__ uint32_t hmul2_raw(uint32_t a, uint32_t b) {
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
+// lo += low half of `pair`, hi += high half: mixed-precision adds (fp32 accumulator, fp16 addend), one instruction each.
+__device__ __forceinline__ void add_half2_to_floats(uint32_t pair, float& lo, float& hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tadd.rn.f32.f16 %0, l, %0;\n\tadd.rn.f32.f16 %1, h, %1;\n\t}"
+        : "+f"(lo), "+f"(hi)
+        : "r"(pair));
+}
 __device__ __forceinline__ uint32_t half2_from(float v) {  // (v, v), saturating to the largest finite half
     uint32_t d;
     asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %1;" : "=r"(d) : "f"(v));
@@ -211,7 +218,10 @@ __device__ __forceinline__ uint32_t half2_from(float v) {  // (v, v), saturating
 // goes into the weight.  weight * 2^11 stays a finite half for |weight| < 32 (it saturates beyond: a V group would
 // need a range above ~240 for that); the half2 sums then carry a factor 2^-13: 11-bit relative precision for sums
 // above 0.5, 2^-11 absolute below.
-constexpr float kWeightUp = 2048.f;
+// The factor 2^11 rides on the probabilities themselves (the softmax exponent is biased by kWeightBits), so the
+// denominator and the offset sums carry it too and drop it once per warp at the end.
+constexpr float kWeightBits = 11.f;
+constexpr float kWeightDown = 1.f / 2048.f;
 constexpr float kSumDown = 8192.f;
 
 // ---- one packed record (codes + FP8 group parameters) against a 32-channel slice ------------------------------
@@ -279,7 +289,7 @@ __device__ __forceinline__ void load_parameters(uint32_t base, int t, int js, fl
     using R = StagedRecord<BITS, GROUP, P, D>;
     const uint32_t meta = base + P * R::kCode + t * R::kGroups;
     if (GROUP == 32) {
-        const float2 so = fp8x2_to_float2(lds8(meta + js) | (lds8(meta + P * R::kGroups + js) << 8));
+        const float2 so = fp8x2_to_float2(prmt(lds8(meta + js), lds8(meta + P * R::kGroups + js), 0x0040u));
         scales = make_float2(so.x, so.x);
         offsets = make_float2(so.y, so.y);
     } else {
@@ -357,7 +367,7 @@ __device__ __forceinline__ void accumulate_record(uint32_t base, int t, int js, 
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             if (w == 0 || (w == 2 && GROUP == 16)) {
-                w_low = half2_from(weight * (w == 0 ? scales.x : scales.y) * kWeightUp);
+                w_low = half2_from(weight * (w == 0 ? scales.x : scales.y));
                 w_high = hmul2_raw(w_low, 0x2C002C00u);  // w/16, exact
             }
             const uint32_t upper = words[w] >> 8;
@@ -374,7 +384,7 @@ __device__ __forceinline__ void accumulate_record(uint32_t base, int t, int js, 
 #pragma unroll
         for (int v = 0; v < 2; ++v) {
             if (v == 0 || GROUP == 16) {
-                wk[0] = half2_from(weight * (v == 0 ? scales.x : scales.y) * kWeightUp);
+                wk[0] = half2_from(weight * (v == 0 ? scales.x : scales.y));
                 wk[1] = hmul2_raw(wk[0], quarter);  // exact: powers of two
                 wk[2] = hmul2_raw(wk[0], sixteenth);
                 wk[3] = hmul2_raw(wk[0], sixtyfourth);
@@ -585,6 +595,8 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     const uint8_t* head_base = p.cache + head * page_bytes;
     const int64_t block_bytes = heads * page_bytes;
     const int anchor_at = P * p.anchor_offset, residual_at = P * p.residual_offset;
+    const uint32_t lane_anchor_at = anchor_at + 16 * lane, lane_residual_at = residual_at + 16 * lane;
+    const uint32_t lane_ring = ring_addr + 16 * lane;
     auto issue = [&](int block, int stage) {
         const uint8_t* k_page = head_base + block * block_bytes;
         const uint8_t* v_page = k_page + p.plane_stride;
@@ -605,11 +617,16 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                     bulk_load(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, C::kResidualBytes, bar);
             }
         } else {
-            warp_copy<C::kAnchorBytes>(dst, k_page + anchor_at, lane);
-            if (C::kResidual) warp_copy<C::kResidualBytes>(dst + C::kAnchorBytes, k_page + residual_at, lane);
-            warp_copy<C::kAnchorBytes>(dst + C::kPlaneBytes, v_page + anchor_at, lane);
-            if (C::kResidual)
-                warp_copy<C::kResidualBytes>(dst + C::kPlaneBytes + C::kAnchorBytes, v_page + residual_at, lane);
+            // two source pointers per plane (the lane's first chunk of each region), everything else is an immediate
+            const uint32_t to = lane_ring + stage * C::kStageBytes;
+            const uint8_t* k_from = k_page + lane_anchor_at;
+            warp_copy<C::kAnchorBytes>(to, k_from, lane);
+            warp_copy<C::kAnchorBytes>(to + C::kPlaneBytes, k_from + p.plane_stride, lane);
+            if (C::kResidual) {
+                const uint8_t* r_from = k_page + lane_residual_at;
+                warp_copy<C::kResidualBytes>(to + C::kAnchorBytes, r_from, lane);
+                warp_copy<C::kResidualBytes>(to + C::kPlaneBytes + C::kAnchorBytes, r_from + p.plane_stride, lane);
+            }
         }
     };
     // block ids of this warp's next 32 pages, one per lane
@@ -682,7 +699,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
 
     // ---- page loop -----------------------------------------------------------------------------------
-    float m = kNever, l = 0.f;        // online-softmax state of this lane's token slot (base-2 logits)
+    float m_biased = kNever, l = 0.f;  // online-softmax state of this lane's token slot (base-2 logits), see below
     uint32_t acc_b[16];                  // half2 partial sums of V, pair 4b+i = (channel 8b+i, channel 8b+i+4)
     float acc[32];
     constexpr bool kTwoOffsets = C::kAdjacent || C::AG == 16 || (C::kResidual && C::RG == 16);  // a record with two groups per slice
@@ -704,9 +721,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float2 f = __half22float2(as_half2(acc_b[i]));
-            acc[2 * i] += f.x;
-            acc[2 * i + 1] += f.y;
+            add_half2_to_floats(acc_b[i], acc[2 * i], acc[2 * i + 1]);
             acc_b[i] = 0u;
         }
     };
@@ -753,8 +768,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             // ---------------- online softmax of the token slot ----------------
             // `m` is the stream's reference exponent, not its exact maximum: it only moves when a score exceeds it
             // by more than kSlack, so probabilities stay below 2^kSlack and rescaling is rare.
-            if (score > m + kSlack) {
-                const float f = fast_exp2(m - score);  // m == -inf gives 0
+            // Inside the loop the exponent is kept as m - kWeightBits, so that exp2(score - m_biased) is the probability
+            // already multiplied by 2^kWeightBits, the form the value weights need.
+            // The rare rescale is taken by the whole warp (lanes that need none multiply by one): no divergence.
+            const bool raise = score > m_biased + (kSlack + kWeightBits);
+            if (__any_sync(kFullMask, raise)) {
+                const float f = raise ? fast_exp2(m_biased + kWeightBits - score) : 1.f;  // a stream without tokens gives 0
                 l *= f;
                 acc_off0 *= f;
                 if (kTwoOffsets) acc_off1 *= f;
@@ -762,9 +781,9 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                 const uint32_t f2 = half2_from(f);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc_b[i] = hmul2_raw(acc_b[i], f2);
-                m = score;
+                if (raise) m_biased = score - kWeightBits;
             }
-            const float prob = live_token ? fast_exp2(score - m) : 0.f;
+            const float prob = live_token ? fast_exp2(score - m_biased) : 0.f;
             l += prob;
 
             // ---------------- V: accumulate prob * V_hat[t] over the slice ----------------
@@ -847,12 +866,13 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     flush();
 
     // ---- fold the 8 token slots of the warp ------------------------------------------------------------
+    const float m = m_biased + kWeightBits;  // kNever stays kNever
     float m_warp = m;
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 4));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 8));
     m_warp = fmaxf(m_warp, __shfl_xor_sync(kFullMask, m_warp, 16));
     const float f_slot = fast_exp2(m - m_warp);  // untouched streams carry zero sums, so their factor is irrelevant
-    float l_warp = l * f_slot;
+    float l_warp = l * kWeightDown * f_slot;
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 4);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 8);
     l_warp += __shfl_xor_sync(kFullMask, l_warp, 16);
@@ -864,7 +884,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             const int pair = e >> 1, b = pair >> 2, i = pair & 3;
             const int local = 8 * b + i + 4 * (e & 1);  // channel inside the slice
             const float off = (kTwoOffsets && local >= 16) ? acc_off1 : acc_off0;
-            scratch[local] = (acc[e] * kSumDown + off) * f_slot;
+            scratch[local] = (acc[e] * kSumDown + off * kWeightDown) * f_slot;
         }
     }
     __syncwarp();
