@@ -728,12 +728,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // One token of the lane's slot: score against the query slice, online softmax, value accumulation.
     // `k_anchor` = shared address of the staged page (stage) the token lives in, `t` = its index inside the page.
-    auto process_token = [&](auto partial_tag, uint32_t k_anchor, int t, bool live_token) {
-        constexpr bool kPartial = decltype(partial_tag)::value;
+    [[maybe_unused]] constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
+    // The scores of a page's token steps do not depend on the softmax state, so they are all computed first: the
+    // integer dot products of the next step overlap the dependent softmax/value chain of the previous one.
+    auto score_token = [&](uint32_t k_anchor, int t, bool live_token) -> float {
         [[maybe_unused]] const uint32_t k_residual = k_anchor + C::kAnchorBytes;
-        const uint32_t v_anchor = k_anchor + (C::kAdjacent ? C::kMaxPrefixBytes : C::kPlaneBytes);
-        [[maybe_unused]] const uint32_t v_residual = v_anchor + C::kAnchorBytes;
-        [[maybe_unused]] constexpr int kResidualAlphaAt = P * (C::kResidualCode + 2 * C::kResidualGroups);
         {
             // ---------------- K: score of token t against the query slice (integer dot products) ----------------
             float part = 0.f;
@@ -763,8 +762,14 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             }
             part += __shfl_xor_sync(kFullMask, part, 1);
             part += __shfl_xor_sync(kFullMask, part, 2);
-            const float score = live_token ? part : kNever;
-
+            return live_token ? part : kNever;
+        }
+    };
+    auto absorb_token = [&](auto partial_tag, uint32_t k_anchor, int t, bool live_token, float score) {
+        constexpr bool kPartial = decltype(partial_tag)::value;
+        const uint32_t v_anchor = k_anchor + (C::kAdjacent ? C::kMaxPrefixBytes : C::kPlaneBytes);
+        [[maybe_unused]] const uint32_t v_residual = v_anchor + C::kAnchorBytes;
+        {
             // ---------------- online softmax of the token slot ----------------
             // `m` is the stream's reference exponent, not its exact maximum: it only moves when a score exceeds it
             // by more than kSlack, so probabilities stay below 2^kSlack and rescaling is rare.
@@ -830,12 +835,18 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         const int valid = history - first_token;  // >= P for every page but the last one of the history
 
         // Full pages run without any per-token predicate; only the last page of a sequence can be partial.
+        float scores[P / 8];
         if (valid >= P) {
 #pragma unroll
-            for (int sub = 0; sub < P / 8; ++sub) process_token(std::false_type{}, k_anchor, sub * 8 + slot, true);
+            for (int sub = 0; sub < P / 8; ++sub) scores[sub] = score_token(k_anchor, sub * 8 + slot, true);
+#pragma unroll
+            for (int sub = 0; sub < P / 8; ++sub) absorb_token(std::false_type{}, k_anchor, sub * 8 + slot, true, scores[sub]);
         } else {
 #pragma unroll
-            for (int sub = 0; sub < P / 8; ++sub) process_token(std::true_type{}, k_anchor, sub * 8 + slot, sub * 8 + slot < valid);
+            for (int sub = 0; sub < P / 8; ++sub) scores[sub] = score_token(k_anchor, sub * 8 + slot, sub * 8 + slot < valid);
+#pragma unroll
+            for (int sub = 0; sub < P / 8; ++sub)
+                absorb_token(std::true_type{}, k_anchor, sub * 8 + slot, sub * 8 + slot < valid, scores[sub]);
         }
 
         if ((it + 1) % kFlushPages == 0) flush();
