@@ -173,8 +173,31 @@ __device__ __forceinline__ float bf16_add(float a, float b) {
 }
 __device__ __forceinline__ float bf16_round(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
 
-template <int D>
+// What the kernel knows at compile time about the group's records.  The general kernel reads everything from its
+// parameters; the headline schedule (three INT2 residual loops predicted from an INT4 g32 anchor in the last loop, least
+// squares coefficient, kernel chain) is also compiled with these values as constants, which unrolls the record loop
+// and drops every other chain's code.  Same arithmetic, same packed bytes.
+struct AnySchedule {
+    static constexpr bool kFixed = false;
+};
+template <int RESIDUAL_GROUP>
+struct Anchor2224 {
+    static constexpr bool kFixed = true;
+    static constexpr int kRecords = 4, kAnchor = 3, kResidualGroup = RESIDUAL_GROUP;
+};
+
+template <int D, class S>
 __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant__ QuantizeParams p) {
+    // run-time values, or the schedule's constants
+    const int num_records = [&] { if constexpr (S::kFixed) return S::kRecords; else return p.num_records; }();
+    const int anchor = [&] { if constexpr (S::kFixed) return S::kAnchor; else return p.anchor; }();
+    const int chain = S::kFixed ? static_cast<int>(RQ_CHAIN_KERNEL) : p.chain;
+    const int coefficient_kind = S::kFixed ? static_cast<int>(RQ_COEFF_LS) : p.coefficient;
+    const int mode = S::kFixed ? static_cast<int>(RQ_REFERENCE_ANCHOR) : p.mode;
+    auto record_bits = [&](int r) { if constexpr (S::kFixed) return r == S::kAnchor ? 4 : 2; else return p.bits[r]; };
+    auto record_group = [&](int r) {
+        if constexpr (S::kFixed) return r == S::kAnchor ? 32 : S::kResidualGroup; else return p.group[r];
+    };
     constexpr int kSlices = D / 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = lane & 7;
@@ -265,7 +288,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
     // Quantize z (already centered) as record r, store it, return the codes and parameters.
     auto commit_as = [&](auto bits_tag, int r, const float (&z)[16], uint16_t alpha_bits) -> GroupCode {
         constexpr int kBits = decltype(bits_tag)::value;
-        const int group = p.group[r];
+        const int group = record_group(r);
         const GroupCode q = group_quantize<kBits>(z, group);
         if (active) {
             constexpr int kCodeBytes = D * kBits / 8;
@@ -292,26 +315,25 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         return q;
     };
     auto commit = [&](int r, const float (&z)[16], uint16_t alpha_bits) -> GroupCode {
-        if (p.bits[r] == 2) return commit_as(std::integral_constant<int, 2>{}, r, z, alpha_bits);
+        if (record_bits(r) == 2) return commit_as(std::integral_constant<int, 2>{}, r, z, alpha_bits);
         return commit_as(std::integral_constant<int, 4>{}, r, z, alpha_bits);
     };
     // den = row_dot(ref, ref) is passed in: in anchor mode every residual record divides by the same sum.
     auto coefficient = [&](const float (&x)[16], const float (&ref)[16], float den) -> float {
-        if (p.coefficient == RQ_COEFF_UNIT) return 1.f;
-        if (p.coefficient == RQ_COEFF_NORM) {
+        if (coefficient_kind == RQ_COEFF_UNIT) return 1.f;
+        if (coefficient_kind == RQ_COEFF_NORM) {
             const float num = row_dot(x, x);
             return den > 0.f ? __fdiv_rn(__fsqrt_rn(num), fmaxf(__fsqrt_rn(den), 1e-6f)) : 0.f;
         }
         return __fdiv_rn(row_dot(x, ref), fmaxf(den, 1e-12f));
     };
     // records in processing order: the anchor, then the others in loop order
-    const int anchor = p.anchor;
     auto record_at = [&](int k) { return k == 0 ? anchor : (k - 1 < anchor ? k - 1 : k); };
 
     uint32_t words[8], ahead[8];
     if (packed_rows) {
         fetch_packed(anchor, words);
-        if (p.num_records > 1) fetch_packed(record_at(1), ahead);
+        if (num_records > 1) fetch_packed(record_at(1), ahead);
     }
 
     float ref[16];  // bf16-valued reconstruction that residuals predict from
@@ -326,7 +348,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         }
         const GroupCode q = commit(anchor, y, 0x3F80u);
         const float scale = fp8_decode(q.scale8), offset = fp8_decode(q.offset8);
-        if (p.chain == RQ_CHAIN_KERNEL) {
+        if (chain == RQ_CHAIN_KERNEL) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 ref[i] = restore_bf16(q.magic[i], scale, offset);
@@ -345,21 +367,22 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         }
     }
     float den = 0.f;
-    if (p.coefficient != RQ_COEFF_UNIT && p.num_records > 1) den = row_dot(ref, ref);
+    if (coefficient_kind != RQ_COEFF_UNIT && num_records > 1) den = row_dot(ref, ref);
 
-    for (int k = 1; k < p.num_records; ++k) {
+#pragma unroll(S::kFixed ? 4 : 1)
+    for (int k = 1; k < num_records; ++k) {
         const int r = record_at(k);
         float y[16], mean[16];
         if (packed_rows) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) words[i] = ahead[i];
-            if (k + 1 < p.num_records) fetch_packed(record_at(k + 1), ahead);
-            unpack(words, y, p.chain == RQ_CHAIN_KERNEL);
+            if (k + 1 < num_records) fetch_packed(record_at(k + 1), ahead);
+            unpack(words, y, chain == RQ_CHAIN_KERNEL);
         } else {
-            load_unpacked(r, y, p.chain == RQ_CHAIN_KERNEL);
+            load_unpacked(r, y, chain == RQ_CHAIN_KERNEL);
         }
         uint16_t alpha_bits;
-        if (p.chain == RQ_CHAIN_KERNEL) {
+        if (chain == RQ_CHAIN_KERNEL) {
             if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
             const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref, den));
             alpha_bits = __bfloat16_as_ushort(stored);
@@ -384,7 +407,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
             for (int i = 0; i < 16; ++i) y[i] = __fsub_rn(y[i], mean[i]);
         }
         const GroupCode q = commit(r, y, alpha_bits);
-        if (p.mode == RQ_REFERENCE_ADJACENT) {
+        if (mode == RQ_REFERENCE_ADJACENT) {
             // the next record predicts from this record's reconstruction (reference: kernel.cuh:195-201)
             const float scale = fp8_decode(q.scale8), offset = fp8_decode(q.offset8);
             const __nv_bfloat16 alpha_bf = __ushort_as_bfloat16(alpha_bits);
@@ -395,7 +418,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
                 ref[i] = __bfloat162float(
                     __hfma(__float2bfloat16_rn(ref[i]), alpha_bf, __float2bfloat16_rn(restored)));
             }
-            if (p.coefficient != RQ_COEFF_UNIT && k + 1 < p.num_records) den = row_dot(ref, ref);
+            if (coefficient_kind != RQ_COEFF_UNIT && k + 1 < num_records) den = row_dot(ref, ref);
         }
     }
 }
@@ -404,10 +427,21 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
 
 cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream) {
     const dim3 grid((p.num_tokens + 15) / 16, p.heads, 2);
-    if (head_dim == 128)
-        quantize_kernel<128><<<grid, 128, 0, stream>>>(p);
-    else
-        quantize_kernel<96><<<grid, 128, 0, stream>>>(p);
+    const bool headline = p.num_records == 4 && p.anchor == 3 && p.mode == RQ_REFERENCE_ANCHOR &&
+                          p.coefficient == RQ_COEFF_LS && p.chain == RQ_CHAIN_KERNEL && p.bits[3] == 4 && p.group[3] == 32 &&
+                          p.bits[0] == 2 && p.bits[1] == 2 && p.bits[2] == 2 && p.group[0] == p.group[1] &&
+                          p.group[1] == p.group[2];
+    if (headline && p.group[0] == 32) {
+        if (head_dim == 128) quantize_kernel<128, Anchor2224<32>><<<grid, 128, 0, stream>>>(p);
+        else quantize_kernel<96, Anchor2224<32>><<<grid, 128, 0, stream>>>(p);
+    } else if (headline && p.group[0] == 16) {
+        if (head_dim == 128) quantize_kernel<128, Anchor2224<16>><<<grid, 128, 0, stream>>>(p);
+        else quantize_kernel<96, Anchor2224<16>><<<grid, 128, 0, stream>>>(p);
+    } else if (head_dim == 128) {
+        quantize_kernel<128, AnySchedule><<<grid, 128, 0, stream>>>(p);
+    } else {
+        quantize_kernel<96, AnySchedule><<<grid, 128, 0, stream>>>(p);
+    }
     return cudaGetLastError();
 }
 
