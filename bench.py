@@ -603,7 +603,7 @@ def run_gpu(args):
     if bf16 is not None:
         line["bf16_kv_comparator"] = bf16
     if not args.no_cpu_baseline:
-        cpu_value, description, _ = cpu_sample(L, args.group, layers, B)
+        cpu_value, description, _ = cpu_sample(L, args.group, layers, B, sample_context=min(L, 4096))  # 5-20 s of CPU work
         line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port", "sample": description}
     print(json.dumps(line))
     if world > 1:
