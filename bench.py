@@ -185,7 +185,7 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def workload_config(args):
@@ -605,15 +605,33 @@ def run_gpu(args):
     if not args.no_cpu_baseline:
         cpu_value, description, _ = cpu_sample(L, args.group, layers, B, sample_context=min(L, 4096))  # 5-20 s of CPU work
         line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port", "sample": description}
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_result_stream = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line of the run, on the process's real standard output."""
+    text = json.dumps(line) + "\n"
+    if _result_stream is not None:
+        os.write(_result_stream, text.encode())
+    else:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+
+
 def main():
-    global HEADS, HEAD_DIM, PAGE
+    global HEADS, HEAD_DIM, PAGE, _result_stream
     args = parse_args()
     HEADS, HEAD_DIM, PAGE = args.heads, args.head_dim, args.page
+    # Libraries print to file descriptor 1 on their own (NCCL announces its version there): keep the real standard
+    # output for the result line and send everything else to standard error.
+    sys.stdout.flush()
+    _result_stream = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
