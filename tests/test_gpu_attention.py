@@ -308,3 +308,17 @@ def test_unwritten_bytes_of_the_last_page_are_ignored(fill, head_dim, page, mode
     cache = helpers.oracle_cache(case, fill=fill)
     for loop in range(4):
         _check(case, cache, loop, splits=2 if loop == 1 else 0)
+
+
+@pytest.mark.parametrize("sharpness", [3.0, 8.0])
+def test_sharp_queries(sharpness):
+    """Queries with a large norm: the softmax concentrates on a few tokens and the score range grows."""
+    import dataclasses
+
+    case = helpers.make_case(53, 128, 2, [600, 90], 32, 16)
+    query = (case.query.astype(np.float32) * sharpness)
+    from residualquant_b200 import synth
+    case = dataclasses.replace(case, query=synth.to_bf16_f32(query))
+    cache = helpers.oracle_cache(case)
+    for loop in range(4):
+        _check(case, cache, loop, splits=2 if loop == 0 else 0)
