@@ -3,13 +3,18 @@
 `DeferredKVGroup` follows plugins/residual_quantization/src/residual_quantization/install_model.py:17-52: the K/V of
 the loops of a KV group are held back (cloned) until the group's last loop arrives, then all records go to
 `quantize` in one call.  `PackedDecodeAttention` follows the decode path of `PackedImpl.forward` and `_store_kv`
-(packed_backend.py:28-137): attention over the packed cache plus the live token, then stage/quantize.  Neither
-touches vLLM; a vLLM attention backend only has to forward its `forward(...)` arguments here.
+(packed_backend.py:28-137): attention over the packed cache plus the live token, then stage/quantize.
+`batch_slices` follows the metadata builder's split of a reordered batch into its decode prefix and its
+full-prompt suffix (`PackedBuilder.build`, packed_backend.py:153-199), and `PackedAttention` runs both parts: decode
+rows through the packed kernel, full prompts through a caller-supplied prefill attention (the reference calls
+flash-attn there, outside the two hot paths), then stages and quantizes the new K/V of the whole batch.  Nothing here
+touches vLLM; a vLLM attention backend only has to forward its `forward(...)` arguments.
 """
 
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -81,6 +86,96 @@ class PackedDecodeAttention:
         _cuda.attention(query, key, value, kv_cache, output, query_start_loc, seq_lens, block_table,
                         self.key_rotation, self.value_rotation, self.key_mean, records, group.reference_mode,
                         group.anchor_index, self.group_loop_index)
+        actual = slot_mapping.numel()
+        staged = group.stage(key[:actual], value[:actual])
+        if staged is not None:
+            _cuda.quantize(staged, kv_cache, slot_mapping, self.key_rotation, self.value_rotation, self.key_mean,
+                           records, group.reference_mode, group.anchor_index, group.coefficient_method)
+        return output
+
+
+@dataclass(frozen=True)
+class BatchSlice:
+    """A run of requests of one kind inside a batch whose one-token requests come first."""
+
+    first_request: int
+    last_request: int     # exclusive
+    first_token: int
+    last_token: int       # exclusive
+    decode: bool          # True: one query token per request; False: full prompts
+
+
+def batch_slices(query_start_loc: Sequence[int], seq_lens: Sequence[int]) -> List[BatchSlice]:
+    """Split a batch into its decode prefix and its full-prompt suffix.
+
+    query_start_loc: host copy of the cumulative query lengths [requests + 1]; seq_lens: host copy [requests].
+    The caller (vLLM's model runner with `reorder_batch_threshold = 1`) has put the one-token requests first.
+    A request with more than one query token must be a whole prompt (query length == sequence length): chunked or
+    recomputed partial prefill is rejected, as in the reference (packed_backend.py:175-178).
+    """
+    starts = [int(v) for v in query_start_loc]
+    requests = len(starts) - 1
+    if requests < 0 or len(seq_lens) < requests:
+        raise ValueError("query_start_loc needs one entry per request plus the final boundary")
+    first_prompt = None
+    for request in range(requests):
+        length = starts[request + 1] - starts[request]
+        if length > 1:
+            if length != int(seq_lens[request]):
+                raise ValueError("Chunked/recomputed partial prefill is unsupported")
+            if first_prompt is None:
+                first_prompt = request
+        elif first_prompt is not None and length == 1:
+            raise ValueError("one-token requests must precede the prompts (reorder the batch)")
+    if first_prompt is None:
+        return [BatchSlice(0, requests, 0, starts[-1], True)] if requests else []
+    slices = []
+    if first_prompt > 0:
+        slices.append(BatchSlice(0, first_prompt, 0, starts[first_prompt], True))
+    slices.append(BatchSlice(first_prompt, requests, starts[first_prompt], starts[-1], False))
+    return slices
+
+
+def causal_prefill(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, output: torch.Tensor,
+                   query_start_loc: Sequence[int]) -> None:
+    """Full-prompt causal attention over the raw bf16 K/V of each prompt (plain PyTorch; any varlen attention kernel
+    with the same contract can be passed to `PackedAttention` instead)."""
+    starts = [int(v) for v in query_start_loc]
+    for begin, end in zip(starts, starts[1:]):
+        q = query[begin:end].transpose(0, 1).unsqueeze(0)
+        k = key[begin:end].transpose(0, 1).unsqueeze(0)
+        v = value[begin:end].transpose(0, 1).unsqueeze(0)
+        out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+        output[begin:end].copy_(out.squeeze(0).transpose(0, 1))
+
+
+class PackedAttention(PackedDecodeAttention):
+    """Decode and full-prompt requests of one batch, then the KV write of the whole batch."""
+
+    def __init__(self, *args, prefill: Callable = causal_prefill, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.prefill = prefill
+
+    def forward_batch(self, query, key, value, kv_cache, query_start_loc, seq_lens, block_table, slot_mapping, output,
+                      query_start_loc_host: Sequence[int], seq_lens_host: Sequence[int]):
+        """Device tensors as in `forward`; the host copies drive the split (the decode-only case needs none of their
+        values beyond the request count, so graph replays may pass stale ones of the right length)."""
+        if output is None:
+            raise ValueError("BF16 output required")
+        group = self.packed_group
+        records = [list(r) for r in group.records]
+        for part in batch_slices(query_start_loc_host, seq_lens_host):
+            tokens = slice(part.first_token, part.last_token)
+            if part.decode:
+                rows = slice(part.first_request, part.last_request)
+                starts = query_start_loc[part.first_request:part.last_request + 1]
+                _cuda.attention(query[tokens], key[tokens], value[tokens], kv_cache, output[tokens], starts.contiguous(),
+                                seq_lens[rows].contiguous(), block_table[rows], self.key_rotation, self.value_rotation,
+                                self.key_mean, records, group.reference_mode, group.anchor_index, self.group_loop_index)
+            else:
+                base = int(query_start_loc_host[part.first_request])
+                local = [int(v) - base for v in query_start_loc_host[part.first_request:part.last_request + 1]]
+                self.prefill(query[tokens], key[tokens], value[tokens], output[tokens], local)
         actual = slot_mapping.numel()
         staged = group.stage(key[:actual], value[:actual])
         if staged is not None:

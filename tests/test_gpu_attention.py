@@ -322,3 +322,63 @@ def test_sharp_queries(sharpness):
     cache = helpers.oracle_cache(case)
     for loop in range(4):
         _check(case, cache, loop, splits=2 if loop == 0 else 0)
+
+
+def test_mixed_batch_of_decodes_and_a_full_prompt():
+    """Two decode requests followed by a 21-token prompt in one batch (the reordered batch of the reference's metadata
+    builder, packed_backend.py:153-199): decode rows go through the packed kernel, the prompt through the prefill
+    attention, and the group's quantize writes the new K/V of all 23 tokens."""
+    from oracle import rq_oracle as O
+    from residualquant_b200 import synth
+    from residualquant_b200.group import DeferredKVGroup, PackedAttention
+
+    case = helpers.make_case(45, 128, 4, [150, 47], 32, 16)
+    L = case.layout
+    kr, vr = G.device_rotations(case)
+    group = DeferredKVGroup(L.records, L.page_tokens)
+    slots = [PackedAttention(group, i, kr, vr) for i in range(4)]
+    # room for the prompt: three fresh blocks after the case's own
+    prompt = 21
+    extra = 3
+    cache_np = np.concatenate([helpers.oracle_cache(case),
+                               np.zeros((2, extra) + helpers.oracle_cache(case).shape[2:], np.uint8)], axis=1)
+    cache = torch.from_numpy(cache_np).cuda()
+    first_new = case.num_blocks
+    table_np = np.zeros((3, case.block_table.shape[1]), np.int32)
+    table_np[:2] = case.block_table
+    table_np[2, :extra] = np.arange(first_new, first_new + extra)
+    table = torch.from_numpy(table_np).cuda()
+    seq_np = np.array([case.seq_lens[0], case.seq_lens[1], prompt], np.int32)
+    starts_np = np.array([0, 1, 2, 2 + prompt], np.int32)
+    live = [int(case.block_table[i, (case.seq_lens[i] - 1) // 16]) * 16 + (case.seq_lens[i] - 1) % 16 for i in range(2)]
+    prompt_slots = [int(table_np[2, t // 16]) * 16 + t % 16 for t in range(prompt)]
+    slot_mapping = torch.tensor(live + prompt_slots, dtype=torch.int64, device="cuda")
+
+    rng = np.random.default_rng(9)
+    prompt_q = synth.to_bf16_f32(rng.standard_normal((prompt, 4, 128)).astype(np.float32))
+    prompt_k = [synth.to_bf16_f32(rng.standard_normal((prompt, 4, 128)).astype(np.float32)) for _ in range(4)]
+    prompt_v = [synth.to_bf16_f32(rng.standard_normal((prompt, 4, 128)).astype(np.float32)) for _ in range(4)]
+    q = torch.cat([G.bf16(case.query), G.bf16(prompt_q)])
+    all_k, all_v = [], []
+    for loop in range(4):
+        k = torch.cat([G.bf16(case.keys[loop][case.live_rows]), G.bf16(prompt_k[loop])])
+        v = torch.cat([G.bf16(case.values[loop][case.live_rows]), G.bf16(prompt_v[loop])])
+        all_k.append(k)
+        all_v.append(v)
+        out = slots[loop].forward_batch(q, k, v, cache, torch.from_numpy(starts_np).cuda(), torch.from_numpy(seq_np).cuda(),
+                                        table, slot_mapping, torch.zeros_like(q), starts_np.tolist(), seq_np.tolist())
+        torch.cuda.synchronize()
+        want = helpers.oracle_attention(case, cache_np[:, :case.num_blocks], loop)
+        got = out.float().cpu().numpy()
+        assert np.all(np.abs(got[:2] - want) <= ATOL + RTOL * np.abs(want))
+        # the prompt rows are plain causal attention over the raw rows
+        scores = np.einsum("thd,shd->hts", prompt_q, prompt_k[loop]) / np.sqrt(128.0)
+        scores = np.where(np.triu(np.ones((prompt, prompt), bool), 1)[None], -np.inf, scores)
+        p = np.exp(scores - scores.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        ref = np.einsum("hts,shd->thd", p, prompt_v[loop])
+        assert np.all(np.abs(got[2:] - ref) <= ATOL + RTOL * np.abs(ref))
+    okr, ovr = helpers.oracle_rotations(case)
+    pairs = [(k.float().cpu().numpy(), v.float().cpu().numpy()) for k, v in zip(all_k, all_v)]
+    O.quantize(pairs, cache_np, slot_mapping.cpu().numpy(), L, okr, ovr, None)
+    assert np.array_equal(cache.cpu().numpy(), cache_np)

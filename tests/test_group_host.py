@@ -38,3 +38,27 @@ def test_invalid_configurations_raise():
         DeferredKVGroup([[2, 32]], 16, coefficient_method="median")
     with pytest.raises(ValueError):
         DeferredKVGroup([[2, 32]], 16, reference_mode="sideways")
+
+
+def test_batch_slices_split_decodes_from_full_prompts():
+    from residualquant_b200.group import BatchSlice, batch_slices, causal_prefill
+
+    assert batch_slices([0], []) == []
+    assert batch_slices([0, 1, 2, 3], [9, 4, 700]) == [BatchSlice(0, 3, 0, 3, True)]
+    # two decodes, then prompts of 5 and 3 tokens
+    assert batch_slices([0, 1, 2, 7, 10], [40, 12, 5, 3]) == [BatchSlice(0, 2, 0, 2, True), BatchSlice(2, 4, 2, 10, False)]
+    assert batch_slices([0, 6], [6]) == [BatchSlice(0, 1, 0, 6, False)]
+    with pytest.raises(ValueError, match="partial prefill"):
+        batch_slices([0, 1, 5], [8, 9])            # 4 query tokens of a 9-token sequence: a chunked prefill
+    with pytest.raises(ValueError, match="precede"):
+        batch_slices([0, 4, 5], [4, 30])           # a decode after a prompt: the batch was not reordered
+    # the default prefill is causal per prompt and keeps prompts independent
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(8, 2, 16) for _ in range(3))
+    out = torch.zeros_like(q)
+    causal_prefill(q, k, v, out, [0, 5, 8])
+    scores = torch.einsum("thd,shd->hts", q[5:8], k[5:8]) / 4.0
+    scores = scores.masked_fill(torch.triu(torch.ones(3, 3, dtype=torch.bool), 1), float("-inf"))
+    want = torch.einsum("hts,shd->thd", scores.softmax(-1), v[5:8])
+    assert torch.allclose(out[5:8], want, atol=1e-5)
+    assert torch.allclose(out[0], v[0], atol=1e-6)  # a prompt's first token attends to itself only
