@@ -25,7 +25,7 @@ class DeferredKVGroup:
     """Owns the packed format of one KV group and keeps raw K/V until every loop of the group has been seen."""
 
     def __init__(self, records: Sequence[Sequence[int]], page_tokens: int, reference_mode: str = "anchor",
-                 anchor_index: Optional[int] = None, coefficient_method: str = "ls"):
+                 anchor_index: Optional[int] = None, coefficient_method: str = "ls", prefill_offload=None):
         self.records = tuple(tuple(int(v) for v in r) for r in records)
         if not self.records:
             raise ValueError("Every packed group must contain at least one record")
@@ -40,6 +40,9 @@ class DeferredKVGroup:
         self.reference_mode = reference_mode
         self.coefficient_method = coefficient_method
         self.pending: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        # optional prefill_offload.PrefillHostStage: non-final loops of a prompt are parked in pinned host memory
+        self.prefill_offload = prefill_offload
+        self.host_buffers: List[Optional[torch.Tensor]] = [None] * (len(self.records) - 1)
 
     def page_width(self, head_dim: int) -> int:
         """Bytes per token of one (head, plane): codes + FP8 scale/offset per group + bf16 alpha, over all records
@@ -53,14 +56,21 @@ class DeferredKVGroup:
         (packed_backend.py:222-223)."""
         return (2, num_blocks, num_kv_heads, self.page_tokens, self.page_width(head_dim))
 
-    def stage(self, key: torch.Tensor, value: torch.Tensor):
-        """Non-final loops: keep a copy, return None.  Final loop: return every (K, V) pair in loop order and reset.
-        The completing call borrows its input, so a one-record group never copies."""
+    def stage(self, key: torch.Tensor, value: torch.Tensor, offload: bool = False):
+        """Non-final loops: keep a copy (on the device, or in pinned host memory with `offload`), return None.  Final
+        loop: return every (K, V) pair in loop order and reset.  The completing call borrows its input, so a
+        one-record group never copies."""
         if len(self.pending) + 1 == len(self.records):
             records = self.pending + [(key, value)]
             self.pending = []
             return records
-        self.pending.append((key.clone(), value.clone()))
+        if offload:
+            index = len(self.pending)
+            buffer = self.prefill_offload.store(key, value, self.host_buffers[index])
+            self.host_buffers[index] = buffer
+            self.pending.append((buffer[0, : key.size(0)], buffer[1, : value.size(0)]))
+        else:
+            self.pending.append((key.clone(), value.clone()))
         return None
 
 
@@ -177,8 +187,14 @@ class PackedAttention(PackedDecodeAttention):
                 local = [int(v) - base for v in query_start_loc_host[part.first_request:part.last_request + 1]]
                 self.prefill(query[tokens], key[tokens], value[tokens], output[tokens], local)
         actual = slot_mapping.numel()
-        staged = group.stage(key[:actual], value[:actual])
+        # prompts in the batch and a host stage on the group: park the held-back loops in pinned memory and bring them
+        # back chunk by chunk for the write (packed_backend.py:45-52, 101-137)
+        offload = group.prefill_offload is not None and any(
+            int(b) - int(a) > 1 for a, b in zip(query_start_loc_host, query_start_loc_host[1:]))
+        staged = group.stage(key[:actual], value[:actual], offload=offload)
         if staged is not None:
-            _cuda.quantize(staged, kv_cache, slot_mapping, self.key_rotation, self.value_rotation, self.key_mean,
-                           records, group.reference_mode, group.anchor_index, group.coefficient_method)
+            parts = group.prefill_offload.chunks(staged, slot_mapping) if offload and len(staged) > 1 else ((staged, slot_mapping),)
+            for chunk_records, chunk_slots in parts:
+                _cuda.quantize(chunk_records, kv_cache, chunk_slots, self.key_rotation, self.value_rotation, self.key_mean,
+                               records, group.reference_mode, group.anchor_index, group.coefficient_method)
         return output

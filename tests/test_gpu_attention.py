@@ -324,10 +324,12 @@ def test_sharp_queries(sharpness):
         _check(case, cache, loop, splits=2 if loop == 0 else 0)
 
 
-def test_mixed_batch_of_decodes_and_a_full_prompt():
+@pytest.mark.parametrize("offload_chunk", [0, 8])
+def test_mixed_batch_of_decodes_and_a_full_prompt(offload_chunk):
     """Two decode requests followed by a 21-token prompt in one batch (the reordered batch of the reference's metadata
     builder, packed_backend.py:153-199): decode rows go through the packed kernel, the prompt through the prefill
-    attention, and the group's quantize writes the new K/V of all 23 tokens."""
+    attention, and the group's quantize writes the new K/V of all 23 tokens -- directly, or with the held-back loops
+    parked in pinned host memory and streamed back 8 tokens at a time (prefill_offload.py of the reference)."""
     from oracle import rq_oracle as O
     from residualquant_b200 import synth
     from residualquant_b200.group import DeferredKVGroup, PackedAttention
@@ -335,7 +337,10 @@ def test_mixed_batch_of_decodes_and_a_full_prompt():
     case = helpers.make_case(45, 128, 4, [150, 47], 32, 16)
     L = case.layout
     kr, vr = G.device_rotations(case)
-    group = DeferredKVGroup(L.records, L.page_tokens)
+    from residualquant_b200.prefill_offload import PrefillHostStage
+
+    stage = PrefillHostStage(offload_chunk) if offload_chunk else None
+    group = DeferredKVGroup(L.records, L.page_tokens, prefill_offload=stage)
     slots = [PackedAttention(group, i, kr, vr) for i in range(4)]
     # room for the prompt: three fresh blocks after the case's own
     prompt = 21
@@ -378,6 +383,8 @@ def test_mixed_batch_of_decodes_and_a_full_prompt():
         p /= p.sum(-1, keepdims=True)
         ref = np.einsum("hts,shd->thd", p, prompt_v[loop])
         assert np.all(np.abs(got[2:] - ref) <= ATOL + RTOL * np.abs(ref))
+        if stage is not None and loop < 3:
+            assert not group.pending[loop][0].is_cuda and group.pending[loop][0].is_pinned()
     okr, ovr = helpers.oracle_rotations(case)
     pairs = [(k.float().cpu().numpy(), v.float().cpu().numpy()) for k, v in zip(all_k, all_v)]
     O.quantize(pairs, cache_np, slot_mapping.cpu().numpy(), L, okr, ovr, None)
