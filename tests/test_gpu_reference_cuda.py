@@ -1,0 +1,194 @@
+"""Second parity source: the reference's OWN CUDA extension, built by oracle/build_ref.py into oracle/_ref/ (a
+git-ignored build product; these tests skip when it is absent).
+
+The reference's quantizer and this repository's agree on everything except rounding-level details that the reference
+itself leaves to the compiler (`--use_fast_math` divisions, TF32-MMA summation order of the rotation): codes may differ
+by one step where a value sits on a rounding boundary, FP8 parameters by one code, bf16 coefficients by one ulp.  So
+the packed caches are compared field by field with those allowances, and the attention outputs of both kernels over
+the SAME (reference-written) cache within the attention tolerance.
+"""
+
+import glob
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import gpu_helpers as G
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+REF_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+ATOL, RTOL = 2e-2, 1e-2
+
+
+def _reference_module():
+    if not glob.glob(os.path.join(REF_DIR, "_cuda*.so")):
+        pytest.skip("the reference's CUDA extension has not been built (python oracle/build_ref.py <checkout>)")
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    import _cuda as reference   # noqa: E402  (the reference's module name)
+    return reference
+
+
+def _fields(cache, layout, head_dim):
+    """Split a packed cache [2, blocks, heads, P, W] viewed per page into per-record arrays."""
+    P = layout.page_tokens
+    pages = cache.reshape(cache.shape[0], cache.shape[1], cache.shape[2], P * cache.shape[4])
+    out = []
+    offset = 0
+    for bits, group in layout.records:
+        code_bytes, groups = head_dim * bits // 8, head_dim // group
+        codes = pages[..., offset:offset + P * code_bytes]
+        offset += P * code_bytes
+        scales = pages[..., offset:offset + P * groups]
+        offset += P * groups
+        offsets = pages[..., offset:offset + P * groups]
+        offset += P * groups
+        alpha = pages[..., offset:offset + 2 * P]
+        offset += 2 * P
+        out.append((bits, codes, scales, offsets, alpha))
+    return out
+
+
+def _unpack(codes, bits):
+    shifts = np.arange(0, 8, bits, dtype=np.uint8)
+    return ((codes[..., None] >> shifts) & ((1 << bits) - 1)).reshape(*codes.shape[:-1], -1).astype(np.int16)
+
+
+@pytest.mark.parametrize("group", [32])
+def test_packed_cache_and_attention_agree_with_the_reference_build(group):
+    reference = _reference_module()
+    from residualquant_b200 import _cuda
+
+    heads, dim = 16, 128                       # the compiled family: Ouro, anchor last, g32
+    case = helpers.make_case(61, dim, heads, [700, 130, 17], group, 16)
+    L = case.layout
+    records = [list(r) for r in L.records]
+    kr, vr = G.device_rotations(case)
+    dense_k = kr.dense() if kr is not None else None
+    dense_v = vr.dense() if vr is not None else None
+    pairs = [(G.bf16(k), G.bf16(v)) for k, v in zip(case.keys, case.values)]
+    slots = torch.from_numpy(case.slots).cuda()
+    shape = (2, case.num_blocks, heads, L.page_tokens, L.page_width)
+
+    theirs = torch.zeros(shape, dtype=torch.uint8, device="cuda")
+    reference.quantize(pairs, theirs, slots, dense_k, dense_v, None, records, "anchor", L.anchor_index, "ls")
+    ours = torch.zeros(shape, dtype=torch.uint8, device="cuda")
+    _cuda.quantize(pairs, ours, slots, kr, vr, None, records, "anchor", L.anchor_index, "ls")
+    torch.cuda.synchronize()
+    a, b = theirs.cpu().numpy(), ours.cpu().numpy()
+    same = float((a == b).mean())
+    assert same >= 0.97, f"only {same:.4f} of the packed bytes are identical"
+    for (bits, ca, sa, oa, aa), (_, cb, sb, ob, ab) in zip(_fields(a, L, dim), _fields(b, L, dim)):
+        step = np.abs(_unpack(ca, bits) - _unpack(cb, bits))
+        assert step.max() <= 1 and float((step > 0).mean()) < 0.03
+        for x, y in ((sa, sb), (oa, ob)):     # FP8 bytes: at most one code apart, ignoring the sign bit layout
+            assert np.abs(x.astype(np.int16) - y.astype(np.int16)).max() <= 1
+        alpha_a = aa.view(np.uint16).astype(np.int32)
+        alpha_b = ab.view(np.uint16).astype(np.int32)
+        assert np.abs(alpha_a - alpha_b).max() <= 1
+
+    # both attention kernels over the reference-written cache
+    rows = len(case.seq_lens)
+    q = G.bf16(case.query)
+    qsl = torch.arange(rows + 1, dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    for loop in range(4):
+        k = G.bf16(case.keys[loop][case.live_rows])
+        v = G.bf16(case.values[loop][case.live_rows])
+        out_theirs, out_ours = torch.zeros_like(q), torch.zeros_like(q)
+        reference.attention(q, k, v, theirs, out_theirs, qsl, seq, table, dense_k, dense_v, None, records, "anchor",
+                            L.anchor_index, loop)
+        _cuda.attention(q, k, v, theirs, out_ours, qsl, seq, table, kr, vr, None, records, "anchor", L.anchor_index, loop)
+        torch.cuda.synchronize()
+        x, y = out_theirs.float().cpu().numpy(), out_ours.float().cpu().numpy()
+        assert np.all(np.abs(x - y) <= ATOL + RTOL * np.abs(x)), f"loop {loop}: {np.abs(x - y).max()}"
+        # and both against the CPU oracle reading the same bytes
+        want = helpers.oracle_attention(case, a, loop)
+        assert np.all(np.abs(y - want) <= ATOL + RTOL * np.abs(want))
+
+
+def test_timing_beside_the_reference_build(capsys):
+    """Both builds on the benchmark's layer shape (batch 64 x context 8192, one layer, CUDA-graph replay).  Prints the
+    device times; asserts only that the outputs agree.  Run with `-s` to see the line."""
+    reference = _reference_module()
+    from residualquant_b200 import _cuda, rotation, synth
+
+    device = "cuda"
+    batch, context, heads, dim, page = 64, 8192, 16, 128, 16
+    records = [[2, 32], [2, 32], [2, 32], [4, 32]]
+    width = 200
+    pages = (context + page - 1) // page
+    blocks = batch * pages + 1
+    g = torch.Generator(device="cpu").manual_seed(5)
+    table = (torch.randperm(blocks - 1, generator=g) + 1).view(batch, pages).to(torch.int32).to(device)
+    signs = synth.signs(np.random.default_rng(3), heads, dim)
+    kr = rotation.signed_hadamard(signs, float(synth.fp16_rsqrt(dim)), device)
+    dense = kr.dense()
+    history = context - 1
+    gd = torch.Generator(device=device).manual_seed(6)
+    rows = [(torch.randn(history, heads, dim, generator=gd, device=device)).bfloat16() for _ in range(8)]
+    pairs = list(zip(rows[:4], rows[4:]))
+    cache = torch.zeros(2, blocks, heads, page, width, dtype=torch.uint8, device=device)
+    positions = torch.arange(history, device=device)
+    for b in range(batch):
+        slots = table[b, positions // page].long() * page + positions % page
+        _cuda.quantize(pairs, cache, slots, kr, None, None, records, "anchor", 3, "ls")
+    q = torch.randn(batch, heads, dim, generator=gd, device=device).bfloat16()
+    k = torch.randn(batch, heads, dim, generator=gd, device=device).bfloat16()
+    v = torch.randn(batch, heads, dim, generator=gd, device=device).bfloat16()
+    qsl = torch.arange(batch + 1, dtype=torch.int32, device=device)
+    seq = torch.full((batch,), context, dtype=torch.int32, device=device)
+    live_slots = (table[:, history // page].long() * page + history % page)
+    live_pairs = [(k, v)] * 4
+    outs = {}
+
+    def timed(fn, reps=5):
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                fn()
+            graph.replay()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            stop.record(stream)
+            stop.synchronize()
+        return 1000.0 * start.elapsed_time(stop) / reps
+
+    line = []
+    for loop in (0, 3):
+        for name, run in (("reference", lambda out, loop=loop: reference.attention(
+                               q, k, v, cache, out, qsl, seq, table, dense, None, None, records, "anchor", 3, loop)),
+                          ("this", lambda out, loop=loop: _cuda.attention(
+                               q, k, v, cache, out, qsl, seq, table, kr, None, None, records, "anchor", 3, loop))):
+            out = torch.zeros_like(q)
+            us = timed(lambda: run(out))
+            outs[(name, loop)] = out.float()
+            line.append(f"attention loop {loop} {name} {us:.1f} us")
+        x, y = outs[("reference", loop)], outs[("this", loop)]
+        assert bool(((x - y).abs() <= ATOL + RTOL * x.abs()).all()), float((x - y).abs().max())
+    scratch = cache.clone()
+    for name, run in (("reference", lambda: reference.quantize(live_pairs, scratch, live_slots, dense, None, None, records,
+                                                                "anchor", 3, "ls")),
+                      ("this", lambda: _cuda.quantize(live_pairs, scratch, live_slots, kr, None, None, records, "anchor", 3,
+                                                      "ls"))):
+        line.append(f"quantize 64 tokens {name} {timed(run):.1f} us")
+    prompt_slots = (table[:2, positions // page].long() * page + positions % page).reshape(-1)
+    prompt_pairs = [(torch.cat([a, a]), torch.cat([b, b])) for a, b in pairs]
+    for name, run in (("reference", lambda: reference.quantize(prompt_pairs, scratch, prompt_slots, dense, None, None, records,
+                                                                "anchor", 3, "ls")),
+                      ("this", lambda: _cuda.quantize(prompt_pairs, scratch, prompt_slots, kr, None, None, records, "anchor", 3,
+                                                      "ls"))):
+        line.append(f"quantize {prompt_slots.numel()} tokens {name} {timed(run, 3):.1f} us")
+    with capsys.disabled():
+        print("\n" + "; ".join(line))
