@@ -4,8 +4,8 @@ git-ignored build product; these tests skip when it is absent).
 The reference's quantizer and this repository's agree on everything except rounding-level details that the reference
 itself leaves to the compiler (`--use_fast_math` divisions, TF32-MMA summation order of the rotation): codes may differ
 by one step where a value sits on a rounding boundary, FP8 parameters by one code, bf16 coefficients by one ulp.  So
-the packed caches are compared field by field with those allowances, and the attention outputs of both kernels over
-the SAME (reference-written) cache within the attention tolerance.
+the packed caches are compared field by field with those allowances (measured: 99.998 % of all bytes identical), and
+both attention kernels read the SAME (reference-written) cache and are compared with the binary64 oracle.
 """
 
 import glob
@@ -54,6 +54,16 @@ def _fields(cache, layout, head_dim):
     return out
 
 
+def _fp8_values(raw):
+    return torch.from_numpy(np.ascontiguousarray(raw)).view(torch.float8_e4m3fn).float().numpy()
+
+
+def _fp8_step(magnitude):
+    """Distance between neighbouring e4m3 values at `magnitude` (3 mantissa bits, smallest subnormal 2^-9)."""
+    exponent = np.floor(np.log2(np.maximum(magnitude, 2.0 ** -6)))
+    return 2.0 ** (exponent - 3)
+
+
 def _unpack(codes, bits):
     shifts = np.arange(0, 8, bits, dtype=np.uint8)
     return ((codes[..., None] >> shifts) & ((1 << bits) - 1)).reshape(*codes.shape[:-1], -1).astype(np.int16)
@@ -82,15 +92,18 @@ def test_packed_cache_and_attention_agree_with_the_reference_build(group):
     torch.cuda.synchronize()
     a, b = theirs.cpu().numpy(), ours.cpu().numpy()
     same = float((a == b).mean())
-    assert same >= 0.97, f"only {same:.4f} of the packed bytes are identical"
+    assert same >= 0.9995, f"only {same:.6f} of the packed bytes are identical"   # measured: 0.99998
     for (bits, ca, sa, oa, aa), (_, cb, sb, ob, ab) in zip(_fields(a, L, dim), _fields(b, L, dim)):
         step = np.abs(_unpack(ca, bits) - _unpack(cb, bits))
-        assert step.max() <= 1 and float((step > 0).mean()) < 0.03
-        for x, y in ((sa, sb), (oa, ob)):     # FP8 bytes: at most one code apart, ignoring the sign bit layout
-            assert np.abs(x.astype(np.int16) - y.astype(np.int16)).max() <= 1
+        assert step.max() <= 1 and float((step > 0).mean()) < 1e-3                # measured: about 1e-5
+        for x, y in ((sa, sb), (oa, ob)):     # FP8 parameters: at most one representable step apart (and -0 == +0)
+            fx, fy = _fp8_values(x), _fp8_values(y)
+            step = _fp8_step(np.maximum(np.abs(fx), np.abs(fy)))
+            assert np.all(np.abs(fx - fy) <= 2 * step), float(np.abs(fx - fy).max())  # 2: across a binade boundary
+            assert float((fx != fy).mean()) < 1e-3                                   # measured: below 1e-4
         alpha_a = aa.view(np.uint16).astype(np.int32)
         alpha_b = ab.view(np.uint16).astype(np.int32)
-        assert np.abs(alpha_a - alpha_b).max() <= 1
+        assert np.abs(alpha_a - alpha_b).max() <= 1 and float((alpha_a != alpha_b).mean()) < 1e-2
 
     # both attention kernels over the reference-written cache
     rows = len(case.seq_lens)
@@ -107,10 +120,14 @@ def test_packed_cache_and_attention_agree_with_the_reference_build(group):
         _cuda.attention(q, k, v, theirs, out_ours, qsl, seq, table, kr, vr, None, records, "anchor", L.anchor_index, loop)
         torch.cuda.synchronize()
         x, y = out_theirs.float().cpu().numpy(), out_ours.float().cpu().numpy()
-        assert np.all(np.abs(x - y) <= ATOL + RTOL * np.abs(x)), f"loop {loop}: {np.abs(x - y).max()}"
-        # and both against the CPU oracle reading the same bytes
+        # The CPU oracle (binary64 arithmetic) reads the same reference-written bytes.  This repository's kernel has
+        # to be inside the tolerance; the reference's kernel accumulates scores and values in bf16 and is measured
+        # at an rms error of 0.011-0.016 (largest element 0.24-0.49) against the same oracle, ten times this kernel's
+        # 0.0013-0.0016, so it is only required to be a noisy version of the same function.
         want = helpers.oracle_attention(case, a, loop)
-        assert np.all(np.abs(y - want) <= ATOL + RTOL * np.abs(want))
+        assert np.all(np.abs(y - want) <= ATOL + RTOL * np.abs(want)), f"loop {loop}: {np.abs(y - want).max()}"
+        assert float(np.sqrt(((x - want) ** 2).mean())) < 0.05, f"loop {loop}: the reference build disagrees with the oracle"
+        assert float(np.sqrt(((x - y) ** 2).mean())) < 0.05
 
 
 def test_timing_beside_the_reference_build(capsys):
@@ -176,7 +193,7 @@ def test_timing_beside_the_reference_build(capsys):
             outs[(name, loop)] = out.float()
             line.append(f"attention loop {loop} {name} {us:.1f} us")
         x, y = outs[("reference", loop)], outs[("this", loop)]
-        assert bool(((x - y).abs() <= ATOL + RTOL * x.abs()).all()), float((x - y).abs().max())
+        assert float(((x - y) ** 2).mean().sqrt()) < 0.05
     scratch = cache.clone()
     for name, run in (("reference", lambda: reference.quantize(live_pairs, scratch, live_slots, dense, None, None, records,
                                                                 "anchor", 3, "ls")),
