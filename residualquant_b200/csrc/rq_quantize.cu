@@ -423,6 +423,112 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
     }
 }
 
+// Decode-sized writes of the headline schedule: a handful of tokens, so latency is what counts.  One warp per
+// (token, head, plane); its four 8-lane groups take the four records of the token side by side: every group loads
+// and rotates its own record at the same time, the last group's anchor is quantized and its bf16 reconstruction is
+// handed to the other three by shuffles, which then form their coefficients and quantize together.  Each row sees the
+// same operations in the same order as in quantize_kernel (8 lanes per row, 16 channels per lane), so the packed bytes
+// are identical; only the four records of a token no longer wait for one another.
+template <int D, int RESIDUAL_GROUP>
+__global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_constant__ QuantizeParams p) {
+    constexpr int kSlices = D / 16, kAnchor = 3;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = lane & 7, record = lane >> 3;
+    const int token = blockIdx.x * 4 + warp;
+    const int head = blockIdx.y, plane = blockIdx.z;
+    if (token >= p.num_tokens) return;
+    const int64_t slot = p.slots[token];
+    if (slot < 0) return;  // padding (the whole warp)
+    const bool owner = j < kSlices;
+
+    const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
+    const int64_t* strides = plane == 0 ? p.key_stride : p.value_stride;
+    const bool rotated = p.rotation[plane] == RQ_ROTATION_SIGNED_HADAMARD;
+    const float rscale = p.rscale[plane];
+    uint32_t sign16 = 0;
+    if (rotated && owner) sign16 = (p.sign[plane][head * (D / 32) + (j >> 1)] >> (16 * (j & 1))) & 0xffffu;
+    const bool centered = plane == 0 && p.mean != nullptr;
+
+    float y[16], mean[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) y[i] = mean[i] = 0.f;
+    if (owner) {
+        const uint4* src = reinterpret_cast<const uint4*>(sources[record] + static_cast<int64_t>(token) * strides[record] +
+                                                          head * D + 16 * j);
+        const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t flip = (((sign16 >> (2 * i)) & 1u) << 15) | (((sign16 >> (2 * i + 1)) & 1u) << 31);
+            const uint32_t word = w[i] ^ flip;  // sign diagonal on the raw bf16 pair
+            y[2 * i] = __uint_as_float(word << 16);
+            y[2 * i + 1] = __uint_as_float(word & 0xffff0000u);
+        }
+        if (centered) {
+            const float4* m4 = reinterpret_cast<const float4*>(p.mean + (static_cast<int64_t>(record) * p.heads + head) * D + 16 * j);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = __ldg(m4 + i);
+                mean[4 * i] = v.x; mean[4 * i + 1] = v.y; mean[4 * i + 2] = v.z; mean[4 * i + 3] = v.w;
+            }
+        }
+    }
+    if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+
+    const int P = p.page_tokens;
+    const int tok = static_cast<int>(slot % P);
+    uint8_t* page = p.cache + plane * p.plane_stride + (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width;
+    uint8_t* out = page + static_cast<int64_t>(P) * p.record_offset[record];
+    auto store_parameters = [&](int code_bytes, int group, const GroupCode& q, uint16_t alpha_bits) {
+        const int groups = D / group;
+        uint8_t* scales = out + P * code_bytes;
+        uint8_t* offsets = scales + P * groups;
+        if (group == 16) {
+            scales[tok * groups + j] = q.scale8;
+            offsets[tok * groups + j] = q.offset8;
+        } else if ((j & 1) == 0) {
+            scales[tok * groups + (j >> 1)] = q.scale8;
+            offsets[tok * groups + (j >> 1)] = q.offset8;
+        }
+        if (j == 0) *reinterpret_cast<uint16_t*>(out + P * (code_bytes + 2 * groups) + tok * 2) = alpha_bits;
+    };
+
+    // ---- the anchor (every group runs the arithmetic on its own row, only the anchor's group keeps the result) ----
+    float ref[16];
+    {
+        float z[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) z[i] = centered ? __fsub_rn(y[i], mean[i]) : y[i];
+        const GroupCode q = group_quantize<4>(z, 32);
+        if (record == kAnchor && owner) {
+            *reinterpret_cast<uint2*>(out + tok * (D / 2) + 8 * j) =
+                make_uint2(pack_codes<4, 8>(q.magic), pack_codes<4, 8>(q.magic + 8));
+            store_parameters(D / 2, 32, q, 0x3F80u);
+        }
+        const float scale = fp8_decode(q.scale8), offset = fp8_decode(q.offset8);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float restored = restore_bf16(q.magic[i], scale, offset);
+            if (centered) restored = bf16_add(restored, bf16_round(mean[i]));
+            ref[i] = __shfl_sync(kFullMask, restored, 8 * kAnchor + j);  // the anchor group's value for this slice
+        }
+    }
+    // ---- the three residual records, side by side ----
+    const float den = row_dot(ref, ref);
+    const __nv_bfloat16 stored = __float2bfloat16_rn(__fdiv_rn(row_dot(y, ref), fmaxf(den, 1e-12f)));
+    const float alpha = __bfloat162float(stored);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        y[i] = __fmaf_rn(-ref[i], alpha, y[i]);
+        if (centered) y[i] = __fsub_rn(y[i], mean[i]);
+    }
+    const GroupCode q = group_quantize<2>(y, RESIDUAL_GROUP);
+    if (record != kAnchor && owner) {
+        *reinterpret_cast<uint32_t*>(out + tok * (D / 4) + 4 * j) = pack_codes<2, 16>(q.magic);
+        store_parameters(D / 4, RESIDUAL_GROUP, q, __bfloat16_as_ushort(stored));
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream) {
@@ -431,6 +537,17 @@ cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t 
                           p.coefficient == RQ_COEFF_LS && p.chain == RQ_CHAIN_KERNEL && p.bits[3] == 4 && p.group[3] == 32 &&
                           p.bits[0] == 2 && p.bits[1] == 2 && p.bits[2] == 2 && p.group[0] == p.group[1] &&
                           p.group[1] == p.group[2];
+    // decode-sized writes of aligned bf16 rows: one warp per token with the records side by side
+    const bool few_tokens = headline && p.num_tokens <= 256 && p.vector_loads && p.rotated_rows[0] == nullptr &&
+                            p.rotated_rows[1] == nullptr;
+    if (few_tokens) {
+        const dim3 token_grid((p.num_tokens + 3) / 4, p.heads, 2);
+        if (head_dim == 128 && p.group[0] == 32) quantize_token_kernel<128, 32><<<token_grid, 128, 0, stream>>>(p);
+        else if (head_dim == 128) quantize_token_kernel<128, 16><<<token_grid, 128, 0, stream>>>(p);
+        else if (p.group[0] == 32) quantize_token_kernel<96, 32><<<token_grid, 128, 0, stream>>>(p);
+        else quantize_token_kernel<96, 16><<<token_grid, 128, 0, stream>>>(p);
+        return cudaGetLastError();
+    }
     if (headline && p.group[0] == 32) {
         if (head_dim == 128) quantize_kernel<128, Anchor2224<32>><<<grid, 128, 0, stream>>>(p);
         else quantize_kernel<96, Anchor2224<32>><<<grid, 128, 0, stream>>>(p);

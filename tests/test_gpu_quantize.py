@@ -31,6 +31,13 @@ def test_packed_bytes_bit_exact(head_dim, group, page):
     _compare(helpers.make_case(11, head_dim, 3, [70, 1, 33, 16], group, page))
 
 
+@pytest.mark.parametrize("head_dim,group,mean", [(128, 32, False), (128, 16, True), (96, 32, True), (96, 16, False)])
+def test_prefill_sized_write_bit_exact(head_dim, group, mean):
+    """More than 256 tokens in one call: the kernel that walks the records of a row one after another (smaller calls
+    of the headline schedule take the one-warp-per-token kernel, which the other cases of this file cover)."""
+    _compare(helpers.make_case(15, head_dim, 2, [300, 41, 130], group, 16, with_mean=mean))
+
+
 @pytest.mark.parametrize("head_dim", [128, 96])
 def test_with_key_mean(head_dim):
     _compare(helpers.make_case(12, head_dim, 2, [45, 20], 32, 16, with_mean=True))
