@@ -69,14 +69,26 @@ def _unpack(codes, bits):
     return ((codes[..., None] >> shifts) & ((1 << bits) - 1)).reshape(*codes.shape[:-1], -1).astype(np.int16)
 
 
-@pytest.mark.parametrize("heads,dim,group", [(16, 128, 32), (16, 128, 16), (55, 96, 32)])
-def test_packed_cache_and_attention_agree_with_the_reference_build(heads, dim, group):
-    """One case per dispatch family of the reference that oracle/build_ref.py may have compiled (Ouro anchor-last g32 /
-    g16, Huginn anchor-last g32); a family that was left out is skipped."""
+def _schedule(text, group):
+    """"2224" -> ((2, g), (2, g), (2, g), (4, 32)): INT4 records always use groups of 32 in the reference's lists."""
+    return tuple((int(c), 32 if c == "4" else group) for c in text)
+
+
+@pytest.mark.parametrize("heads,dim,schedule,group,mode,anchor", [
+    (16, 128, "2224", 32, "anchor", 3), (16, 128, "2224", 16, "anchor", 3), (55, 96, "2224", 32, "anchor", 3),
+    (16, 128, "4444", 32, "anchor", 3), (16, 128, "2222", 32, "anchor", 3), (16, 128, "4222", 32, "anchor", 3),
+    (16, 128, "4222", 32, "anchor", 0), (16, 128, "4222", 16, "anchor", 0), (16, 128, "2222", 16, "anchor", 0),
+    (16, 128, "4222", 32, "adjacent", 0), (16, 128, "2224", 32, "adjacent", 0), (16, 128, "4222", 16, "adjacent", 0),
+    (16, 128, "4", 32, "adjacent", 0), (16, 128, "2", 16, "adjacent", 0),
+])
+def test_packed_cache_and_attention_agree_with_the_reference_build(heads, dim, schedule, group, mode, anchor):
+    """One case per (dispatch family, schedule) of the reference that oracle/build_ref.py may have compiled; a family
+    that was left out is skipped."""
     reference = _reference_module()
     from residualquant_b200 import _cuda
 
-    case = helpers.make_case(61, dim, heads, [700, 130, 17] if heads == 16 else [300, 40, 17], group, 16)
+    case = helpers.make_case(61, dim, heads, [700, 130, 17] if heads == 16 else [300, 40, 17], page_tokens=16,
+                             records=_schedule(schedule, group), anchor_index=anchor, reference_mode=mode)
     L = case.layout
     records = [list(r) for r in L.records]
     kr, vr = G.device_rotations(case)
@@ -88,20 +100,22 @@ def test_packed_cache_and_attention_agree_with_the_reference_build(heads, dim, g
 
     theirs = torch.zeros(shape, dtype=torch.uint8, device="cuda")
     try:
-        reference.quantize(pairs, theirs, slots, dense_k, dense_v, None, records, "anchor", L.anchor_index, "ls")
+        reference.quantize(pairs, theirs, slots, dense_k, dense_v, None, records, mode, L.anchor_index, "ls")
     except RuntimeError as error:
         if "No compiled packed CUDA kernel" in str(error):
             pytest.skip("this dispatch family of the reference was not built")
         raise
     ours = torch.zeros(shape, dtype=torch.uint8, device="cuda")
-    _cuda.quantize(pairs, ours, slots, kr, vr, None, records, "anchor", L.anchor_index, "ls")
+    _cuda.quantize(pairs, ours, slots, kr, vr, None, records, mode, L.anchor_index, "ls")
     torch.cuda.synchronize()
     a, b = theirs.cpu().numpy(), ours.cpu().numpy()
     same = float((a == b).mean())
     assert same >= 0.9995, f"only {same:.6f} of the packed bytes are identical"   # measured: 0.99998
     for (bits, ca, sa, oa, aa), (_, cb, sb, ob, ab) in zip(_fields(a, L, dim), _fields(b, L, dim)):
         step = np.abs(_unpack(ca, bits) - _unpack(cb, bits))
-        assert step.max() <= 1 and float((step > 0).mean()) < 1e-3                # measured: about 1e-5
+        # measured: about 1e-5 of the codes differ, by one step -- by more only in the rare rows whose bf16
+        # coefficient came out an ulp or two apart, which moves the whole residual of an outlier channel
+        assert float((step > 0).mean()) < 1e-3 and float((step > 1).mean()) < 1e-4
         for x, y in ((sa, sb), (oa, ob)):     # FP8 parameters: at most one representable step apart (and -0 == +0)
             fx, fy = _fp8_values(x), _fp8_values(y)
             step = _fp8_step(np.maximum(np.abs(fx), np.abs(fy)))
@@ -109,9 +123,11 @@ def test_packed_cache_and_attention_agree_with_the_reference_build(heads, dim, g
             # the residual of an outlier channel moves enough to shift a group's range by a few steps.
             assert float((np.abs(fx - fy) > 2 * step).mean()) < 1e-4
             assert float((fx != fy).mean()) < 1e-3                                   # measured: below 1e-4
-        alpha_a = aa.view(np.uint16).astype(np.int32)
-        alpha_b = ab.view(np.uint16).astype(np.int32)
-        assert np.abs(alpha_a - alpha_b).max() <= 1 and float((alpha_a != alpha_b).mean()) < 1e-2
+        # bf16 coefficients: a couple of ulps apart at most (compared as numbers: near zero the bit patterns are far apart)
+        alpha_a = (aa.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+        alpha_b = (ab.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+        assert np.all(np.abs(alpha_a - alpha_b) <= 2.0 ** -6 * np.maximum(np.abs(alpha_a), np.abs(alpha_b)) + 1e-3)
+        assert float((alpha_a != alpha_b).mean()) < 1e-2
 
     # both attention kernels over the reference-written cache
     rows = len(case.seq_lens)
@@ -119,13 +135,13 @@ def test_packed_cache_and_attention_agree_with_the_reference_build(heads, dim, g
     qsl = torch.arange(rows + 1, dtype=torch.int32, device="cuda")
     seq = torch.from_numpy(case.seq_lens).cuda()
     table = torch.from_numpy(case.block_table).cuda()
-    for loop in range(4):
+    for loop in range(len(records)):
         k = G.bf16(case.keys[loop][case.live_rows])
         v = G.bf16(case.values[loop][case.live_rows])
         out_theirs, out_ours = torch.zeros_like(q), torch.zeros_like(q)
-        reference.attention(q, k, v, theirs, out_theirs, qsl, seq, table, dense_k, dense_v, None, records, "anchor",
+        reference.attention(q, k, v, theirs, out_theirs, qsl, seq, table, dense_k, dense_v, None, records, mode,
                             L.anchor_index, loop)
-        _cuda.attention(q, k, v, theirs, out_ours, qsl, seq, table, kr, vr, None, records, "anchor", L.anchor_index, loop)
+        _cuda.attention(q, k, v, theirs, out_ours, qsl, seq, table, kr, vr, None, records, mode, L.anchor_index, loop)
         torch.cuda.synchronize()
         x, y = out_theirs.float().cpu().numpy(), out_ours.float().cpu().numpy()
         # The CPU oracle (binary64 arithmetic) reads the same reference-written bytes.  This repository's kernel has
