@@ -14,8 +14,8 @@ bool attention_variant_available(const AttentionVariant& v) {
     if (v.adjacent) return true;  // record types are checked by the caller (INT4 g32, INT2 g16/g32; at most 4 records)
     const int ab = v.anchor_bits, ag = v.anchor_group, rb = v.residual_bits, rg = v.residual_group;
     if (ab == 4 && ag == 32) return rb == 0 || (rb == 2 && (rg == 16 || rg == 32)) || (rb == 4 && rg == 32);
-    if (ab == 2 && ag == 32) return rb == 0 || (rb == 2 && rg == 32);
-    if (ab == 2 && ag == 16) return rb == 0 || (rb == 2 && rg == 16);
+    if (ab == 2 && ag == 32) return rb == 0 || (rb == 2 && rg == 32) || (rb == 4 && rg == 32);
+    if (ab == 2 && ag == 16) return rb == 0 || (rb == 2 && rg == 16) || (rb == 4 && rg == 32);
     return false;
 }
 

@@ -1048,9 +1048,11 @@ cudaError_t launch_records(const AttentionVariant& v, const AttentionParams& p, 
     } else if (ab == 2 && ag == 32) {
         if (rb == 0) return launch_mean<D, 2, 32, 0, 32, P>(v.has_mean, p, stream);
         if (rb == 2 && rg == 32) return launch_mean<D, 2, 32, 2, 32, P>(v.has_mean, p, stream);
+        if (rb == 4 && rg == 32) return launch_mean<D, 2, 32, 4, 32, P>(v.has_mean, p, stream);  // "4222"/"2224", INT2 anchor
     } else if (ab == 2 && ag == 16) {
         if (rb == 0) return launch_mean<D, 2, 16, 0, 32, P>(v.has_mean, p, stream);
         if (rb == 2 && rg == 16) return launch_mean<D, 2, 16, 2, 16, P>(v.has_mean, p, stream);
+        if (rb == 4 && rg == 32) return launch_mean<D, 2, 16, 4, 32, P>(v.has_mean, p, stream);
     }
     return cudaErrorInvalidDeviceFunction;
 }

@@ -267,6 +267,9 @@ def test_decode_step_through_the_group_mirror():
     (((4, 32), (2, 16), (2, 16), (2, 16)), 0),
     (((4, 32),), 0),
     (((2, 32),), 0),
+    (((4, 32), (2, 32), (2, 32), (2, 32)), 3),      # "4222" with the anchor last: INT2 anchor, INT4 first loop
+    (((4, 32), (2, 16), (2, 16), (2, 16)), 3),
+    (((2, 32), (2, 32), (2, 32), (4, 32)), 0),      # "2224" with the anchor first
 ])
 @pytest.mark.parametrize("head_dim", [128, 96])
 def test_other_schedules_of_the_registry(records, anchor, head_dim):

@@ -80,6 +80,7 @@ def _schedule(text, group):
     (16, 128, "4222", 32, "anchor", 0), (16, 128, "4222", 16, "anchor", 0), (16, 128, "2222", 16, "anchor", 0),
     (16, 128, "4222", 32, "adjacent", 0), (16, 128, "2224", 32, "adjacent", 0), (16, 128, "4222", 16, "adjacent", 0),
     (16, 128, "4", 32, "adjacent", 0), (16, 128, "2", 16, "adjacent", 0),
+    (16, 128, "4222", 16, "anchor", 3), (16, 128, "2224", 32, "anchor", 0), (16, 128, "2224", 16, "anchor", 0),
 ])
 def test_packed_cache_and_attention_agree_with_the_reference_build(heads, dim, schedule, group, mode, anchor):
     """One case per (dispatch family, schedule) of the reference that oracle/build_ref.py may have compiled; a family
