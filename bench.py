@@ -387,6 +387,13 @@ def run_gpu(args):
         seq_lens.add_(1)
 
     stream = torch.cuda.Stream(device)
+
+    def join_default_stream():
+        """Everything queued on the default stream (input tensors, lengths, tables) is complete before the side stream
+        reads it: a kernel that saw half-initialised lengths or block ids would read outside the cache."""
+        stream.wait_stream(torch.cuda.current_stream(device))
+
+    join_default_stream()
     with torch.cuda.stream(stream):
         step_body()                      # eager warm-up: workspace, per-variant attributes
     stream.synchronize()
@@ -414,6 +421,7 @@ def run_gpu(args):
     def timed(fn, steps):
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
+        join_default_stream()
         with torch.cuda.stream(stream):
             start.record(stream)
             for _ in range(steps):
@@ -425,6 +433,7 @@ def run_gpu(args):
 
     sampler = ClockSampler(local_rank)
     # ---------------- device-resident throughput ----------------
+    join_default_stream()
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             graph.replay()
@@ -460,6 +469,7 @@ def run_gpu(args):
         host_out.copy_(out, non_blocking=True)
         host_lens.add_(1)
 
+    join_default_stream()
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             e2e_step()
@@ -481,6 +491,7 @@ def run_gpu(args):
     def graph_timed(fn, replays):
         """Capture `fn` once (after an eager warm-up) and time `replays` replays: per-kernel device time without
         the Python launch overhead of eager calls."""
+        join_default_stream()
         with torch.cuda.stream(stream):
             fn()
         stream.synchronize()

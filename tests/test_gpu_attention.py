@@ -124,6 +124,7 @@ def test_cuda_graph_replay_follows_changed_metadata():
         _cuda.quantize(list(zip(live_k, live_v)), cache, live_slots, kr, vr, None, records, "anchor", 3, "ls")
 
     side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())   # the inputs were created on the default stream
     with torch.cuda.stream(side):
         step()                                   # warm-up: creates the workspace outside capture
     side.synchronize()

@@ -193,6 +193,7 @@ def test_timing_beside_the_reference_build(capsys, batch):
 
     def timed(fn, reps=5):
         stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())   # inputs, lengths and tables come from the default stream
         with torch.cuda.stream(stream):
             fn()
             stream.synchronize()
