@@ -142,8 +142,10 @@ class HeadGather:
             self.state = torch.zeros(64, dtype=torch.int32, device=self.device)
             self._owner = _DeviceBytes(self.base, self.nbytes)
             self._bytes = torch.as_tensor(self._owner, device=self.device)
+        # the zero fill of the allocation and of the barrier state is complete on this GPU ...
+        torch.cuda.synchronize(self.device)
         if self.world > 1:
-            dist.barrier()   # every rank has mapped every allocation before anyone writes
+            dist.barrier()   # ... and every rank has mapped every allocation before anyone writes
 
     def peer_pointers(self, buffer: int) -> List[int]:
         if not 0 <= buffer < self.buffers:
