@@ -16,22 +16,30 @@ Printed JSON line:
   e2e       tokens/s when each step also copies its q/k/v rows from pinned host memory and reads the outputs back
   roofline  the dominant kernel (attention of a residual loop): algorithmic packed-KV bytes per launch / CUDA-event
             time per launch, against the measured HBM copy bandwidth of MEASURED_PEAKS.json
-  cpu_baseline  the CPU oracle (a restatement of the reference's algorithm) timed on a bounded sample, scaled
-            to the same unit
+  sweep     attention alone over batch {1, 8, 32, 64} x context {2048, 4096, 8192}, residual and anchor loop
+  ragged    a 64-row batch of one 8192-token row and 63 short rows against the time its pages imply at the uniform rate
+  other_shapes  the same kernels with INT2 g16 residuals, and at 55 heads x 96 (batch 16 x 4096)
+  bf16_kv_comparator  a BF16-KV decode attention (library kernel, contiguous KV) of one layer's four loops
+  reference_cuda  the reference's own CUDA kernels on the same GPU, cache and inputs, when oracle/_ref holds its build
+  head_sharded  (N > 1 only) the 55 x 96 shape with the KV heads spread over the ranks and the output gather fused
+            into the attention kernel
+  cpu_baseline  the reference's PyTorch statement of the path (FP32Chain.reconstruct + probabilities + p @ V) timed on
+            this machine's host cores; the numpy restatement when those files are absent
 
-`--impl reference` times that CPU restatement alone (the reference has no native CPU path and its PyTorch
-code cannot travel to the benchmark machine).
+`--impl reference` times that CPU path alone, with every host thread, on the same workload description.
 """
 
 from __future__ import annotations
 
 import argparse
+import glob
 import json
 import os
 import statistics
 import subprocess
 import sys
 import time
+from dataclasses import dataclass, replace
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -41,8 +49,28 @@ import numpy as np  # noqa: E402
 
 METRIC = "decode_tokens_per_s"
 UNIT = "tokens/s"
-HEADS, HEAD_DIM, PAGE = 16, 128, 16
 FALLBACK_HBM_GBS = 6650.0
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+@dataclass(frozen=True)
+class Shape:
+    """One workload: a stack of `layers` KV groups of 4 loops ([2, group] x 3 + [4, 32], anchor last)."""
+    batch: int
+    context: int
+    layers: int
+    heads: int = 16
+    head_dim: int = 128
+    page: int = 16
+    group: int = 32
+
+    @property
+    def records(self):
+        return [[2, self.group]] * 3 + [[4, 32]]
+
+    @property
+    def width(self):
+        return 3 * record_bytes(2, self.group, self.head_dim) + record_bytes(4, 32, self.head_dim)
 
 
 def parse_args():
@@ -63,35 +91,30 @@ def parse_args():
                         "all sequences but only its KV heads and all-gathers the attention output (strong scaling)")
     p.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                    help="with --shard heads: fused = the attention kernel stores into every GPU's gathered output over "
-                        "NVLink and a barrier kernel follows (captured in the graph); nccl = one all-gather per call, eager")
-    p.add_argument("--splits", type=int, default=0, help="force the number of KV partitions per row (0 = library default)")
-    p.add_argument("--compare-bf16", action="store_true",
-                   help="also time a BF16-KV decode attention (torch SDPA, contiguous KV) of one layer's 4 loops")
+                        "NVLink (captured in the graph); nccl = one all-gather per call, eager")
+    p.add_argument("--splits", type=int, default=0,
+                   help="force the number of KV partitions per row (0 = the kernel picks them per row from the lengths)")
+    p.add_argument("--quick", action="store_true",
+                   help="only the headline numbers: no sweep, other shapes, comparators or CPU baseline")
     p.add_argument("--no-cpu-baseline", action="store_true")
-    p.add_argument("--sweep", action="store_true", help="also time attention alone over the batch x context grid")
     return p.parse_args()
 
 
-def record_bytes(bits, group, dim=None):
-    dim = HEAD_DIM if dim is None else dim
+def record_bytes(bits, group, dim):
     return dim * bits // 8 + 2 * dim // group + 2
 
 
-def attention_bytes(batch, context, group, loop_is_anchor, heads=None, dim=None):
+def attention_bytes(history_tokens, rows, shape, loop_is_anchor):
     """Algorithmic bytes of one attention launch: every cached token's anchor record without its alpha column,
-    plus the loop's own residual record, for K and V; plus q, live k, live v, out in bf16."""
-    heads = HEADS if heads is None else heads
-    dim = HEAD_DIM if dim is None else dim
-    anchor = record_bytes(4, 32, dim) - 2
-    per_token = anchor if loop_is_anchor else anchor + record_bytes(2, group, dim)
-    return batch * (context - 1) * heads * 2 * per_token + batch * heads * dim * 8
+    plus the loop's own residual record, for K and V; plus q, live k, live v, out in bf16.  `history_tokens` is the sum
+    over the rows of their cached tokens."""
+    anchor = record_bytes(4, 32, shape.head_dim) - 2
+    per_token = anchor if loop_is_anchor else anchor + record_bytes(2, shape.group, shape.head_dim)
+    return history_tokens * shape.heads * 2 * per_token + rows * shape.heads * shape.head_dim * 8
 
 
-def quantize_bytes(tokens, group, heads=None, dim=None):
-    heads = HEADS if heads is None else heads
-    dim = HEAD_DIM if dim is None else dim
-    width = 3 * record_bytes(2, group, dim) + record_bytes(4, 32, dim)
-    return 2 * 4 * tokens * heads * dim * 2 + 2 * tokens * heads * width
+def quantize_bytes(tokens, shape):
+    return 2 * 4 * tokens * shape.heads * shape.head_dim * 2 + 2 * tokens * shape.heads * shape.width
 
 
 def measured_peak():
@@ -104,70 +127,132 @@ def measured_peak():
 
 
 # ----------------------------------------------------------------------------------------------------------
-# CPU restatement (oracle) timed on a bounded sample
+# CPU arm: the reference's own PyTorch statement of the path, timed on this machine's host cores
 # ----------------------------------------------------------------------------------------------------------
 
 
-def cpu_sample(context, group, layers, batch, sample_context=2048, seed=0):
-    """One sequence, one layer, context `sample_context`: quantize of the whole prompt (K and V, 4 loops) and the
-    decode attention of the 4 loops.  Returns (tokens/s scaled to the full workload, description)."""
-    from oracle import rq_oracle as O
+def reference_python_available():
+    return all(os.path.isfile(os.path.join(REF_DIR, "py", "calibration", name))
+               for name in ("quantization.py", "rotation_math.py", "rotation_training.py"))
+
+
+class ReferenceCpuPath:
+    """One layer of ONE sequence at the workload's full context, through the reference's own functions
+    (scripts/calibration/rotation_training.py:46-62 FP32Chain.reconstruct, rotation_math.py:44-49 probabilities):
+
+      set-up (timed apart): quantize + reconstruct the `context - 1` cached tokens of the four loops, K and V;
+      one step:  the four decode attentions (probabilities over the reconstructed keys + the live key, p @ V) and the
+                 quantize + reconstruct of the step's new token, K and V.
+
+    The workload's step is `layers x batch` such independent units; nothing is extrapolated along the context."""
+
+    def __init__(self, shape: Shape, threads: int, seed: int = 0):
+        import torch
+
+        sys.path.insert(0, os.path.join(REF_DIR, "py"))
+        from calibration.rotation_math import hadamard, probabilities
+        from calibration.rotation_training import FP32Chain
+
+        torch.set_num_threads(threads)
+        torch.set_grad_enabled(False)
+        self.torch, self.shape, self.probabilities = torch, shape, probabilities
+        H, D, T = shape.heads, shape.head_dim, shape.context
+        g = torch.Generator().manual_seed(seed)
+
+        def loops():
+            scale = torch.exp(0.5 * torch.randn(H, D, generator=g))
+            anchor = torch.randn(T, H, D, generator=g) * scale
+            for h in range(H):
+                anchor[:, h, torch.randperm(D, generator=g)[:4]] *= 8
+            return [(anchor * 0.9 + 0.3 * torch.randn(T, H, D, generator=g)).bfloat16() for _ in range(3)] + [anchor.bfloat16()]
+
+        self.keys, self.values = loops(), loops()
+        sign = (torch.randint(0, 2, (H, D), generator=g) * 2 - 1).float()
+        self.rotation = (sign[:, :, None] * hadamard("cpu", D)[None]).half().float().contiguous()
+        self.chain = FP32Chain([2, 2, 2, 4], "anchor", [shape.group] * 3 + [32], anchor_index=3)
+        self.query = torch.randn(1, H, D, generator=g).bfloat16()
+        t0 = time.perf_counter()
+        history = [{"k": k[: T - 1], "v": v[: T - 1]} for k, v in zip(self.keys, self.values)]
+        self.k_hat = self.chain.reconstruct(history, "k", [self.rotation], None)
+        self.v_hat = self.chain.reconstruct(history, "v", [self.rotation], None)
+        self.setup_seconds = time.perf_counter() - t0
+        # the decode contract: cached tokens reconstructed, the last token live (raw bf16)
+        self.k_all = [torch.cat([self.k_hat[i], self.keys[i][T - 1:].float()]) for i in range(4)]
+        self.v_all = [torch.cat([self.v_hat[i], self.values[i][T - 1:].float()]) for i in range(4)]
+        self.last = torch.tensor([T - 1])
+
+    def step(self):
+        torch, T = self.torch, self.shape.context
+        t0 = time.perf_counter()
+        for loop in range(4):
+            p = self.probabilities(self.query, self.k_all[loop], self.last, head_dim=self.shape.head_dim)
+            torch.bmm(p, self.v_all[loop].transpose(0, 1))
+        t1 = time.perf_counter()
+        live = [{"k": k[T - 1:], "v": v[T - 1:]} for k, v in zip(self.keys, self.values)]
+        self.chain.reconstruct(live, "k", [self.rotation], None)
+        self.chain.reconstruct(live, "v", [self.rotation], None)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+
+
+def cpu_reference(shape: Shape, steps: int, warmup: int):
+    """(tokens/s of the workload on the host cores, cpu_baseline dict, seconds of one whole-workload step)."""
+    threads = max(1, os.cpu_count() or 1)
+    path = ReferenceCpuPath(shape, threads)
+    attention, write = [], []
+    for i in range(warmup + steps):
+        a, w = path.step()
+        if i >= warmup:
+            attention.append(a)
+            write.append(w)
+    unit = statistics.median(attention) + statistics.median(write)   # one sequence, one layer
+    step_seconds = unit * shape.layers * shape.batch
+    value = shape.batch / step_seconds
+    sample = (f"the reference's PyTorch path (FP32Chain.reconstruct + probabilities + p@V, torch {path.torch.__version__}, "
+              f"{threads} threads) on 1 sequence x 1 layer at the full context {shape.context}: 4 decode attentions "
+              f"{1e3 * statistics.median(attention):.1f} ms + write of the new token {1e3 * statistics.median(write):.1f} ms, "
+              f"median of {steps}; the step is {shape.layers} layers x {shape.batch} sequences of this unit "
+              f"(set-up, not in the step: quantize+reconstruct of the {shape.context - 1} cached tokens "
+              f"{path.setup_seconds:.2f} s = {(shape.context - 1) / path.setup_seconds:.0f} tokens/s)")
+    baseline = {"value": value, "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample,
+                "prefill_write_tokens_per_s": (shape.context - 1) / path.setup_seconds}
+    return value, baseline, step_seconds
+
+
+def cpu_port(shape: Shape, sample_context=1024, seed=0):
+    """Fallback when the reference's PyTorch files were not placed under oracle/_ref/py: the numpy restatement, one
+    sequence, one layer, at a reduced context (it is a scalar port), scaled linearly along the context."""
     from tests import helpers
 
-    case = helpers.make_case(seed, HEAD_DIM, HEADS, [sample_context], group, PAGE)
+    case = helpers.make_case(seed, shape.head_dim, shape.heads, [sample_context], shape.group, shape.page)
     t0 = time.perf_counter()
     cache = helpers.oracle_cache(case)
     t1 = time.perf_counter()
     for loop in range(4):
         helpers.oracle_attention(case, cache, loop)
     t2 = time.perf_counter()
-    quantize_per_token = (t1 - t0) / max(1, sample_context - 1)
-    attention_per_cached_token = (t2 - t1) / max(1, sample_context - 1)
-    # one decode step of the full workload for ONE sequence: `layers` x (4 attentions over `context` + 1 write)
-    step_seconds = layers * (attention_per_cached_token * (context - 1) + quantize_per_token)
-    description = (
-        f"numpy oracle, 1 sequence x 1 layer x context {sample_context} (quantize {t1 - t0:.2f}s, "
-        f"4 attentions {t2 - t1:.2f}s), scaled linearly to {layers} layers x context {context}"
-    )
-    return 1.0 / step_seconds, description, (t2 - t0)
+    write = (t1 - t0) / max(1, sample_context - 1)
+    attention = (t2 - t1) / max(1, sample_context - 1) * (shape.context - 1)
+    step_seconds = (attention + write) * shape.layers * shape.batch
+    value = shape.batch / step_seconds
+    sample = (f"numpy restatement (oracle/rq_oracle.py), 1 sequence x 1 layer x context {sample_context} (quantize "
+              f"{t1 - t0:.2f} s, 4 attentions {t2 - t1:.2f} s), scaled linearly to context {shape.context}; the reference's "
+              "PyTorch files were not found under oracle/_ref/py")
+    return value, {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample}, step_seconds
 
 
-def _reference_worker(job):
-    context, group, layers, batch, sample_context, seed = job
-    import numpy  # noqa: F401  (each worker is a fresh interpreter)
-    value, description, seconds = cpu_sample(context, group, layers, batch, sample_context, seed)
-    return value, description, seconds
+def cpu_baseline(shape: Shape, steps=3, warmup=1):
+    if reference_python_available():
+        return cpu_reference(shape, steps, warmup)
+    return cpu_port(shape)
 
 
-def run_reference(args):
-    """The CPU restatement on every host core: one worker process per core, each running the hot path of one
-    sequence (quantize of a 512-token prompt for one layer + the 4 decode attentions), scaled to the workload's unit."""
-    import concurrent.futures
-
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def run_reference(args, shape):
+    """`--impl reference`: the CPU path alone.  Rank 0 only; the other ranks have nothing to do."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    cores = max(1, min(os.cpu_count() or 1, 64))
-    values, description = [], ""
-    begin = time.perf_counter()
-    with concurrent.futures.ProcessPoolExecutor(max_workers=cores) as pool:
-        for i in range(args.warmup + args.steps):
-            jobs = [(args.context, args.group, args.layers, args.batch, 512, 1000 * i + w) for w in range(cores)]
-            t0 = time.perf_counter()
-            results = list(pool.map(_reference_worker, jobs))
-            wall = time.perf_counter() - t0
-            description = results[0][1]
-            # `cores` sequences advanced concurrently; each needs sum(seconds)/cores of wall time per sample
-            per_sequence = [1.0 / r[0] for r in results]            # scaled step seconds of one sequence
-            busy = sum(r[2] for r in results)
-            stretch = wall * cores / busy if busy > 0 else 1.0      # oversubscription / turbo effects
-            step_seconds = statistics.mean(per_sequence) * stretch
-            if i >= args.warmup:
-                values.append(cores / step_seconds)
-    elapsed = time.perf_counter() - begin
-    value = statistics.median(values)
-    sample = f"{cores} worker processes x ({description})"
-    line = {
+    value, baseline, step_seconds = cpu_baseline(shape, max(1, args.steps), max(1, args.warmup))
+    emit({
         "impl": "reference",
         "metric": METRIC,
         "value": value,
@@ -175,32 +260,31 @@ def run_reference(args):
         "n_gpus": args.gpus,
         "steps": args.steps,
         "warmup": args.warmup,
-        "ms_per_step": 1000.0 * elapsed / max(1, args.warmup + args.steps),
+        "ms_per_step": 1000.0 * step_seconds,
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "f32",
         "data": "synthetic",
-        "config": workload_config(args),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_config(args, shape),
+        "cpu_baseline": baseline,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    emit(line)
+    })
 
 
-def workload_config(args):
+def workload_config(args, shape):
     return {
-        "workload": f"config1 kernel sweep point: batch {args.batch} x context {args.context}, INT2 g{args.group} "
-                    f"residuals + INT4 g32 anchor, {args.layers} layers x 4 loops, {args.heads} heads x {args.head_dim}, block {args.page}, "
-                    "CUDA-graph decode step (4 attention + 1 quantize launch per layer)"
+        "workload": f"config1 kernel sweep point: batch {shape.batch} x context {shape.context}, INT2 g{shape.group} "
+                    f"residuals + INT4 g32 anchor, {shape.layers} layers x 4 loops, {shape.heads} heads x {shape.head_dim}, "
+                    f"block {shape.page}, CUDA-graph decode step (4 attention + 1 quantize launch per layer)"
                     + ("" if args.shard != "heads" else
                        "; KV heads sharded over the ranks, output rows stored into every GPU's gathered buffer by the attention "
-                       "kernel + one barrier kernel per call, captured in the graph" if args.gather == "fused" else
+                       "kernel, captured in the graph" if args.gather == "fused" else
                        "; KV heads sharded over the ranks, one NCCL all-gather of the output per attention call, eager step"),
-        "batch_per_gpu": args.batch,
+        "batch_per_gpu": shape.batch,
         "sharding": args.shard,
-        "context": args.context,
-        "layers": args.layers,
+        "context": shape.context,
+        "layers": shape.layers,
         "l2": "inputs larger than L2 (each layer's packed cache is read once per step)",
     }
 
@@ -257,54 +341,379 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
-def build_stack(args, device, torch):
+class Stack:
     """Packed caches of `layers` layers for `batch` sequences of `context` tokens (+ head room), filled by the
     quantizer kernel from seeded synthetic rows; every layer shares one block table, as under vLLM."""
-    from residualquant_b200 import _cuda, rotation, synth
 
-    records = [[2, args.group]] * 3 + [[4, 32]]
-    width = 3 * record_bytes(2, args.group) + record_bytes(4, 32)
-    head_room = 128
-    blocks_per_seq = (args.context + head_room + PAGE - 1) // PAGE
-    num_blocks = args.batch * blocks_per_seq + 1
-    rng = np.random.default_rng(1234 + int(os.environ.get("RANK", "0")))
-    pool = rng.permutation(num_blocks - 1) + 1          # block 0 stays unused, like vLLM's null block
-    table_np = pool.reshape(args.batch, blocks_per_seq).astype(np.int32)
-    block_table = torch.from_numpy(table_np).to(device)
-    key_rot = rotation.signed_hadamard(synth.signs(rng, HEADS, HEAD_DIM), float(synth.fp16_rsqrt(HEAD_DIM)), device)
-    value_rot = rotation.signed_hadamard(synth.signs(rng, HEADS, HEAD_DIM), float(synth.fp16_rsqrt(HEAD_DIM)), device)
+    def __init__(self, shape: Shape, device, torch, heads_here=None, seed_offset=0):
+        from residualquant_b200 import _cuda, rotation, synth
 
-    gen = torch.Generator(device=device)
-    gen.manual_seed(99 + int(os.environ.get("RANK", "0")))
-    channel_scale = torch.exp(0.5 * torch.randn(HEADS, HEAD_DIM, device=device, generator=gen))
-    outlier = torch.ones(HEADS, HEAD_DIM, device=device)
-    for h in range(HEADS):
-        outlier[h, torch.randperm(HEAD_DIM, device=device, generator=gen)[:4]] = 8.0
-    channel_scale = channel_scale * outlier
+        self.shape, self.device, self.torch = shape, device, torch
+        heads = shape.heads if heads_here is None else heads_here   # a head-sharded rank holds only its slice
+        self.heads = heads
+        D, P = shape.head_dim, shape.page
+        self.records = shape.records
+        head_room = 128
+        blocks_per_seq = (shape.context + head_room + P - 1) // P
+        num_blocks = shape.batch * blocks_per_seq + 1
+        rng = np.random.default_rng(1234 + seed_offset)
+        pool = rng.permutation(num_blocks - 1) + 1          # block 0 stays unused, like vLLM's null block
+        self.block_table = torch.from_numpy(pool.reshape(shape.batch, blocks_per_seq).astype(np.int32)).to(device)
+        self.key_rot = rotation.signed_hadamard(synth.signs(rng, heads, D), float(synth.fp16_rsqrt(D)), device)
 
-    def rows(tokens):
-        anchor = torch.randn(tokens, HEADS, HEAD_DIM, device=device, generator=gen) * channel_scale
-        loops = [(0.9 * anchor + 0.3 * torch.randn(tokens, HEADS, HEAD_DIM, device=device, generator=gen)).bfloat16()
-                 for _ in range(3)]
-        return loops + [anchor.bfloat16()]
+        gen = torch.Generator(device=device)
+        gen.manual_seed(99 + seed_offset)
+        channel_scale = torch.exp(0.5 * torch.randn(heads, D, device=device, generator=gen))
+        outlier = torch.ones(heads, D, device=device)
+        for h in range(heads):
+            outlier[h, torch.randperm(D, device=device, generator=gen)[:4]] = 8.0
+        channel_scale = channel_scale * outlier
 
-    caches = [torch.zeros((2, num_blocks, HEADS, PAGE, width), dtype=torch.uint8, device=device)]
-    # fill layer 0 sequence by sequence, then clone it into the other layers
-    positions = torch.arange(args.context, device=device)
-    for b in range(args.batch):
-        slots = block_table[b, positions // PAGE].long() * PAGE + positions % PAGE
-        k, v = rows(args.context), rows(args.context)
-        _cuda.quantize(list(zip(k, v)), caches[0], slots, key_rot, None, None, records, "anchor", 3, "ls")
-    torch.cuda.synchronize(device)
-    for _ in range(1, args.layers):
-        caches.append(caches[0].clone())
-    return {
-        "records": records, "caches": caches, "block_table": block_table, "key_rot": key_rot, "value_rot": value_rot,
-        "rows": rows, "width": width,
-    }
+        def rows(tokens):
+            anchor = torch.randn(tokens, heads, D, device=device, generator=gen) * channel_scale
+            loops = [(0.9 * anchor + 0.3 * torch.randn(tokens, heads, D, device=device, generator=gen)).bfloat16()
+                     for _ in range(3)]
+            return loops + [anchor.bfloat16()]
+
+        self.rows = rows
+        self.caches = [torch.zeros((2, num_blocks, heads, P, shape.width), dtype=torch.uint8, device=device)]
+        # fill layer 0 sequence by sequence, then clone it into the other layers
+        positions = torch.arange(shape.context, device=device)
+        for b in range(shape.batch):
+            slots = self.block_table[b, positions // P].long() * P + positions % P
+            k, v = rows(shape.context), rows(shape.context)
+            # The model's weights absorb the value rotation in the served configuration (weights.py:9-37 of the
+            # reference), so the kernels see value_rotation=None and V arrives rotated.
+            _cuda.quantize(list(zip(k, v)), self.caches[0], slots, self.key_rot, None, None, self.records, "anchor", 3, "ls")
+        torch.cuda.synchronize(device)
+        for _ in range(1, shape.layers):
+            self.caches.append(self.caches[0].clone())
+        L, B = shape.layers, shape.batch
+        # per (layer, loop) inputs of a step, device resident
+        self.q = torch.randn(L, 4, B, heads, D, device=device, generator=gen).bfloat16()
+        live = rows(B * L)
+        self.k_live = torch.stack([r.view(L, B, heads, D) for r in live], dim=1).contiguous()   # [layers, 4, B, H, D]
+        live = rows(B * L)
+        self.v_live = torch.stack([r.view(L, B, heads, D) for r in live], dim=1).contiguous()
+        self.out = torch.zeros_like(self.q)
+        self.qsl = torch.arange(B + 1, dtype=torch.int32, device=device)
+        self.seq_lens = torch.full((B,), shape.context, dtype=torch.int32, device=device)
+        self.slot_mapping = torch.zeros(B, dtype=torch.int64, device=device)
+        self.batch_index = torch.arange(B, device=device)
+
+    def advance(self):
+        # position of the live token = seq_len - 1; its slot is where this step's quantize writes
+        P = self.shape.page
+        position = (self.seq_lens - 1).long()
+        self.slot_mapping.copy_(self.block_table[self.batch_index, position // P].long() * P + position % P)
+
+    def attention(self, layer, loop, rows=None, seq_lens=None, qsl=None, **extra):
+        from residualquant_b200 import _cuda
+
+        rows = self.shape.batch if rows is None else rows
+        _cuda.attention(self.q[layer, loop, :rows], self.k_live[layer, loop, :rows], self.v_live[layer, loop, :rows],
+                        self.caches[layer], self.out[layer, loop, :rows], self.qsl if qsl is None else qsl,
+                        self.seq_lens if seq_lens is None else seq_lens, self.block_table[:rows], self.key_rot, None, None,
+                        self.records, "anchor", 3, loop, **extra)
+
+    def quantize(self, layer):
+        from residualquant_b200 import _cuda
+
+        _cuda.quantize([(self.k_live[layer, i], self.v_live[layer, i]) for i in range(4)], self.caches[layer],
+                       self.slot_mapping, self.key_rot, None, None, self.records, "anchor", 3, "ls")
 
 
-def run_gpu(args):
+class Timer:
+    """CUDA-event timing on a side stream, barrier + synchronize on both sides, maximum over the ranks."""
+
+    def __init__(self, torch, dist, device, world):
+        self.torch, self.dist, self.device, self.world = torch, dist, device, world
+        self.stream = torch.cuda.Stream(device)
+
+    def join_default_stream(self):
+        """Everything queued on the default stream (input tensors, lengths, tables) is complete before the side stream
+        reads it: a kernel that saw half-initialised lengths or block ids would read outside the cache."""
+        self.stream.wait_stream(self.torch.cuda.current_stream(self.device))
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.device)
+
+    def timed(self, fn, steps, collective=True):
+        from residualquant_b200 import sharding
+
+        torch = self.torch
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if collective:
+            self.barrier()
+        else:
+            torch.cuda.synchronize(self.device)
+        self.join_default_stream()
+        with torch.cuda.stream(self.stream):
+            start.record(self.stream)
+            for _ in range(steps):
+                fn()
+            stop.record(self.stream)
+        stop.synchronize()
+        if not collective:
+            return start.elapsed_time(stop)
+        self.barrier()
+        return sharding.max_over_ranks(start.elapsed_time(stop), self.device)
+
+    def capture(self, fn):
+        """Eager warm-up, then one CUDA graph of `fn`."""
+        torch = self.torch
+        self.join_default_stream()
+        with torch.cuda.stream(self.stream):
+            fn()
+        self.stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=self.stream):
+            fn()
+        return graph
+
+    def graph_ms(self, fn, replays, collective=False):
+        """Capture `fn` and time `replays` replays: per-kernel device time without the Python launch overhead."""
+        graph = self.capture(fn)
+        self.timed(graph.replay, 1, collective)
+        return self.timed(graph.replay, replays, collective) / replays
+
+
+def kernel_figures(timer, stack, peak, reps):
+    """Residual-loop and anchor-loop attention, decode write and prefill-sized write of one stack, each alone."""
+    torch, shape = stack.torch, stack.shape
+    L, B = shape.layers, shape.batch
+    stack.seq_lens.fill_(shape.context)
+    sized = replace(shape, heads=stack.heads)
+    out = {}
+    for name, loop in (("attention_residual_loop", 0), ("attention_anchor_loop", 3)):
+        ms = timer.graph_ms(lambda: [stack.attention(layer, loop) for layer in range(L)], reps) / L
+        nbytes = attention_bytes(B * (shape.context - 1), B, sized, loop == 3)
+        out[name] = {"us_per_launch": 1000 * ms, "algorithmic_bytes_per_launch": nbytes,
+                     "achieved": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+    stack.advance()
+    ms = timer.graph_ms(lambda: [stack.quantize(layer) for layer in range(L)], reps) / L
+    out["quantize_decode_write"] = {"tokens": B, "us_per_launch": 1000 * ms,
+                                    "achieved": quantize_bytes(B, sized) / (ms * 1e-3) / 1e9}
+    # prefill-sized write: two full prompts (2 x context tokens) of layer 0 re-quantized in one call
+    from residualquant_b200 import _cuda
+
+    prompts = min(2, B)
+    tokens = prompts * shape.context
+    pk, pv = stack.rows(tokens), stack.rows(tokens)
+    positions = torch.arange(shape.context, device=stack.device)
+    slots = torch.cat([stack.block_table[b, positions // shape.page].long() * shape.page + positions % shape.page
+                       for b in range(prompts)])
+    ms = timer.graph_ms(lambda: _cuda.quantize(list(zip(pk, pv)), stack.caches[0], slots, stack.key_rot, None, None,
+                                               stack.records, "anchor", 3, "ls"), 5)
+    nbytes = quantize_bytes(tokens, sized)
+    out["quantize_prefill_write"] = {"tokens": tokens, "us_per_launch": 1000 * ms, "achieved": nbytes / (ms * 1e-3) / 1e9,
+                                     "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+    return out
+
+
+def sweep_figures(timer, stack, peak, reps):
+    """Attention alone over the batch x context grid of the kernel-sweep configuration (one launch per layer, so every
+    launch reads a cache that the previous launches pushed out of L2)."""
+    torch, shape = stack.torch, stack.shape
+    rows_out = []
+    for batch in (1, 8, 32, 64):
+        if batch > shape.batch:
+            continue
+        for context in (2048, 4096, 8192):
+            if context > shape.context:
+                continue
+            lens = torch.full((batch,), context, dtype=torch.int32, device=stack.device)
+            starts = torch.arange(batch + 1, dtype=torch.int32, device=stack.device)
+            for loop in (0, 3):
+                ms = timer.graph_ms(lambda: [stack.attention(layer, loop, batch, lens, starts)
+                                             for layer in range(shape.layers)], reps) / shape.layers
+                nbytes = attention_bytes(batch * (context - 1), batch, shape, loop == 3)
+                rows_out.append({"batch": batch, "context": context, "loop": loop, "us": round(1000 * ms, 2),
+                                 "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                                 "frac": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4)})
+    return rows_out
+
+
+def decode_step_figures(timer, stack, reps):
+    """The latency protocol of the reference's own measurements (batch 1 at 2k / 4k / 8k): one whole decode step of the
+    stack (4 attention + 1 write launch per layer) under CUDA-graph replay."""
+    torch, shape = stack.torch, stack.shape
+    out = []
+    for context in (2048, 4096, 8192):
+        if context > shape.context:
+            continue
+        lens = torch.full((1,), context, dtype=torch.int32, device=stack.device)
+        starts = torch.arange(2, dtype=torch.int32, device=stack.device)
+        slot = (stack.block_table[:1, (context - 1) // shape.page].long() * shape.page + (context - 1) % shape.page)
+        from residualquant_b200 import _cuda
+
+        def step():
+            for layer in range(shape.layers):
+                for loop in range(4):
+                    stack.attention(layer, loop, 1, lens, starts)
+                _cuda.quantize([(stack.k_live[layer, i, :1], stack.v_live[layer, i, :1]) for i in range(4)],
+                               stack.caches[layer], slot, stack.key_rot, None, None, stack.records, "anchor", 3, "ls")
+        ms = timer.graph_ms(step, reps)
+        out.append({"batch": 1, "context": context, "ms_per_step": round(ms, 4), "tokens_per_s": round(1000.0 / ms, 1),
+                    "launches": 5 * shape.layers})
+    return out
+
+
+def ragged_figures(timer, stack, peak, reps, uniform_us):
+    """One 8192-token row among 63 rows of 17..600 tokens: what length-aware partitioning is for.  `implied_us` is the time
+    the batch's cached tokens would take at the rate of the uniform batch (same rows, every row at the full context)."""
+    torch, shape = stack.torch, stack.shape
+    if shape.batch < 64:
+        return None
+    rng = np.random.default_rng(7)
+    lengths = np.concatenate([[shape.context], rng.integers(17, 601, size=63)]).astype(np.int32)
+    lens = torch.from_numpy(lengths).to(stack.device)
+    starts = torch.arange(65, dtype=torch.int32, device=stack.device)
+    history = int((lengths - 1).sum())
+    out = {"rows": 64, "lengths": f"{shape.context} + 63 rows of 17..600 (seed 7), {history} cached tokens in all"}
+    for name, loop in (("residual_loop", 0), ("anchor_loop", 3)):
+        ms = timer.graph_ms(lambda: [stack.attention(layer, loop, 64, lens, starts) for layer in range(shape.layers)],
+                            reps) / shape.layers
+        implied = uniform_us[name] * history / (64 * (shape.context - 1))
+        out[name] = {"us": round(1000 * ms, 2), "implied_us": round(implied, 2), "ratio": round(1000 * ms / implied, 3),
+                     "frac": round(attention_bytes(history, 64, shape, loop == 3) / (ms * 1e-3) / 1e9 / peak, 4)}
+    return out
+
+
+def bf16_comparator(timer, stack, packed_ms_per_layer):
+    """One layer's four loop attentions over BF16 K/V of the same shape (contiguous [B, H, L, D], no paging, library
+    kernel): the comparator the packed path has to beat.  4 loops x (K + V) = 8 tensors of B*H*L*D bf16."""
+    torch, shape = stack.torch, stack.shape
+    import torch.nn.functional as F
+
+    B, H, L, D = shape.batch, shape.heads, shape.context, shape.head_dim
+    kv = [torch.randn(B, H, L, D, device=stack.device, dtype=torch.bfloat16) for _ in range(8)]
+    qb = torch.randn(4, B, H, 1, D, device=stack.device, dtype=torch.bfloat16)
+    ob = torch.empty_like(qb)
+
+    def bf16_layer():
+        for loop in range(4):
+            ob[loop] = F.scaled_dot_product_attention(qb[loop], kv[2 * loop], kv[2 * loop + 1])
+    ms = timer.graph_ms(bf16_layer, 5)
+    nbytes = 8 * B * H * L * D * 2
+    del kv
+    return {"kernel": "torch.nn.functional.scaled_dot_product_attention, contiguous BF16 KV, 4 loops of one layer",
+            "ms_per_layer": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "packed_ms_per_layer": packed_ms_per_layer,
+            "speedup": ms / packed_ms_per_layer, "bf16_kv_bytes_per_layer": nbytes,
+            "bf16_kv_bytes_whole_stack": nbytes * shape.layers}
+
+
+def reference_cuda_figures(timer, stack):
+    """The reference's own CUDA kernels (built from its sources by oracle/build_ref.py into oracle/_ref) beside this
+    library's, on one layer of the stack: same GPU, same packed cache, same inputs, CUDA-graph replay.  The reference takes
+    its rotation as a dense fp16 matrix (TF32 tensor-core product per call); this library is timed both ways: with the
+    same dense matrix ("dense") and with the fused Walsh-Hadamard transform the matrix's structure allows ("fwht")."""
+    if not glob.glob(os.path.join(REF_DIR, "_cuda*.so")):
+        return {"unavailable": "oracle/_ref holds no build of the reference's extension"}
+    torch, shape = stack.torch, stack.shape
+    from residualquant_b200 import _cuda
+
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    try:
+        import _cuda as reference   # the reference's module name
+    except Exception as error:      # built against another torch, missing symbols, ...
+        return {"unavailable": f"import failed: {error}"[:200]}
+    B, P = shape.batch, shape.page
+    dense = stack.key_rot.dense()
+    q, k, v = stack.q[0, 0], stack.k_live[0, 0], stack.v_live[0, 0]
+    cache = stack.caches[0]
+    stack.seq_lens.fill_(shape.context)
+    stack.advance()
+    torch.cuda.synchronize(stack.device)
+    live_pairs = [(stack.k_live[0, i], stack.v_live[0, i]) for i in range(4)]
+    prompts = min(2, B)
+    tokens = prompts * (shape.context - 1)
+    positions = torch.arange(shape.context - 1, device=stack.device)
+    prompt_slots = torch.cat([stack.block_table[b, positions // P].long() * P + positions % P for b in range(prompts)])
+    pk, pv = stack.rows(tokens), stack.rows(tokens)
+    prompt_pairs = list(zip(pk, pv))
+    scratch = cache.clone()
+    out_ref, out_ours = torch.zeros_like(q), torch.zeros_like(q)
+    figures = {"shape": f"batch {B} x context {shape.context}, one layer, {shape.heads} heads x {shape.head_dim}, g{shape.group}",
+               "note": "us per call under CUDA-graph replay; the caches of consecutive replays are the same, larger than L2 "
+                       "for batch >= 8"}
+
+    def attention_of(module, rotation, out, loop):
+        return lambda: module.attention(q, k, v, cache, out, stack.qsl, stack.seq_lens, stack.block_table, rotation, None,
+                                        None, stack.records, "anchor", 3, loop)
+
+    def quantize_of(module, rotation, pairs, slots):
+        return lambda: module.quantize(pairs, scratch, slots, rotation, None, None, stack.records, "anchor", 3, "ls")
+
+    try:
+        for name, loop in (("attention_residual_us", 0), ("attention_anchor_us", 3)):
+            figures[name] = {
+                "reference": round(1000 * timer.graph_ms(attention_of(reference, dense, out_ref, loop), 5), 2),
+                "this_dense": round(1000 * timer.graph_ms(attention_of(_cuda, dense, out_ours, loop), 5), 2),
+                "this_fwht": round(1000 * timer.graph_ms(attention_of(_cuda, stack.key_rot, out_ours, loop), 5), 2),
+            }
+            figures[name]["outputs_rms_difference"] = float((out_ref.float() - out_ours.float()).pow(2).mean().sqrt())
+        for name, pairs, slots in (("quantize_decode_us", live_pairs, stack.slot_mapping),
+                                   ("quantize_prefill_us", prompt_pairs, prompt_slots)):
+            figures[name] = {
+                "tokens": int(slots.numel()),
+                "reference": round(1000 * timer.graph_ms(quantize_of(reference, dense, pairs, slots), 3), 2),
+                "this_dense": round(1000 * timer.graph_ms(quantize_of(_cuda, dense, pairs, slots), 3), 2),
+                "this_fwht": round(1000 * timer.graph_ms(quantize_of(_cuda, stack.key_rot, pairs, slots), 3), 2),
+            }
+    except RuntimeError as error:
+        figures["unavailable"] = f"{error}"[:200]
+    return figures
+
+
+def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup):
+    """BASELINE's largest configuration's kernel shape (55 heads x 96, batch 16 at context 4096, 4 core layers x 8 groups
+    = 32 caches, 128 attention calls per step) with the KV heads spread over the ranks: strong scaling.  Every rank
+    stores its finished rows into every GPU's gathered output from inside the attention kernel; the whole step is one
+    CUDA graph per rank."""
+    from residualquant_b200 import sharding
+
+    shape = Shape(batch=16, context=4096, layers=32, heads=55, head_dim=96, page=16, group=32)
+    local = sharding.shard_counts(shape.heads, world)[rank]
+    stack = Stack(shape, device, torch, heads_here=local, seed_offset=1000 + rank)
+    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
+
+    def step():
+        stack.advance()
+        for layer in range(shape.layers):
+            for loop in range(4):
+                stack.attention(layer, loop, gather=gather, gather_buffer=loop % 2)
+                gather.barrier()
+            stack.quantize(layer)
+        stack.seq_lens.add_(1)
+
+    graph = timer.capture(step)
+    stack.seq_lens.fill_(shape.context)
+    timer.join_default_stream()
+    with torch.cuda.stream(timer.stream):
+        for _ in range(warmup):
+            graph.replay()
+    ms = timer.timed(graph.replay, steps)
+    gather.check()
+    expected = sharding.gather_heads(stack.out[shape.layers - 1, 3], shape.heads)
+    equal = bool(torch.equal(gather.gathered(3 % 2), expected))
+    flags = torch.tensor([1 if equal else 0], device=device)
+    if world > 1:
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 32 write launches "
+                       "per step, INT2 g32 + INT4 g32",
+              "n": world, "heads_per_rank": sharding.shard_counts(shape.heads, world),
+              "tokens_per_s": shape.batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
+              "gathered_equal_nccl": bool(flags.item() == 1), "scaling": "strong"}
+    del stack, gather
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_gpu(args, shape):
     import torch
     import torch.distributed as dist
 
@@ -326,132 +735,80 @@ def run_gpu(args):
     else:
         kernel_build.build()
 
-    global HEADS
-    heads_total = args.heads
     shard_heads = args.shard == "heads"
+    heads_here = None
     if shard_heads:
-        HEADS = sharding.shard_counts(heads_total, world)[rank]   # this rank's slice of every cache and of q/k/v
-        if HEADS == 0:
+        heads_here = sharding.shard_counts(shape.heads, world)[rank]   # this rank's slice of every cache and of q/k/v
+        if heads_here == 0:
             raise RuntimeError("more ranks than KV heads")
     replicas = 1 if shard_heads else world                          # independent copies of the batch in the job
-    B, L, layers = args.batch, args.context, args.layers
+    B, L, layers = shape.batch, shape.context, shape.layers
     _cuda.set_attention_splits(args.splits)
-    stack = build_stack(args, device, torch)
-    records, caches = stack["records"], stack["caches"]
-    # The model's weights absorb the value rotation in the served configuration (weights.py:9-37 of the reference),
-    # so the kernels see value_rotation=None and V arrives rotated.
-    key_rot = stack["key_rot"]
-    block_table = stack["block_table"]
-
-    # per (layer, loop) inputs of a step, device resident
-    q = torch.randn(layers, 4, B, HEADS, HEAD_DIM, device=device).bfloat16()
-    live = stack["rows"](B * layers)
-    k_live = torch.stack([r.view(layers, B, HEADS, HEAD_DIM) for r in live], dim=1).contiguous()   # [layers, 4, B, H, D]
-    live = stack["rows"](B * layers)
-    v_live = torch.stack([r.view(layers, B, HEADS, HEAD_DIM) for r in live], dim=1).contiguous()
-    out = torch.zeros_like(q)
-    qsl = torch.arange(B + 1, dtype=torch.int32, device=device)
-    seq_lens = torch.full((B,), L, dtype=torch.int32, device=device)
-    slot_mapping = torch.zeros(B, dtype=torch.int64, device=device)
-    batch_index = torch.arange(B, device=device)
-
-    def advance():
-        # position of the live token = seq_len - 1; its slot is where this step's quantize writes
-        position = (seq_lens - 1).long()
-        slot_mapping.copy_(block_table[batch_index, position // PAGE].long() * PAGE + position % PAGE)
+    timer = Timer(torch, dist, device, world)
+    stack = Stack(shape, device, torch, heads_here, seed_offset=rank)
+    peak, peak_kind = measured_peak()
 
     gathered = [None]
     # Head sharding: the output projection needs every head.  "fused": the attention kernel stores its rows into every
-    # GPU's gathered buffer over NVLink and a barrier kernel follows (graph capturable); "nccl": one all-gather per call.
-    fused_gather = sharding.HeadGather(B, heads_total, HEAD_DIM, device) if shard_heads and args.gather == "fused" else None
+    # GPU's gathered buffer over NVLink (graph capturable); "nccl": one all-gather per call.
+    fused_gather = sharding.HeadGather(B, shape.heads, shape.head_dim, device) if shard_heads and args.gather == "fused" else None
 
     def hot_path():
         for layer in range(layers):
             for loop in range(4):
                 if fused_gather is not None:
-                    _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer],
-                                    out[layer, loop], qsl, seq_lens, block_table, key_rot, None, None, records,
-                                    "anchor", 3, loop, gather=fused_gather, gather_buffer=loop % 2)
+                    stack.attention(layer, loop, gather=fused_gather, gather_buffer=loop % 2)
                     fused_gather.barrier()
                     continue
-                _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer], out[layer, loop],
-                                qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
+                stack.attention(layer, loop)
                 if shard_heads:
-                    gathered[0] = sharding.gather_heads(out[layer, loop], heads_total)
-            _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
-                           key_rot, None, None, records, "anchor", 3, "ls")
+                    gathered[0] = sharding.gather_heads(stack.out[layer, loop], shape.heads)
+            stack.quantize(layer)
 
     def step_body():
-        advance()
+        stack.advance()
         hot_path()
-        seq_lens.add_(1)
+        stack.seq_lens.add_(1)
 
-    stream = torch.cuda.Stream(device)
-
-    def join_default_stream():
-        """Everything queued on the default stream (input tensors, lengths, tables) is complete before the side stream
-        reads it: a kernel that saw half-initialised lengths or block ids would read outside the cache."""
-        stream.wait_stream(torch.cuda.current_stream(device))
-
-    join_default_stream()
-    with torch.cuda.stream(stream):
-        step_body()                      # eager warm-up: workspace, per-variant attributes
-    stream.synchronize()
-    seq_lens.fill_(L)
     if shard_heads and world > 1 and fused_gather is None:
         # The step contains NCCL all-gathers; it is replayed eagerly rather than from a captured graph.
+        timer.join_default_stream()
+        with torch.cuda.stream(timer.stream):
+            step_body()
+        timer.stream.synchronize()
+
         class _Eager:
             @staticmethod
             def replay():
                 step_body()
         graph = _Eager()
     else:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step_body()
-    seq_lens.fill_(L)
+        graph = timer.capture(step_body)
+    stack.seq_lens.fill_(L)
     torch.cuda.synchronize(device)
     launches_per_step = layers * (9 if fused_gather is not None else 5)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(device)
-
-    def timed(fn, steps):
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        join_default_stream()
-        with torch.cuda.stream(stream):
-            start.record(stream)
-            for _ in range(steps):
-                fn()
-            stop.record(stream)
-        stop.synchronize()
-        barrier()
-        return sharding.max_over_ranks(start.elapsed_time(stop), device)
-
     sampler = ClockSampler(local_rank)
     # ---------------- device-resident throughput ----------------
-    join_default_stream()
-    with torch.cuda.stream(stream):
+    timer.join_default_stream()
+    with torch.cuda.stream(timer.stream):
         for _ in range(args.warmup):
             graph.replay()
     if rank == 0:
         sampler.start()
-    ms = timed(graph.replay, args.steps)
+    ms = timer.timed(graph.replay, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     if fused_gather is not None:
         # the gathered rows of the last call must equal an NCCL all-gather of every rank's own output
         fused_gather.check()
-        last = out[layers - 1, 3]
-        expected = sharding.gather_heads(last, heads_total)
+        expected = sharding.gather_heads(stack.out[layers - 1, 3], shape.heads)
         if not torch.equal(fused_gather.gathered(3 % 2), expected):
             raise RuntimeError("fused head gather differs from the all-gathered outputs")
     value = replicas * B * args.steps / (ms * 1e-3)
 
     # ---------------- end to end: host rows in, outputs back ----------------
-    seq_lens.fill_(L)
+    stack.seq_lens.fill_(L)
+    q, k_live, v_live, out = stack.q, stack.k_live, stack.v_live, stack.out
     host_q = torch.empty(q.shape, dtype=q.dtype).pin_memory().copy_(q)
     host_k = torch.empty(k_live.shape, dtype=q.dtype).pin_memory().copy_(k_live)
     host_v = torch.empty(v_live.shape, dtype=q.dtype).pin_memory().copy_(v_live)
@@ -464,118 +821,70 @@ def run_gpu(args):
         q.copy_(host_q, non_blocking=True)
         k_live.copy_(host_k, non_blocking=True)
         v_live.copy_(host_v, non_blocking=True)
-        seq_lens.copy_(host_lens, non_blocking=True)
+        stack.seq_lens.copy_(host_lens, non_blocking=True)
         graph.replay()
         host_out.copy_(out, non_blocking=True)
         host_lens.add_(1)
 
-    join_default_stream()
-    with torch.cuda.stream(stream):
+    timer.join_default_stream()
+    with torch.cuda.stream(timer.stream):
         for _ in range(args.warmup):
             e2e_step()
-    stream.synchronize()
+    timer.stream.synchronize()
     host_lens.fill_(L)
-    ms_e2e = timed(e2e_step, args.steps)
+    ms_e2e = timer.timed(e2e_step, args.steps)
     e2e_value = replicas * B * args.steps / (ms_e2e * 1e-3)
+    del host_q, host_k, host_v, host_out
 
-    # ---------------- dominant kernel alone: attention of a residual loop, one launch per layer ----------------
-    seq_lens.fill_(L)
-
-    def attention_only(loop):
-        def run():
-            for layer in range(layers):
-                _cuda.attention(q[layer, loop], k_live[layer, loop], v_live[layer, loop], caches[layer], out[layer, loop],
-                                qsl, seq_lens, block_table, key_rot, None, None, records, "anchor", 3, loop)
-        return run
-
-    def graph_timed(fn, replays):
-        """Capture `fn` once (after an eager warm-up) and time `replays` replays: per-kernel device time without
-        the Python launch overhead of eager calls."""
-        join_default_stream()
-        with torch.cuda.stream(stream):
-            fn()
-        stream.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
-            fn()
-        timed(g.replay, 1)
-        return timed(g.replay, replays)
-
+    # ---------------- every kernel alone ----------------
     reps = max(3, 48 // layers)
-    ms_res = graph_timed(attention_only(0), reps) / (reps * layers)
-    ms_anchor = graph_timed(attention_only(3), reps) / (reps * layers)
-    bytes_res = attention_bytes(B, L, args.group, False)
-    bytes_anchor = attention_bytes(B, L, args.group, True)
-    peak, peak_kind = measured_peak()
-    achieved = bytes_res / (ms_res * 1e-3) / 1e9
-
-    def quantize_only():
-        for layer in range(layers):
-            _cuda.quantize([(k_live[layer, i], v_live[layer, i]) for i in range(4)], caches[layer], slot_mapping,
-                           key_rot, None, None, records, "anchor", 3, "ls")
-    ms_quant = graph_timed(quantize_only, reps) / (reps * layers)
-
-    # prefill-sized write: two full prompts (2 x context tokens) of layer 0 re-quantized in one call
-    prefill_tokens = min(2, B) * L
-    pk, pv = stack["rows"](prefill_tokens), stack["rows"](prefill_tokens)
-    positions = torch.arange(L, device=device)
-    prefill_slots = torch.cat([block_table[b, positions // PAGE].long() * PAGE + positions % PAGE
-                               for b in range(min(2, B))])
-
-    def quantize_prefill():
-        _cuda.quantize(list(zip(pk, pv)), caches[0], prefill_slots, key_rot, None, None, records, "anchor", 3, "ls")
-    ms_prefill = graph_timed(quantize_prefill, 5) / 5
-    del pk, pv
+    kernels = kernel_figures(timer, stack, peak, reps)
+    residual, anchor = kernels["attention_residual_loop"], kernels["attention_anchor_loop"]
     _cuda.attention_status(device)
 
-    bf16 = None
-    if args.compare_bf16 and rank == 0:
-        # One layer's four loop attentions over BF16 K/V of the same shape (contiguous [B, H, L, D], no paging, library
-        # kernel): the comparator the packed path has to beat.  4 loops x (K + V) = 8 tensors of B*H*L*D bf16.
-        import torch.nn.functional as F
-        kv = [torch.randn(B, HEADS, L, HEAD_DIM, device=device, dtype=torch.bfloat16) for _ in range(8)]
-        qb = torch.randn(4, B, HEADS, 1, HEAD_DIM, device=device, dtype=torch.bfloat16)
-        ob = torch.empty_like(qb)
-
-        def bf16_layer():
-            for loop in range(4):
-                ob[loop] = F.scaled_dot_product_attention(qb[loop], kv[2 * loop], kv[2 * loop + 1])
-        ms_bf16 = graph_timed(bf16_layer, 5) / 5
-        bytes_bf16 = 8 * B * HEADS * L * HEAD_DIM * 2
-        packed_layer_ms = 3 * ms_res + ms_anchor + ms_quant
-        bf16 = {"kernel": "torch.nn.functional.scaled_dot_product_attention, contiguous BF16 KV, 4 loops of one layer",
-                "ms_per_layer": ms_bf16, "gbs": bytes_bf16 / (ms_bf16 * 1e-3) / 1e9,
-                "packed_ms_per_layer": packed_layer_ms, "speedup": ms_bf16 / packed_layer_ms,
-                "bf16_kv_bytes_per_layer": bytes_bf16}
-        del kv
-
-    sweep = None
-    if args.sweep and rank == 0:
-        sweep = []
-        for batch in (1, 8, 32, 64):
-            if batch > B:
-                continue
-            for context in (2048, 4096, 8192):
-                if context > L:
-                    continue
-                lens = torch.full((batch,), context, dtype=torch.int32, device=device)
-                starts = torch.arange(batch + 1, dtype=torch.int32, device=device)
-                for loop in (0, 3):
-                    def run():
-                        for layer in range(layers):
-                            _cuda.attention(q[layer, loop, :batch], k_live[layer, loop, :batch], v_live[layer, loop, :batch],
-                                            caches[layer], out[layer, loop, :batch], starts, lens, block_table[:batch],
-                                            key_rot, None, None, records, "anchor", 3, loop)
-                    t = graph_timed(run, reps) / (reps * layers)
-                    nbytes = attention_bytes(batch, context, args.group, loop == 3)
-                    sweep.append({"batch": batch, "context": context, "loop": loop, "us": 1000 * t,
-                                  "gbs": nbytes / (t * 1e-3) / 1e9, "frac": nbytes / (t * 1e-3) / 1e9 / peak})
+    extras = {}
+    full = not args.quick and not shard_heads
+    if full and rank == 0 and world == 1:
+        # Only the single-GPU run carries the side measurements; a multi-GPU launch reports scaling.
+        extras["sweep"] = sweep_figures(timer, stack, peak, reps)
+        extras["decode_step_batch1"] = decode_step_figures(timer, stack, reps)
+        ragged = ragged_figures(timer, stack, peak, reps, {"residual_loop": residual["us_per_launch"],
+                                                            "anchor_loop": anchor["us_per_launch"]})
+        if ragged is not None:
+            extras["ragged"] = ragged
+        packed_layer_ms = (3 * residual["us_per_launch"] + anchor["us_per_launch"]
+                           + kernels["quantize_decode_write"]["us_per_launch"]) / 1000.0
+        extras["reference_cuda"] = reference_cuda_figures(timer, stack)
+        if shape.batch * shape.heads * shape.context * shape.head_dim * 16 < 40e9:
+            extras["bf16_kv_comparator"] = bf16_comparator(timer, stack, packed_layer_ms)
+    if full and world > 1:
+        # every rank takes part; rank 0 reports
+        del stack
+        stack = None
+        torch.cuda.empty_cache()
+        extras["head_sharded"] = head_sharded_figures(timer, torch, dist, device, rank, world, args.steps, args.warmup)
+    if full and rank == 0 and world == 1:
+        del stack
+        stack = None
+        torch.cuda.empty_cache()
+        other = {}
+        for name, variant in (("g16", replace(shape, group=16, layers=min(4, layers))),
+                              ("huginn_55x96", Shape(batch=16, context=4096, layers=8, heads=55, head_dim=96, page=16, group=32))):
+            s = Stack(variant, device, torch, seed_offset=17)
+            figures = kernel_figures(timer, s, peak, 3)
+            figures["shape"] = (f"batch {variant.batch} x context {variant.context}, {variant.heads} heads x "
+                                f"{variant.head_dim}, g{variant.group}, {variant.layers} layers")
+            other[name] = figures
+            del s
+            torch.cuda.empty_cache()
+        extras["other_shapes"] = other
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
+    achieved = residual["achieved"]
     line = {
         "metric": METRIC,
         "value": value,
@@ -589,7 +898,7 @@ def run_gpu(args):
         "vs_baseline": None,
         "dtype": "f16 dot products and value sums with fp32 softmax/accumulation (attention); f32 (quantizer)",
         "data": "synthetic",
-        "config": workload_config(args),
+        "config": workload_config(args, shape),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / args.steps},
@@ -599,23 +908,17 @@ def run_gpu(args):
             "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
             # DRAM bytes per launch = algorithmic bytes x 1.128, the ratio ncu measured on a smaller launch of the same
             # kernel (profiles/attention_kernel_b32_ctx8192.md); traffic grows in proportion to the tokens read
-            "traffic": 1.128 * bytes_res, "algorithmic_bytes_per_launch": bytes_res, "us_per_launch": 1000 * ms_res,
-            "anchor_loop": {"us_per_launch": 1000 * ms_anchor, "achieved": bytes_anchor / (ms_anchor * 1e-3) / 1e9,
-                            "frac": bytes_anchor / (ms_anchor * 1e-3) / 1e9 / peak},
-            "quantize_decode_write": {"us_per_launch": 1000 * ms_quant,
-                                      "achieved": quantize_bytes(B, args.group) / (ms_quant * 1e-3) / 1e9},
-            "quantize_prefill_write": {"tokens": prefill_tokens, "us_per_launch": 1000 * ms_prefill,
-                                       "achieved": quantize_bytes(prefill_tokens, args.group) / (ms_prefill * 1e-3) / 1e9,
-                                       "frac": quantize_bytes(prefill_tokens, args.group) / (ms_prefill * 1e-3) / 1e9 / peak},
+            "traffic": 1.128 * residual["algorithmic_bytes_per_launch"],
+            "algorithmic_bytes_per_launch": residual["algorithmic_bytes_per_launch"],
+            "us_per_launch": residual["us_per_launch"],
+            "anchor_loop": {k: anchor[k] for k in ("us_per_launch", "achieved", "frac")},
+            "quantize_decode_write": kernels["quantize_decode_write"],
+            "quantize_prefill_write": kernels["quantize_prefill_write"],
         },
     }
-    if sweep is not None:
-        line["sweep"] = sweep
-    if bf16 is not None:
-        line["bf16_kv_comparator"] = bf16
-    if not args.no_cpu_baseline:
-        cpu_value, description, _ = cpu_sample(L, args.group, layers, B, sample_context=min(L, 4096))  # 5-20 s of CPU work
-        line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port", "sample": description}
+    line.update(extras)
+    if not args.no_cpu_baseline and not args.quick:
+        _, line["cpu_baseline"], _ = cpu_baseline(shape)
     emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -635,18 +938,19 @@ def emit(line: dict) -> None:
 
 
 def main():
-    global HEADS, HEAD_DIM, PAGE, _result_stream
+    global _result_stream
     args = parse_args()
-    HEADS, HEAD_DIM, PAGE = args.heads, args.head_dim, args.page
+    shape = Shape(batch=args.batch, context=args.context, layers=args.layers, heads=args.heads, head_dim=args.head_dim,
+                  page=args.page, group=args.group)
     # Libraries print to file descriptor 1 on their own (NCCL announces its version there): keep the real standard
     # output for the result line and send everything else to standard error.
     sys.stdout.flush()
     _result_stream = os.dup(1)
     os.dup2(2, 1)
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, shape)
     else:
-        run_gpu(args)
+        run_gpu(args, shape)
 
 
 if __name__ == "__main__":

@@ -35,6 +35,18 @@ extern "C" {
 #define RQ_MAX_RECORDS 8
 #define RQ_MAX_PEERS 8 /* GPUs of one node that a head-sharded output can be stored to */
 
+/* RqQuantizeArgs.flags / RqAttentionArgs.flags.
+ * By default both kernels are launched as PROGRAMMATIC DEPENDENTS of the previous kernel of the stream
+ * (cudaLaunchAttributeProgrammaticStreamSerialization): the part of the kernel that only reads -- metadata, cache
+ * pages, the K/V/Q rows -- may start while that previous kernel is still running if, and only if, that kernel signals
+ * early; every write of this library's kernels is ordered behind the previous kernel's completion by
+ * griddepcontrol.wait.  The only kernel of this library that signals early is the attention kernel, so the rule a
+ * caller has to know is: do not pass the OUTPUT (or the workspace) of one rq_attention call as an INPUT tensor of the
+ * rq_attention / rq_quantize call that follows it directly on the same stream.  (Model code never does: a projection
+ * sits in between.)  RQ_FLAG_SERIAL_LAUNCH launches the call with plain stream order instead;
+ * rq_set_programmatic_launch(0) or RQ_PROGRAMMATIC_LAUNCH=0 in the environment does so for every call. */
+#define RQ_FLAG_SERIAL_LAUNCH 1
+
 typedef enum RqStatus {
     RQ_OK = 0,
     RQ_ERR_INVALID_ARGUMENT = -1, /* a shape, pointer, alignment or enum is wrong (the TORCH_CHECKs of api.cpp) */
@@ -113,6 +125,7 @@ typedef struct RqQuantizeArgs {
     void* stream;
     void* workspace;         /* only for RQ_ROTATION_DENSE_FP16: rq_quantize_workspace_bytes() bytes, 16-byte aligned */
     size_t workspace_bytes;
+    int32_t flags;           /* RQ_FLAG_* */
 } RqQuantizeArgs;
 
 /* Scratch a quantize call needs: fp32 copies of the rotated rows of every plane whose rotation is dense
@@ -147,7 +160,9 @@ typedef struct RqAttentionArgs {
     RqRotation value_rotation;      /* kind NONE when the model's weights absorbed it (weights.py:9-37) */
     const float* key_mean;          /* fp32 [num_records][heads][head_dim], rotated coordinates, or NULL */
     int32_t loop_index;             /* which record of the group this layer slot reads, 0 <= loop < num_records */
-    int32_t num_splits;             /* KV partitions per query row; 0 = let rq_attention_default_splits choose */
+    int32_t num_splits;             /* 0 = the kernel cuts every row into KV partitions in proportion to its OWN length, read
+                                       on the device (the reference's per-call schedule, attention/prepare.cuh:237-386);
+                                       n > 0 = exactly n partitions for every row */
     void* workspace;                /* rq_attention_workspace_bytes() bytes, 256-byte aligned, zeroed once with
                                        rq_attention_workspace_init() before its first use */
     size_t workspace_bytes;
@@ -162,14 +177,21 @@ typedef struct RqAttentionArgs {
     int32_t gather_head_offset;      /* first head of this rank inside a gathered row */
     int64_t gather_stride;           /* ELEMENTS between rows of the gathered buffers (>= total heads * head_dim) */
     void* peer_output[RQ_MAX_PEERS];
+    int32_t flags;                   /* RQ_FLAG_* */
 } RqAttentionArgs;
 
-/* Partition count the library would pick for this shape on the current device (a pure host function of its
- * arguments and the SM count, so it is stable across CUDA-graph replays). */
+/* A uniform partition count for callers that want to force one (num_splits > 0): what a host-side cost model picks
+ * for a batch whose rows all span max_blocks_per_request pages.  rq_attention does not use it when num_splits == 0. */
 int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32_t max_blocks_per_request,
                                     int32_t page_tokens);
-/* Bytes of scratch one rq_attention call needs: per-partition (max, denominator, value sums), one arrival
- * counter per (row, head), a status word and room for the densely rotated query rows.  The reference allocates the equivalent per call
+/* Work items (row partitions) per head that a num_splits == 0 call provides for: the rows plus spare items that long
+ * rows are cut into.  A pure host function of its arguments and the SM count -- never of sequence lengths or of the
+ * page-table width -- so the grid is stable across CUDA-graph replays (attention/launch.cuh:53-80 of the reference
+ * sizes its work list the same way). */
+int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads);
+/* Bytes of scratch one rq_attention call needs: per-work-item (max, denominator, value sums), one arrival
+ * counter per (row, head), a status word and room for the densely rotated query rows.  num_splits as in
+ * RqAttentionArgs (0 = sized for rq_attention_work_capacity()).  The reference allocates the equivalent per call
  * (attention/launch.cuh:85-98). */
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits);
 /* Zero the counters and the status word (asynchronous, on `stream`).  Needed once per workspace; every call
@@ -178,8 +200,12 @@ int32_t rq_attention_workspace_init(void* workspace, size_t workspace_bytes, voi
 /* Split-KV online-softmax decode attention over the packed pages.  One launch. */
 int32_t rq_attention(const RqAttentionArgs* args);
 /* Synchronizes `stream` and reads the workspace status word: RQ_OK, or RQ_ERR_DEVICE_TIMEOUT if a bounded
- * wait inside the kernel ever gave up since the last init (outputs of that call are then undefined). */
+ * wait inside the kernel ever gave up since the last init (outputs of that call are then undefined).  Only the
+ * bulk-copy build of the kernel (RQ_ATTENTION_BULK_COPY=1) contains such a wait; the default build stages pages with
+ * cp.async commit groups, which cannot time out, and never raises the word. */
 int32_t rq_attention_status(const void* workspace, void* stream);
+/* Process-wide switch for the programmatic dependent launch described at RQ_FLAG_SERIAL_LAUNCH (default on). */
+void rq_set_programmatic_launch(int32_t enabled);
 
 /* Maximum scratch rq_attention_noalloc can serve: the size of the library's built-in device buffer. */
 #define RQ_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
@@ -190,12 +216,16 @@ int32_t rq_attention_status(const void* workspace, void* stream);
  * counters live in a buffer of RQ_STATIC_SCRATCH_BYTES that is compiled into the library as device memory, so every
  * GPU that loads the library holds those 8 MiB until the process exits.  A shape whose
  * rq_attention_workspace_bytes() exceeds that size is rejected with RQ_ERR_WORKSPACE.  The call makes no
- * cudaMalloc/cudaFree and uses no allocating library.  The first call on each device looks up the buffer's
- * device address (with that device current) and should therefore be made before any stream capture begins.
- * Every call clears the status word and the counters it is about to use, on `stream`, before the kernel.  All
+ * cudaMalloc/cudaFree and uses no allocating library.  The first call on each device (whichever thread makes it)
+ * looks up the buffer's device address, with that device current, and should therefore be made before any stream
+ * capture begins.  Every call clears the status word and the counters it is about to use, on `stream`, before the
+ * kernel, and launches the kernel in plain stream order (RQ_FLAG_SERIAL_LAUNCH).  All
  * calls on a device share the one buffer: two calls whose kernels overlap on the GPU (different streams) race;
  * keep them on one stream or order them with events. */
 int32_t rq_attention_noalloc(const RqAttentionArgs* args);
+/* rq_attention_status() for the built-in buffer of the current device (callers of rq_attention_noalloc never see
+ * its address). */
+int32_t rq_attention_noalloc_status(void* stream);
 
 /* Barrier between the GPUs of one node, for the fused output gather above: a one-CTA kernel on `stream` that publishes
  * this rank's arrival in every peer's flag array (system-scope release store over NVLink) and then waits until every

@@ -9,12 +9,19 @@ reference's own binding.cpp links unchanged.  Output: oracle/_ref/_cuda*.so, imp
 reference's `attention(...)` and `quantize(...)`.
 
     python oracle/build_ref.py <reference checkout> [family ...]     # default family: ouro_anchor_3_g32
+    python oracle/build_ref.py <reference checkout> --python-only    # only the PyTorch statement (seconds)
+
+Besides the extension, `place_python` puts the reference's PyTorch statement of the same maths
+(scripts/calibration/{quantization,rotation_math,rotation_training}.py: FP32Chain.reconstruct, probabilities) under
+oracle/_ref/py/calibration/, so that the benchmark machine -- which has no checkout -- can time the reference's own CPU
+path.  oracle/_ref/ is a build product: git-ignored, never part of the repository's history.
 """
 
 from __future__ import annotations
 
 import concurrent.futures
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
@@ -23,6 +30,22 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 FAMILIES = [f"{model}_{mode}_{group}" for model in ("ouro", "huginn")
             for mode in ("anchor_0", "anchor_3", "adjacent_0") for group in ("g16", "g32")]
+
+
+PYTHON_FILES = ("quantization.py", "rotation_math.py", "rotation_training.py")
+
+
+def place_python(reference: str) -> str:
+    """Copy the reference's three calibration modules into oracle/_ref/py/calibration/ (importable as `calibration.*`
+    with oracle/_ref/py on sys.path, the package name their own imports use)."""
+    source = os.path.join(reference, "scripts", "calibration")
+    if not all(os.path.isfile(os.path.join(source, name)) for name in PYTHON_FILES):
+        raise SystemExit(f"{source} does not hold {PYTHON_FILES}")
+    target = os.path.join(OUT, "py", "calibration")
+    os.makedirs(target, exist_ok=True)
+    for name in PYTHON_FILES:
+        shutil.copyfile(os.path.join(source, name), os.path.join(target, name))
+    return target
 
 
 def main(reference: str, families) -> str:
@@ -89,4 +112,6 @@ def main(reference: str, families) -> str:
 if __name__ == "__main__":
     if len(sys.argv) < 2:
         raise SystemExit(__doc__)
-    print(main(sys.argv[1], sys.argv[2:] or ["ouro_anchor_3_g32"]))
+    print(place_python(sys.argv[1]))
+    if "--python-only" not in sys.argv[2:]:
+        print(main(sys.argv[1], [a for a in sys.argv[2:] if not a.startswith("--")] or ["ouro_anchor_3_g32"]))

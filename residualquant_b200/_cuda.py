@@ -8,10 +8,12 @@ Differences a caller can see:
     `SignedHadamardRotation`.  A tensor that was passed once to `residualquant_b200.rotation.register_rotation` and
     recognised as diag(+-1) @ Hadamard runs the fused Walsh-Hadamard path; any other matrix is rotated by a
     tensor-core launch (TF32 products like the reference) in front of the quantizer / attention kernel.
-  * scratch memory for the split-KV merge comes from one cached buffer per (device, size) instead of five
-    allocations per call (attention/launch.cuh:85-98); under CUDA-graph capture the buffer is whatever was
-    cached before capture began, so warm up once before capturing, as the reference does
-    (install_cache.py:187-256).
+  * scratch memory for the split-KV merge comes from one cached buffer per device instead of five allocations per
+    call (attention/launch.cuh:85-98).  A buffer that was handed out once is never released: when a later call needs
+    more, a larger buffer takes over and the old one stays alive for the CUDA graphs that captured its address.  A
+    call made DURING capture that finds no buffer large enough takes its scratch from the graph's own memory pool, as
+    the reference does.  All attention calls of a device share the buffer: issue them on one stream (the reference is
+    called from vLLM's single model-runner thread), or order streams with events.
 """
 
 from __future__ import annotations
@@ -28,7 +30,8 @@ __all__ = ("attention", "quantize", "set_quantizer_chain", "set_attention_splits
 
 _chain = "kernel"
 _forced_splits = 0
-_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_workspaces: Dict[int, torch.Tensor] = {}
+_superseded: List[torch.Tensor] = []   # earlier, smaller workspaces: captured graphs may still point into them
 
 
 def set_quantizer_chain(chain: str) -> None:
@@ -90,20 +93,25 @@ def _rotation_arg(rotation, device, heads: int, head_dim: int, keep: list) -> _l
     return out
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    key = (device.index or 0, 0)
+def _workspace(device: torch.device, nbytes: int) -> Tuple[torch.Tensor, bool]:
+    """(scratch buffer of at least `nbytes`, True when it was created for this one call during graph capture)."""
+    key = device.index or 0
     buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
-        _require(
-            not torch.cuda.is_current_stream_capturing(),
-            "attention workspace must exist before CUDA-graph capture: run one warm-up call first",
-        )
-        size = max(nbytes, 1 << 20)
-        buf = torch.empty(size, dtype=torch.uint8, device=device)
-        stream = torch.cuda.current_stream(device).cuda_stream
-        _lib.check(_lib.load().rq_attention_workspace_init(buf.data_ptr(), size, stream))
-        _workspaces[key] = buf
-    return buf
+    if buf is not None and buf.numel() >= nbytes:
+        return buf, False
+    stream = torch.cuda.current_stream(device).cuda_stream
+    if torch.cuda.is_current_stream_capturing():
+        # graph-private memory: lives as long as the graph, zeroed by a memset node in front of the kernel
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _lib.check(_lib.load().rq_attention_workspace_init(buf.data_ptr(), nbytes, stream))
+        return buf, True
+    size = max(nbytes, 1 << 20, 2 * buf.numel() if buf is not None else 0)
+    fresh = torch.empty(size, dtype=torch.uint8, device=device)
+    _lib.check(_lib.load().rq_attention_workspace_init(fresh.data_ptr(), size, stream))
+    if buf is not None:
+        _superseded.append(buf)
+    _workspaces[key] = fresh
+    return fresh, False
 
 
 def quantize(
@@ -282,12 +290,15 @@ def attention(
         args.gather_head_offset = gather.head_offset
         args.gather_stride = gather.heads * head_dim
     with torch.cuda.device(query.device):
-        splits = _forced_splits or lib.rq_attention_default_splits(rows, heads, block_table.size(1), kv_cache.size(3))
-        args.num_splits = splits
-        nbytes = lib.rq_attention_workspace_bytes(rows, heads, head_dim, splits)
-        workspace = _workspace(query.device, nbytes)
+        # 0: the kernel cuts every row into partitions in proportion to its own length, read on the device
+        args.num_splits = _forced_splits
+        nbytes = lib.rq_attention_workspace_bytes(rows, heads, head_dim, _forced_splits)
+        workspace, one_call = _workspace(query.device, nbytes)
+        keep.append(workspace)
         args.workspace = workspace.data_ptr()
         args.workspace_bytes = workspace.numel()
+        if one_call:
+            args.flags = _lib.FLAG_SERIAL_LAUNCH   # the kernel follows the memset of its own counters
         args.stream = torch.cuda.current_stream(query.device).cuda_stream
         _lib.check(lib.rq_attention(ctypes.byref(args)))
 
@@ -295,7 +306,7 @@ def attention(
 def attention_status(device=None) -> None:
     """Synchronize and raise if a bounded wait inside an attention kernel ever gave up on this device."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    buf = _workspaces.get((device.index or 0, 0))
+    buf = _workspaces.get(device.index or 0)
     if buf is None:
         return
     with torch.cuda.device(device):

@@ -12,6 +12,7 @@ RQ_MAX_RECORDS = 8
 RQ_MAX_PEERS = 8
 RQ_PEER_HANDLE_BYTES = 64
 RQ_OK = 0
+FLAG_SERIAL_LAUNCH = 1
 REFERENCE_MODES = {"anchor": 0, "adjacent": 1}
 COEFFICIENTS = {"unit": 0, "norm": 1, "ls": 2}
 CHAINS = {"kernel": 0, "calibration": 1}
@@ -23,6 +24,9 @@ EXPORTS = (
     "rq_quantize",
     "rq_quantize_workspace_bytes",
     "rq_attention_default_splits",
+    "rq_attention_work_capacity",
+    "rq_attention_noalloc_status",
+    "rq_set_programmatic_launch",
     "rq_attention_workspace_bytes",
     "rq_attention_workspace_init",
     "rq_attention",
@@ -77,6 +81,7 @@ class RqQuantizeArgs(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("flags", ctypes.c_int32),
     ]
 
 
@@ -113,6 +118,7 @@ class RqAttentionArgs(ctypes.Structure):
         ("gather_head_offset", ctypes.c_int32),
         ("gather_stride", ctypes.c_int64),
         ("peer_output", ctypes.c_void_p * RQ_MAX_PEERS),
+        ("flags", ctypes.c_int32),
     ]
 
 
@@ -151,6 +157,12 @@ def load() -> ctypes.CDLL:
     lib.rq_quantize.restype = ctypes.c_int32
     lib.rq_attention_default_splits.argtypes = [ctypes.c_int32] * 4
     lib.rq_attention_default_splits.restype = ctypes.c_int32
+    lib.rq_attention_work_capacity.argtypes = [ctypes.c_int32] * 2
+    lib.rq_attention_work_capacity.restype = ctypes.c_int32
+    lib.rq_attention_noalloc_status.argtypes = [ctypes.c_void_p]
+    lib.rq_attention_noalloc_status.restype = ctypes.c_int32
+    lib.rq_set_programmatic_launch.argtypes = [ctypes.c_int32]
+    lib.rq_set_programmatic_launch.restype = None
     lib.rq_attention_workspace_bytes.argtypes = [ctypes.c_int32] * 4
     lib.rq_attention_workspace_bytes.restype = ctypes.c_size_t
     lib.rq_attention_workspace_init.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]

@@ -5,16 +5,19 @@
 // and its page staging (attention/async_copy.cuh:109-168).
 //
 // Shape of the computation
-//   CTA  = one (query row, KV partition, head); grid = rows * splits * heads, heads fastest so that CTAs that
-//          run together read neighbouring pages of the same block.
+//   CTA  = one (work item, head); a work item is one KV partition of one query row.  grid = items * heads, heads
+//          fastest so that CTAs that run together read neighbouring pages of the same block.  How many partitions a
+//          row gets is decided on the device from the sequence lengths (find_work): proportional to the row's pages,
+//          inside a capacity the host fixed, so the grid stays CUDA-graph static.
 //   warp = an independent consumer of every 4th page of the partition with its OWN ring of shared-memory
-//          stages, filled by 1-D bulk async copies (cp.async.bulk + mbarrier complete_tx) that lane 0 issues
-//          STAGES pages ahead.  There is no CTA-wide barrier inside the page loop.
+//          stages.  Default staging: every lane issues 16-byte cp.async.cg copies, one commit group per page, STAGES
+//          pages ahead (build flag RQ_ATTENTION_BULK_COPY=1: lane 0 issues cp.async.bulk copies that complete on an
+//          mbarrier instead).  There is no CTA-wide barrier inside the page loop.
 //   lane = (token slot, 32-channel slice): 4 lanes per token, 8 tokens per warp step.  A slice is exactly one
 //          INT4 g32 anchor group, so scale/offset handling is per lane, not per channel.
 //   maths: no code is ever converted to a floating-point number one at a time.
 //          K: integer dot products (dp2a) of the masked code bytes against the rotated query quantized once per CTA
-//             to 12/10 bits, factored per slice as scale * sum(q*code) + offset * sum(q);
+//             to 11 bits (INT4 records) or 13 bits (INT2 records), factored per slice as scale * sum(q*code) + offset * sum(q);
 //          softmax: one online-softmax stream per 4-lane token slot (fp32 reference exponent that moves only when a
 //             score exceeds it by more than a slack, denominator and offsets in fp32, base-2 exponent);
 //          V: `word & mask` read as a half2 IS a pair of codes times 2^-24 (subnormal halves are linear in their bit
@@ -23,11 +26,13 @@
 //   merge: each warp folds its 8 streams, the CTA folds its 4 warps, and -- when the row has several
 //          partitions -- the LAST CTA to arrive (one atomic ticket per (row, head)) folds the partitions, adds the
 //          live token, undoes an explicit value rotation and stores bf16.  No second launch, no spin wait.
+//   launch: as a programmatic dependent of the previous kernel of the stream: the prologue and the whole page loop only
+//          read global memory and may overlap that kernel's tail; griddepcontrol.wait sits in front of the first write.
 //
 // The query rotation (signed Walsh-Hadamard) is fused into the prologue of every CTA (128 values, one warp).
 //
-// Every wait on an mbarrier is bounded; on expiry the kernel raises the workspace status word, drains what it
-// can and returns.
+// In the bulk-copy build every wait on an mbarrier is bounded; on expiry the kernel raises the workspace status word,
+// drains what it can and returns.  The default build has no wait that can fail.
 #include <atomic>
 #include <type_traits>
 
@@ -535,6 +540,143 @@ __device__ __forceinline__ void unrotate_history(const AttentionParams& p, int h
     }
 }
 
+// ---- work decomposition ------------------------------------------------------------------------------------
+// A work item is one KV partition of one query row (all heads of it: the CTA index is item * heads + head).
+struct WorkItem {
+    int row, request, seq_len;
+    int part, parts;  // this CTA's partition of the row and how many the row has
+    int first;        // index of the row's first work item: partial results of the row sit at items first .. first+parts-1
+};
+
+// Cost of running `items` equally sized CTAs per head, in units of (pages one CTA consumes while four share an SM):
+// full waves of `slots` CTAs plus a tail wave in which an SM holding 1/2/3/4 CTAs delivers 0.45/0.85/0.92/1 of its
+// throughput (fitted to measurements on B200: the kernel is bound by instruction issue).
+__device__ __forceinline__ float wave_count(float ctas, float slots, float sms) {
+    const float full = floorf(ctas / slots);
+    const float rest = ctas - full * slots;
+    const int per_sm = static_cast<int>(ceilf(rest / sms));
+    const float tail = per_sm <= 0 ? 0.f : per_sm == 1 ? 1.f / 0.45f : per_sm == 2 ? 2.f / 0.85f : per_sm == 3 ? 3.f / 0.92f : 4.f;
+    return full + 0.25f * tail;
+}
+
+// Maps a work-item index to (row, partition).  Replaces the reference's prepare_partition_schedule
+// (plugins/residual_quantization/csrc/attention/prepare.cuh:237-386), which a single CTA of a separate kernel runs
+// and parks in a work list; here every CTA derives the same answer from the sequence lengths in a few warp-wide
+// steps, so there is no extra launch and no list to read back.
+//   * p.splits > 0 (forced): every row has exactly p.splits partitions.
+//   * p.splits == 0: one chunk size c (pages) is chosen for the whole call from the TOTAL number of pages of the batch,
+//     row r gets max(1, ceil(pages_r / c)) partitions -- proportional to its length -- and the items are laid out
+//     request by request.  c is the candidate (4, 8, ..., 1024 pages, or "never split") with the lowest modelled time;
+//     a floor on c keeps the number of items within p.capacity, which fixed the grid on the host.
+// Every lane of the warp calls this with the same arguments and gets the same result.
+template <int P>
+__device__ __forceinline__ bool find_work(const AttentionParams& p, int item, int lane, WorkItem& out) {
+    const int num_requests = p.num_requests;
+    const int total_rows = min(__ldg(p.query_start_loc + num_requests), p.num_rows);
+    if (p.splits > 0) {
+        const int row = item / p.splits;
+        if (row >= total_rows) return false;
+        // Decode batches have one row per request, so request == row is the guess; it is re-read only if wrong.
+        int request = min(row, num_requests - 1);
+        const int guess_begin = __ldg(p.query_start_loc + request), guess_end = __ldg(p.query_start_loc + request + 1);
+        int seq_len = __ldg(p.seq_lens + request);
+        if (!(guess_begin <= row && row < guess_end)) {
+            int lo = 0, hi = num_requests - 1;  // largest r with query_start_loc[r] <= row
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (p.query_start_loc[mid] <= row) lo = mid; else hi = mid - 1;
+            }
+            request = lo;
+            seq_len = p.seq_lens[request];
+        }
+        out.row = row;
+        out.request = request;
+        out.seq_len = seq_len;
+        out.parts = p.splits;
+        out.part = item - row * p.splits;
+        out.first = row * p.splits;
+        return true;
+    }
+    if (item >= p.capacity) return false;
+
+    constexpr int kCandidates = 9;          // chunk sizes 4 << k pages, k = 0..8; candidate 9 = one partition per row
+    constexpr float kOverhead = 256.f / P;  // fixed cost of a CTA (prologue, first fetch, fold), in pages
+    auto load_request = [&](int r, int& begin, int& rows, int& pages, int& len) {
+        begin = rows = pages = len = 0;
+        if (r < num_requests) {
+            len = __ldg(p.seq_lens + r);
+            begin = __ldg(p.query_start_loc + r);
+            rows = max(0, min(__ldg(p.query_start_loc + r + 1), total_rows) - begin);
+            pages = rows > 0 ? (max(len - 1, 0) + P - 1) / P : 0;
+        }
+    };
+    // pass 1: pages of the whole batch, and how many items each candidate chunk size would make
+    int total_pages = 0, longest = 0;
+    int counts[kCandidates];
+#pragma unroll
+    for (int k = 0; k < kCandidates; ++k) counts[k] = 0;
+    for (int base = 0; base < num_requests; base += 32) {
+        int begin, rows, pages, len;
+        load_request(base + lane, begin, rows, pages, len);
+        total_pages += rows * pages;
+        longest = max(longest, pages);
+#pragma unroll
+        for (int k = 0; k < kCandidates; ++k) counts[k] += rows * max(1, (pages + (4 << k) - 1) >> (k + 2));
+    }
+    total_pages = __reduce_add_sync(kFullMask, total_pages);
+    longest = __reduce_max_sync(kFullMask, longest);
+    int my_items = total_rows;  // lanes >= kCandidates stand for "never split"
+#pragma unroll
+    for (int k = 0; k < kCandidates; ++k) {
+        const int sum = __reduce_add_sync(kFullMask, counts[k]);
+        if (lane == k) my_items = sum;
+    }
+    const int candidate = min(lane, kCandidates);
+    const float sms = static_cast<float>(p.sm_count), slots = sms * 4.f;  // four CTAs of this kernel fit on an SM
+    const float items = static_cast<float>(max(my_items, 1));
+    const float largest = candidate < kCandidates ? fminf(static_cast<float>(4 << candidate), static_cast<float>(longest))
+                                                  : static_cast<float>(longest);
+    float cost = wave_count(items * p.heads, slots, sms) * (static_cast<float>(total_pages) / items + kOverhead);
+    cost = fmaxf(cost, (0.25f / 0.45f) * (largest + kOverhead));  // the largest item alone on an SM is the floor
+    cost *= 1.f + 0.01f * static_cast<float>(kCandidates - candidate);  // near ties go to fewer partitions
+    uint32_t key = (__float_as_uint(cost) & ~15u) | static_cast<uint32_t>(kCandidates - candidate);
+    if (my_items > p.capacity) key = 0xffffffffu;  // does not fit the grid ("never split" always does)
+    const int chosen = kCandidates - static_cast<int>(__reduce_min_sync(kFullMask, key) & 15u);
+    const int shift = chosen + 2;  // chunk = 1 << shift pages; chosen == kCandidates: one partition per row
+    auto parts_of = [&](int pages) { return chosen < kCandidates ? max(1, (pages + (1 << shift) - 1) >> shift) : 1; };
+
+    // pass 2: which request owns this item
+    int before = 0;
+    for (int base = 0; base < num_requests; base += 32) {
+        int begin, rows, pages, len;
+        load_request(base + lane, begin, rows, pages, len);
+        const int parts = parts_of(pages);
+        const int mine = rows * parts;
+        int upto = mine;  // inclusive prefix sum over the lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(kFullMask, upto, d);
+            if (lane >= d) upto += v;
+        }
+        const uint32_t owners = __ballot_sync(kFullMask, item < before + upto);
+        if (owners != 0u) {
+            const int src = __ffs(owners) - 1;
+            const int local = item - before - (__shfl_sync(kFullMask, upto, src) - __shfl_sync(kFullMask, mine, src));
+            const int owner_parts = __shfl_sync(kFullMask, parts, src);
+            const int row_in_request = owner_parts == 1 ? local : local / owner_parts;
+            out.request = base + src;
+            out.seq_len = __shfl_sync(kFullMask, len, src);
+            out.row = __shfl_sync(kFullMask, begin, src) + row_in_request;
+            out.parts = owner_parts;
+            out.part = local - row_in_request * owner_parts;
+            out.first = item - out.part;
+            return true;
+        }
+        before += __shfl_sync(kFullMask, upto, 31);
+    }
+    return false;
+}
+
 template <class C>
 __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(const __grid_constant__ AttentionParams p) {
     constexpr int D = C::D, P = C::P;
@@ -547,30 +689,20 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     uint64_t* barriers = reinterpret_cast<uint64_t*>(smem + C::kOffBarriers);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int heads = p.heads, splits = p.splits;
+    const int heads = p.heads;
     const int head = blockIdx.x % heads;
-    const int split = (blockIdx.x / heads) % splits;
-    const int row = blockIdx.x / (heads * splits);
 
-    // ---- which request, which pages -----------------------------------------------------------------
-    // Decode batches have one row per request, so request == row is the guess; everything that only needs the guess
-    // is loaded in one go (independent loads, one memory latency) and re-read only if the guess was wrong.
-    const int num_requests = p.num_requests;
-    int request = min(row, num_requests - 1);
-    const int total_rows = __ldg(p.query_start_loc + num_requests);
-    const int guess_begin = __ldg(p.query_start_loc + request), guess_end = __ldg(p.query_start_loc + request + 1);
-    int seq_len = __ldg(p.seq_lens + request);
-    if (row >= total_rows) return;  // graph padding: leave the output row untouched
-    if (!(guess_begin <= row && row < guess_end)) {
-        int lo = 0, hi = num_requests - 1;  // largest r with query_start_loc[r] <= row
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (p.query_start_loc[mid] <= row) lo = mid; else hi = mid - 1;
-        }
-        request = lo;
-        seq_len = p.seq_lens[request];
-    }
-    const int history = max(0, seq_len - 1);
+    // Let the next kernel of the stream start its own prologue and page fetches while this one runs (it was launched as
+    // a programmatic dependent; without that attribute this is a no-op).  Everything up to pdl_wait() below only READS
+    // global memory: metadata, cache pages, the q/k/v rows.  The first write (partial results, counters, output) comes
+    // after pdl_wait(), i.e. after the previous kernel of the stream has completed.
+    pdl_launch_dependents();
+
+    // ---- which work item: (row, partition) and the row's request ---------------------------------------
+    WorkItem work;
+    if (!find_work<P>(p, blockIdx.x / heads, lane, work)) return;  // graph padding or spare capacity: nothing to do
+    const int row = work.row, request = work.request, split = work.part, splits = work.parts;
+    const int history = max(0, work.seq_len - 1);
     const int pages = (history + P - 1) / P;
     const int chunk = (pages + splits - 1) / splits;
     const int page_begin = min(pages, split * chunk), page_end = min(pages, page_begin + chunk);
@@ -929,9 +1061,15 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         if (tid < D) value += warp_acc[w * D + tid] * f;
     }
 
+    // From here on the CTA writes global memory (partial results, counters, output rows): the previous kernel of the
+    // stream -- which may still be reading or writing the same scratch and output buffers -- has to be complete.
+    pdl_wait();
+
     // ---- several partitions: park the partial, the last CTA to arrive folds them -----------------------
     if (splits > 1) {
-        float* mine = p.partials + ((static_cast<int64_t>(row) * heads + head) * splits + split) * (D + 2);
+        // partial results are stored item-major: the row's partitions are `heads` records apart
+        const int64_t item_stride = static_cast<int64_t>(heads) * (D + 2);
+        float* mine = p.partials + (static_cast<int64_t>(work.first + split) * heads + head) * (D + 2);
         if (tid == 0) { mine[0] = part_m; mine[1] = part_l; }
         if (tid < D) mine[2 + tid] = value;
         __threadfence();
@@ -944,18 +1082,18 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         __syncthreads();
         if (misc[0] == 0.f) return;
         __threadfence();
-        const float* all = p.partials + (static_cast<int64_t>(row) * heads + head) * splits * (D + 2);
+        const float* all = p.partials + (static_cast<int64_t>(work.first) * heads + head) * (D + 2);
         part_m = kNever;
 #pragma unroll 8
-        for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * (D + 2)));
+        for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * item_stride));
         part_l = 0.f;
         value = 0.f;
 #pragma unroll 4
         for (int s = 0; s < splits; ++s) {
-            const float ms = __ldcg(all + s * (D + 2));
+            const float ms = __ldcg(all + s * item_stride);
             const float f = fast_exp2(ms - part_m);
-            part_l += __ldcg(all + s * (D + 2) + 1) * f;
-            if (tid < D) value += __ldcg(all + s * (D + 2) + 2 + tid) * f;
+            part_l += __ldcg(all + s * item_stride + 1) * f;
+            if (tid < D) value += __ldcg(all + s * item_stride + 2 + tid) * f;
         }
     }
 
@@ -1020,9 +1158,18 @@ cudaError_t launch_one(const AttentionParams& p, cudaStream_t stream) {
         if (err != cudaSuccess) return err;
         configured.fetch_or(bit, std::memory_order_release);
     }
-    const int64_t blocks = static_cast<int64_t>(p.num_rows) * p.splits * p.heads;
-    attention_kernel<C><<<static_cast<unsigned>(blocks), kThreads, C::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
+    const int64_t items = p.splits > 0 ? static_cast<int64_t>(p.num_rows) * p.splits : p.capacity;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(items * p.heads));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = C::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = p.programmatic_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&config, attention_kernel<C>, p);
 }
 
 template <int D, int AB, int AG, int RB, int RG, int P>

@@ -3,8 +3,10 @@
 // No allocation, no synchronization, no host read of device memory on the launch path.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "rq_kernels.h"
@@ -73,6 +75,38 @@ int check_rotation(const RqRotation& r, const char* name) {
 
 constexpr size_t kStatusBytes = 256;
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Multiprocessors of the current device, looked up once per device and process.
+int current_sm_count() {
+    static std::atomic<int> cache[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    int sms = cache[device].load(std::memory_order_relaxed);
+    if (sms == 0) {
+        int value = 0;
+        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0) sms = value;
+        else sms = 148;
+        cache[device].store(sms, std::memory_order_relaxed);
+    }
+    return sms;
+}
+
+// Programmatic dependent launch of the attention and quantize kernels: on unless RQ_PROGRAMMATIC_LAUNCH=0 is in the
+// environment or rq_set_programmatic_launch(0) was called.
+std::atomic<int> g_programmatic{-1};
+bool programmatic_launch_enabled() {
+    int state = g_programmatic.load(std::memory_order_relaxed);
+    if (state < 0) {
+        const char* text = getenv("RQ_PROGRAMMATIC_LAUNCH");
+        state = (text != nullptr && text[0] == '0') ? 0 : 1;
+        g_programmatic.store(state, std::memory_order_relaxed);
+    }
+    return state != 0;
+}
+
+size_t work_items(int32_t rows, int32_t heads, int32_t num_splits) {
+    return num_splits > 0 ? static_cast<size_t>(rows) * num_splits : static_cast<size_t>(rq_attention_work_capacity(rows, heads));
+}
 
 }  // namespace
 
@@ -165,6 +199,7 @@ int32_t rq_quantize(const RqQuantizeArgs* a) {
     p.coefficient = a->coefficient;
     p.chain = a->chain;
     p.vector_loads = vector_loads ? 1 : 0;
+    p.programmatic_launch = programmatic_launch_enabled() && !(a->flags & RQ_FLAG_SERIAL_LAUNCH) ? 1 : 0;
     // Dense learned rotations: one tensor-core launch per plane writes the rotated rows to the caller's scratch.
     const size_t need = rq_quantize_workspace_bytes(&s, a->num_tokens, a->key_rotation.kind, a->value_rotation.kind);
     if (need > 0) {
@@ -204,17 +239,7 @@ int32_t rq_quantize(const RqQuantizeArgs* a) {
 int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32_t max_blocks_per_request,
                                     int32_t page_tokens) {
     if (num_query_rows < 1 || heads < 1) return 1;
-    static thread_local int sm_count_cache[64] = {0};
-    int device = 0;
-    int sms = 148;
-    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64) {
-        if (sm_count_cache[device] == 0) {
-            int value = 0;
-            if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0)
-                sm_count_cache[device] = value;
-        }
-        if (sm_count_cache[device] > 0) sms = sm_count_cache[device];
-    }
+    const int sms = current_sm_count();
     // Cost model fitted to measurements on B200 (batch 1..64 x 16 heads and 16 x 55 heads, contexts 2k..8k).  A CTA
     // costs its pages plus a fixed overhead worth about 16 pages (prologue, first fetch, merge).  Four CTAs fit on an
     // SM; the grid runs as full waves of 4 per SM plus a tail wave of c = ceil(rest / SMs) per SM, and an SM holding c
@@ -242,11 +267,25 @@ int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32
     return best;
 }
 
+int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads) {
+    if (num_query_rows < 1 || heads < 1) return 0;
+    // Every row is one work item; the spare items are what long rows can be cut into.  Two waves of resident CTAs
+    // (four per multiprocessor) is as many as the partition choice on the device ever asks for, fifteen spare items per
+    // row is the reference's ceiling (attention/launch.cuh:70-80: sixteen partitions per request), and a single long
+    // row among short ones can always have its sixteen.
+    const int64_t slots = 4LL * current_sm_count();
+    int64_t spare = (2 * slots + heads - 1) / heads;
+    if (spare > 15LL * num_query_rows) spare = 15LL * num_query_rows;
+    if (spare < 15) spare = 15;
+    const int64_t capacity = num_query_rows + spare;
+    return capacity > 0x7fffffff / 64 ? 0 : static_cast<int32_t>(capacity);
+}
+
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits) {
-    if (num_query_rows < 0 || heads < 1 || head_dim < 1 || num_splits < 1) return 0;
+    if (num_query_rows < 0 || heads < 1 || head_dim < 1 || num_splits < 0) return 0;
     const size_t counters = round_up(static_cast<size_t>(num_query_rows) * heads * sizeof(int32_t), 256);
     const size_t partials =
-        num_splits > 1 ? static_cast<size_t>(num_query_rows) * heads * num_splits * (head_dim + 2) * sizeof(float) : 0;
+        num_splits != 1 ? work_items(num_query_rows, heads, num_splits) * heads * (head_dim + 2) * sizeof(float) : 0;
     const size_t rotated_query = round_up(static_cast<size_t>(num_query_rows) * heads * head_dim * sizeof(float), 256);
     return kStatusBytes + counters + round_up(partials, 256) + rotated_query;
 }
@@ -329,11 +368,12 @@ int32_t rq_attention(const RqAttentionArgs* a) {
                     s.heads, s.head_dim, v.anchor_bits, v.anchor_group, v.residual_bits, v.residual_group,
                     int(v.has_mean), s.page_tokens);
 
-    int splits = a->num_splits;
-    if (splits == 0)
-        splits = rq_attention_default_splits(a->num_query_rows, s.heads, a->max_blocks_per_request, s.page_tokens);
-    if (splits < 1 || splits > 1024) return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside 1..1024", splits);
-    if (static_cast<int64_t>(a->num_query_rows) * splits * s.heads > 0x7fffffffLL)
+    // 0 = the kernel cuts every row into partitions proportional to its length; n > 0 = exactly n per row
+    const int splits = a->num_splits;
+    if (splits < 0 || splits > 1024) return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside 0..1024", splits);
+    const int capacity = splits == 0 ? rq_attention_work_capacity(a->num_query_rows, s.heads) : 0;
+    if (splits == 0 && capacity < a->num_query_rows) return fail(RQ_ERR_INVALID_ARGUMENT, "too many query rows in one call");
+    if (static_cast<int64_t>(work_items(a->num_query_rows, s.heads, splits)) * s.heads > 0x7fffffffLL)
         return fail(RQ_ERR_INVALID_ARGUMENT, "grid too large");
     const size_t need = rq_attention_workspace_bytes(a->num_query_rows, s.heads, s.head_dim, splits);
     if (a->workspace == nullptr || !aligned(a->workspace, 256) || a->workspace_bytes < need)
@@ -378,6 +418,9 @@ int32_t rq_attention(const RqAttentionArgs* a) {
         for (int r = 0; r <= p.chain_count; ++r) p.chain_offset[r] = rq_record_offset(&s, r);
     }
     p.splits = splits;
+    p.capacity = capacity;
+    p.sm_count = current_sm_count();
+    p.programmatic_launch = programmatic_launch_enabled() && !(a->flags & RQ_FLAG_SERIAL_LAUNCH) ? 1 : 0;
     uint8_t* base = static_cast<uint8_t*>(a->workspace);
     p.status = reinterpret_cast<int32_t*>(base);
     p.counters = reinterpret_cast<int32_t*>(base + kStatusBytes);
@@ -386,7 +429,7 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     if (a->key_rotation.kind == RQ_ROTATION_DENSE_FP16) {
         // q @ R on the tensor cores, once per call, into the tail of the workspace
         const size_t partial_bytes =
-            splits > 1 ? static_cast<size_t>(a->num_query_rows) * s.heads * splits * (s.head_dim + 2) * sizeof(float) : 0;
+            splits != 1 ? work_items(a->num_query_rows, s.heads, splits) * s.heads * (s.head_dim + 2) * sizeof(float) : 0;
         float* rotated = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.partials) + round_up(partial_bytes, 256));
         rq::RotateParams rp;
         memset(&rp, 0, sizeof(rp));
@@ -429,39 +472,57 @@ int32_t rq_attention(const RqAttentionArgs* a) {
 // needs comes from cudaGetSymbolAddress, looked up once per device with that device current.
 static __device__ __align__(256) unsigned char g_static_scratch[RQ_STATIC_SCRATCH_BYTES];
 
-int32_t rq_attention_noalloc(const RqAttentionArgs* a) {
-    if (a == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null arguments");
-    static thread_local void* addresses[64] = {nullptr};
+// Device address of the built-in buffer on the current device.  The cache is process-wide (one slot per device), so
+// the lookup runs once per device whichever thread gets there first.
+static int static_scratch_address(void** address) {
+    static std::atomic<void*> addresses[64];
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
     if (device < 0 || device >= 64) return fail(RQ_ERR_INVALID_ARGUMENT, "device index %d not supported", device);
-    if (addresses[device] == nullptr) {
-        void* address = nullptr;
-        err = cudaGetSymbolAddress(&address, g_static_scratch);
+    void* known = addresses[device].load(std::memory_order_acquire);
+    if (known == nullptr) {
+        err = cudaGetSymbolAddress(&known, g_static_scratch);
         if (err != cudaSuccess) return fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
-        addresses[device] = address;
+        addresses[device].store(known, std::memory_order_release);
     }
-    if (a->num_query_rows <= 0) return rq_attention(a);  // nothing to launch; reuse the argument checks
-    int splits = a->num_splits;
-    if (splits == 0)
-        splits = rq_attention_default_splits(a->num_query_rows, a->spec.heads, a->max_blocks_per_request,
-                                             a->spec.page_tokens);
-    const size_t need = rq_attention_workspace_bytes(a->num_query_rows, a->spec.heads, a->spec.head_dim, splits);
+    *address = known;
+    return RQ_OK;
+}
+
+int32_t rq_attention_noalloc(const RqAttentionArgs* a) {
+    if (a == nullptr) return fail(RQ_ERR_INVALID_ARGUMENT, "null arguments");
+    void* scratch = nullptr;
+    int status = static_scratch_address(&scratch);
+    if (status != RQ_OK) return status;
+    if ((status = check_spec(&a->spec)) != RQ_OK) return status;  // a bad spec is reported as such, not as a size problem
+    if (a->num_query_rows <= 0) return rq_attention(a);            // nothing to launch; reuse the argument checks
+    if (a->num_splits < 0 || a->num_splits > 1024)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside 0..1024", a->num_splits);
+    const size_t need = rq_attention_workspace_bytes(a->num_query_rows, a->spec.heads, a->spec.head_dim, a->num_splits);
     if (need == 0 || need > RQ_STATIC_SCRATCH_BYTES)
         return fail(RQ_ERR_WORKSPACE,
                     "this shape needs %zu bytes of scratch; the built-in buffer holds %u (use rq_attention with a "
-                    "caller-provided workspace, or fewer splits)", need, RQ_STATIC_SCRATCH_BYTES);
+                    "caller-provided workspace, or fewer rows per call)", need, RQ_STATIC_SCRATCH_BYTES);
     // The buffer keeps whatever the previous call left: the status word and the arrival counters must start at zero.
     const size_t clear = kStatusBytes + round_up(static_cast<size_t>(a->num_query_rows) * a->spec.heads * sizeof(int32_t), 256);
-    err = cudaMemsetAsync(addresses[device], 0, clear, static_cast<cudaStream_t>(a->stream));
+    const cudaError_t err = cudaMemsetAsync(scratch, 0, clear, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "clearing the static scratch");
     RqAttentionArgs copy = *a;
-    copy.num_splits = splits;
-    copy.workspace = addresses[device];
+    copy.workspace = scratch;
     copy.workspace_bytes = RQ_STATIC_SCRATCH_BYTES;
+    copy.flags |= RQ_FLAG_SERIAL_LAUNCH;  // the kernel follows a memset of its own counters: plain stream order
     return rq_attention(&copy);
 }
+
+int32_t rq_attention_noalloc_status(void* stream) {
+    void* scratch = nullptr;
+    const int status = static_scratch_address(&scratch);
+    if (status != RQ_OK) return status;
+    return rq_attention_status(scratch, stream);
+}
+
+void rq_set_programmatic_launch(int32_t enabled) { g_programmatic.store(enabled ? 1 : 0, std::memory_order_relaxed); }
 
 // ---- node-level barrier for the fused head gather ------------------------------------------------------------
 int32_t rq_peer_barrier(const RqPeerBarrierArgs* a) {

@@ -30,6 +30,13 @@ __device__ __forceinline__ __half2 fp8x2_to_half2(uint32_t pair) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits) { return __uint_as_float(bits << 16); }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------
+// launch_dependents: the next kernel of the stream (if it was launched as a programmatic dependent) may be scheduled
+// once every CTA of this grid has said so or exited.  wait: returns when the previous kernel of the stream has
+// completed and its writes are visible.  Both are no-ops in a kernel launched with plain stream order.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- Walsh-Hadamard helpers ---------------------------------------------------------------------------
 // In-register butterflies with strides 1, 2, ..., N/2 over x[0..N), (a, b) -> (a + b, a - b).
 template <int N>

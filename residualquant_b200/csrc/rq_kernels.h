@@ -31,6 +31,7 @@ struct QuantizeParams {
     // Dense learned rotation: rows already rotated by rotate_rows_kernel, fp32 [records][tokens][heads][head_dim]
     // per plane (nullptr = read the bf16 inputs and rotate with the fused Walsh-Hadamard transform, or not at all).
     const float* rotated_rows[2];
+    int programmatic_launch;  // launch with the programmatic-stream-serialization attribute
 };
 
 // y = x @ R for bf16 rows and a dense fp16 matrix per head (TF32 tensor-core products, fp32 accumulation).
@@ -51,7 +52,8 @@ cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t 
 // Layout of the attention workspace (all offsets multiples of 256 bytes):
 //   [0, 256)                         status word (int32) + padding
 //   [256, 256 + 4*rows*heads)        arrival counters, one int32 per (row, head)
-//   [partials_offset, ...)           float [rows][heads][splits][head_dim + 2]  (max, denominator, value sums)
+//   [partials_offset, ...)           float [work items][heads][head_dim + 2]  (max, denominator, value sums);
+//                                    work items = rows * splits, or the capacity when the device picks the partitions
 struct AttentionParams {
     const __nv_bfloat16* query;
     const __nv_bfloat16* key;
@@ -78,7 +80,13 @@ struct AttentionParams {
     int chain_count;             // loop_index + 1 (0 in anchor mode)
     int chain_bits[4], chain_group[4];
     int chain_offset[5];         // bytes per token before record r; [chain_count] = bytes of the staged prefix
+    // Work decomposition.  splits > 0: every row is cut into exactly `splits` partitions (grid = rows * splits * heads).
+    // splits == 0: the grid is capacity * heads and every CTA derives the (row, partition) of its work item from the
+    // sequence lengths on the device: partitions per row proportional to the row's pages (see find_work).
     int splits;
+    int capacity;                // work items per head the grid and the partial-result buffer provide (splits == 0)
+    int sm_count;                // multiprocessors of the device (input of the on-device partition choice)
+    int programmatic_launch;     // launch with the programmatic-stream-serialization attribute
     int32_t* status;
     int32_t* counters;
     float* partials;

@@ -341,6 +341,9 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         float y[16], mean[16];
         if (packed_rows) unpack(words, y, true); else load_unpacked(anchor, y, true);
         if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+        // Launched as a programmatic dependent: the loads above may have overlapped the previous kernel of the stream
+        // (an attention call that is still reading these pages); the stores below wait for it to complete.
+        pdl_wait();
         if (centered) {
             load_mean(anchor, mean);
 #pragma unroll
@@ -474,6 +477,7 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
         }
     }
     if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+    pdl_wait();  // everything above only read; the previous kernel of the stream may still be reading these pages
 
     const int P = p.page_tokens;
     const int tok = static_cast<int>(slot % P);
@@ -529,6 +533,20 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
     }
 }
 
+template <class Kernel>
+cudaError_t launch_with_order(Kernel kernel, dim3 grid, const QuantizeParams& p, cudaStream_t stream) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(128);
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = p.programmatic_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, p);
+}
+
 }  // namespace
 
 cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream) {
@@ -542,24 +560,21 @@ cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t 
                             p.rotated_rows[1] == nullptr;
     if (few_tokens) {
         const dim3 token_grid((p.num_tokens + 3) / 4, p.heads, 2);
-        if (head_dim == 128 && p.group[0] == 32) quantize_token_kernel<128, 32><<<token_grid, 128, 0, stream>>>(p);
-        else if (head_dim == 128) quantize_token_kernel<128, 16><<<token_grid, 128, 0, stream>>>(p);
-        else if (p.group[0] == 32) quantize_token_kernel<96, 32><<<token_grid, 128, 0, stream>>>(p);
-        else quantize_token_kernel<96, 16><<<token_grid, 128, 0, stream>>>(p);
-        return cudaGetLastError();
+        if (head_dim == 128 && p.group[0] == 32) return launch_with_order(quantize_token_kernel<128, 32>, token_grid, p, stream);
+        if (head_dim == 128) return launch_with_order(quantize_token_kernel<128, 16>, token_grid, p, stream);
+        if (p.group[0] == 32) return launch_with_order(quantize_token_kernel<96, 32>, token_grid, p, stream);
+        return launch_with_order(quantize_token_kernel<96, 16>, token_grid, p, stream);
     }
     if (headline && p.group[0] == 32) {
-        if (head_dim == 128) quantize_kernel<128, Anchor2224<32>><<<grid, 128, 0, stream>>>(p);
-        else quantize_kernel<96, Anchor2224<32>><<<grid, 128, 0, stream>>>(p);
-    } else if (headline && p.group[0] == 16) {
-        if (head_dim == 128) quantize_kernel<128, Anchor2224<16>><<<grid, 128, 0, stream>>>(p);
-        else quantize_kernel<96, Anchor2224<16>><<<grid, 128, 0, stream>>>(p);
-    } else if (head_dim == 128) {
-        quantize_kernel<128, AnySchedule><<<grid, 128, 0, stream>>>(p);
-    } else {
-        quantize_kernel<96, AnySchedule><<<grid, 128, 0, stream>>>(p);
+        if (head_dim == 128) return launch_with_order(quantize_kernel<128, Anchor2224<32>>, grid, p, stream);
+        return launch_with_order(quantize_kernel<96, Anchor2224<32>>, grid, p, stream);
     }
-    return cudaGetLastError();
+    if (headline && p.group[0] == 16) {
+        if (head_dim == 128) return launch_with_order(quantize_kernel<128, Anchor2224<16>>, grid, p, stream);
+        return launch_with_order(quantize_kernel<96, Anchor2224<16>>, grid, p, stream);
+    }
+    if (head_dim == 128) return launch_with_order(quantize_kernel<128, AnySchedule>, grid, p, stream);
+    return launch_with_order(quantize_kernel<96, AnySchedule>, grid, p, stream);
 }
 
 }  // namespace rq

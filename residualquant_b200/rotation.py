@@ -11,6 +11,7 @@ the per-call path is a dictionary lookup.
 
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
@@ -90,7 +91,8 @@ def analyze(rotation: torch.Tensor) -> Optional[Tuple[np.ndarray, float]]:
     return signs.astype(np.int8), scale
 
 
-_registry: Dict[Tuple[int, int, Tuple[int, ...]], SignedHadamardRotation] = {}
+# key -> (structure, weak reference to the registered tensor, its version counter at registration)
+_registry: Dict[Tuple[int, int, Tuple[int, ...]], Tuple[SignedHadamardRotation, "weakref.ref", int]] = {}
 
 
 def _key(rotation: torch.Tensor):
@@ -99,18 +101,38 @@ def _key(rotation: torch.Tensor):
 
 def register_rotation(rotation: torch.Tensor) -> Optional[SignedHadamardRotation]:
     """Inspect a dense fp16 rotation once; remember its structure when it is a signed Hadamard matrix.
-    The tensor must stay alive and unmodified while it is registered."""
+    The entry is tied to this very tensor object: it is dropped when the tensor dies or is modified in place, so a
+    different matrix that later lands at the same address is never mistaken for it."""
     found = analyze(rotation)
     if found is None:
         return None
     signs, scale = found
     structured = signed_hadamard(signs, scale, rotation.device)
-    _registry[_key(rotation)] = structured
+    key = _key(rotation)
+    _registry[key] = (structured, weakref.ref(rotation), rotation._version)
+    weakref.finalize(rotation, _drop_if_dead, key)
     return structured
 
 
+def _drop_if_dead(key) -> None:
+    entry = _registry.get(key)
+    if entry is not None and entry[1]() is None:
+        del _registry[key]
+
+
 def lookup(rotation: torch.Tensor) -> Optional[SignedHadamardRotation]:
-    return _registry.get(_key(rotation))
+    key = _key(rotation)
+    entry = _registry.get(key)
+    if entry is None:
+        return None
+    structured, owner, version = entry
+    alive = owner()
+    # While the registered tensor lives, nothing else can be allocated at its address: any tensor that matches the key
+    # is that tensor or a view of it.  Its version counter moves with every in-place write.
+    if alive is None or alive._version != version:
+        del _registry[key]
+        return None
+    return structured
 
 
 def forget(rotation: torch.Tensor) -> None:

@@ -43,7 +43,7 @@ def _args(case, cache, q, k, v, out, qsl, seq, table, kr, vr, loop, splits):
     return a
 
 
-@pytest.mark.parametrize("splits", [3, 1])
+@pytest.mark.parametrize("splits", [3, 1, 0])
 def test_noalloc_entry_matches_regular_entry_twice(splits):
     from residualquant_b200 import _lib
 
@@ -75,10 +75,14 @@ def test_noalloc_entry_matches_regular_entry_twice(splits):
         for attempt in range(2):
             out = torch.zeros_like(q)
             b = _args(case, cache, q, k, v, out, qsl, seq, table, kr, vr, loop, splits)
-            before = torch.cuda.memory_allocated()
+            # free device memory as the driver sees it: a raw cudaMalloc inside the call would show here
+            # (torch's own counters only see torch's allocator)
+            torch.cuda.synchronize()
+            before = torch.cuda.mem_get_info()[0]
             _lib.check(lib.rq_attention_noalloc(ctypes.byref(b)))
             torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == before
+            assert torch.cuda.mem_get_info()[0] == before
+            assert lib.rq_attention_noalloc_status(torch.cuda.current_stream().cuda_stream) == 0
             got, ref = out.float().cpu().numpy(), regular.float().cpu().numpy()
             assert np.all(np.abs(got - ref) <= 2e-2 + 1e-2 * np.abs(ref)), f"attempt {attempt}: differs from rq_attention"
             assert np.all(np.abs(got - want) <= 2e-2 + 1e-2 * np.abs(want)), f"attempt {attempt}: differs from the oracle"
@@ -100,3 +104,51 @@ def test_noalloc_entry_rejects_shapes_beyond_its_buffer():
     a = _args(case, cache, q, q, q, out, qsl, seq, table, kr, vr, 0, 64)
     assert lib.rq_attention_noalloc(ctypes.byref(a)) == -3
     assert b"built-in buffer" in lib.rq_last_error()
+
+
+def test_noalloc_entry_reports_a_bad_spec_as_such():
+    from residualquant_b200 import _lib
+
+    lib = _lib.load()
+    case = helpers.make_case(78, 128, 4, [40], 32, 16)
+    cache = torch.from_numpy(helpers.oracle_cache(case)).cuda()
+    kr, vr = G.device_rotations(case)
+    q = G.bf16(case.query)
+    qsl = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    a = _args(case, cache, q, q, q, torch.zeros_like(q), qsl, seq, table, kr, vr, 0, 0)
+    a.spec.heads = 0
+    assert lib.rq_attention_noalloc(ctypes.byref(a)) == -1          # RQ_ERR_INVALID_ARGUMENT, not a workspace error
+    a.spec.heads = 4
+    a.num_splits = -2
+    assert lib.rq_attention_noalloc(ctypes.byref(a)) == -1
+
+
+def test_noalloc_entry_with_a_dense_key_rotation():
+    """A dense (learned) key rotation makes the call use the tail of the built-in buffer for the rotated query rows."""
+    from residualquant_b200 import _lib
+
+    lib = _lib.load()
+    case = helpers.make_case(79, 128, 4, [260, 33], 32, 16)
+    cache_np = helpers.oracle_cache(case)
+    cache = torch.from_numpy(cache_np).cuda()
+    kr, vr = G.device_rotations(case)
+    dense = kr.dense().contiguous()
+    rows = len(case.seq_lens)
+    qsl = torch.arange(rows + 1, dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    q = G.bf16(case.query)
+    k, v = G.bf16(case.keys[1][case.live_rows]), G.bf16(case.values[1][case.live_rows])
+    want = helpers.oracle_attention(case, cache_np, 1)
+    for attempt in range(2):
+        out = torch.zeros_like(q)
+        a = _args(case, cache, q, k, v, out, qsl, seq, table, kr, vr, 1, 0)
+        a.key_rotation.kind = _lib.ROTATION_DENSE_FP16
+        a.key_rotation.scale = 1.0
+        a.key_rotation.data = dense.data_ptr()
+        _lib.check(lib.rq_attention_noalloc(ctypes.byref(a)))
+        torch.cuda.synchronize()
+        got = out.float().cpu().numpy()
+        assert np.all(np.abs(got - want) <= 2e-2 + 1e-2 * np.abs(want)), f"attempt {attempt}"
