@@ -682,16 +682,18 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
     gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
 
     def step():
-        stack.advance()
         for layer in range(shape.layers):
             for loop in range(4):
                 stack.attention(layer, loop, gather=gather, gather_buffer=loop % 2)
                 gather.barrier()
             stack.quantize(layer)
         stack.seq_lens.add_(1)
+        stack.advance()
 
+    stack.advance()
     graph = timer.capture(step)
     stack.seq_lens.fill_(shape.context)
+    stack.advance()
     timer.join_default_stream()
     with torch.cuda.stream(timer.stream):
         for _ in range(warmup):
@@ -765,10 +767,20 @@ def run_gpu(args, shape):
                     gathered[0] = sharding.gather_heads(stack.out[layer, loop], shape.heads)
             stack.quantize(layer)
 
+    # The engine's promise of RQ_FLAG_STABLE_METADATA: lengths, tables and slots are written once per step, never by the
+    # kernel right in front of an attention call -- here at the END of the captured step, for the next replay.
+    _cuda.set_stable_metadata(True)
+
     def step_body():
-        stack.advance()
         hot_path()
         stack.seq_lens.add_(1)
+        stack.advance()
+
+    def rewind():
+        stack.seq_lens.fill_(L)
+        stack.advance()
+
+    rewind()
 
     if shard_heads and world > 1 and fused_gather is None:
         # The step contains NCCL all-gathers; it is replayed eagerly rather than from a captured graph.
@@ -784,7 +796,7 @@ def run_gpu(args, shape):
         graph = _Eager()
     else:
         graph = timer.capture(step_body)
-    stack.seq_lens.fill_(L)
+    rewind()
     torch.cuda.synchronize(device)
     launches_per_step = layers * (9 if fused_gather is not None else 5)
 
@@ -807,7 +819,7 @@ def run_gpu(args, shape):
     value = replicas * B * args.steps / (ms * 1e-3)
 
     # ---------------- end to end: host rows in, outputs back ----------------
-    stack.seq_lens.fill_(L)
+    rewind()
     q, k_live, v_live, out = stack.q, stack.k_live, stack.v_live, stack.out
     host_q = torch.empty(q.shape, dtype=q.dtype).pin_memory().copy_(q)
     host_k = torch.empty(k_live.shape, dtype=q.dtype).pin_memory().copy_(k_live)
@@ -822,6 +834,7 @@ def run_gpu(args, shape):
         k_live.copy_(host_k, non_blocking=True)
         v_live.copy_(host_v, non_blocking=True)
         stack.seq_lens.copy_(host_lens, non_blocking=True)
+        stack.advance()
         graph.replay()
         host_out.copy_(out, non_blocking=True)
         host_lens.add_(1)

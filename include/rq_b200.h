@@ -36,16 +36,25 @@ extern "C" {
 #define RQ_MAX_PEERS 8 /* GPUs of one node that a head-sharded output can be stored to */
 
 /* RqQuantizeArgs.flags / RqAttentionArgs.flags.
+ *
  * By default both kernels are launched as PROGRAMMATIC DEPENDENTS of the previous kernel of the stream
- * (cudaLaunchAttributeProgrammaticStreamSerialization): the part of the kernel that only reads -- metadata, cache
- * pages, the K/V/Q rows -- may start while that previous kernel is still running if, and only if, that kernel signals
- * early; every write of this library's kernels is ordered behind the previous kernel's completion by
- * griddepcontrol.wait.  The only kernel of this library that signals early is the attention kernel, so the rule a
- * caller has to know is: do not pass the OUTPUT (or the workspace) of one rq_attention call as an INPUT tensor of the
- * rq_attention / rq_quantize call that follows it directly on the same stream.  (Model code never does: a projection
- * sits in between.)  RQ_FLAG_SERIAL_LAUNCH launches the call with plain stream order instead;
- * rq_set_programmatic_launch(0) or RQ_PROGRAMMATIC_LAUNCH=0 in the environment does so for every call. */
+ * (cudaLaunchAttributeProgrammaticStreamSerialization): the launch and the scheduling of the CTAs overlap that kernel,
+ * and every CTA then waits (griddepcontrol.wait) for that kernel to complete before it reads or writes anything.  That
+ * is indistinguishable from plain stream order for the caller, only faster.  Each kernel lets its own successor be
+ * scheduled once that wait is over, so at most two kernels of a stream overlap.
+ *
+ * RQ_FLAG_SERIAL_LAUNCH        launch this call with plain stream order instead (rq_set_programmatic_launch(0) or
+ *                              RQ_PROGRAMMATIC_LAUNCH=0 in the environment does so for every call).
+ * RQ_FLAG_STABLE_METADATA      rq_attention only; a promise by the caller: the kernel launched immediately before this
+ *                              call on the same stream did not write query_start_loc, seq_lens, block_table or the
+ *                              cached tokens this call reads.  The work lookup, the page-table fetch and the first page
+ *                              copies then run BEFORE the wait, i.e. in the shadow of the previous kernel; q, k, v are
+ *                              still read after it.  True under a serving engine, which writes the metadata once per
+ *                              step and whose previous kernel is the projection that produces q/k/v.  The library
+ *                              withdraws the early start by itself when the last rq_quantize on the stream wrote the
+ *                              same cache. */
 #define RQ_FLAG_SERIAL_LAUNCH 1
+#define RQ_FLAG_STABLE_METADATA 2
 
 typedef enum RqStatus {
     RQ_OK = 0,

@@ -26,10 +26,11 @@ import torch
 from . import _lib
 from .rotation import SignedHadamardRotation, lookup
 
-__all__ = ("attention", "quantize", "set_quantizer_chain", "set_attention_splits")
+__all__ = ("attention", "quantize", "set_quantizer_chain", "set_attention_splits", "set_stable_metadata")
 
 _chain = "kernel"
 _forced_splits = 0
+_stable_metadata = False
 _workspaces: Dict[int, torch.Tensor] = {}
 _superseded: List[torch.Tensor] = []   # earlier, smaller workspaces: captured graphs may still point into them
 
@@ -47,6 +48,16 @@ def set_attention_splits(splits: int) -> None:
     """Force the number of KV partitions per query row (0 = library default)."""
     global _forced_splits
     _forced_splits = int(splits)
+
+
+def set_stable_metadata(stable: bool) -> None:
+    """Promise (or withdraw the promise) that the kernel launched immediately before an `attention` call on its stream
+    never writes that call's `query_start_loc`, `seq_lens`, `block_table` or cached tokens (RQ_FLAG_STABLE_METADATA of
+    include/rq_b200.h).  A serving engine that builds its metadata once per step, like the reference's vLLM builder
+    (packed_backend.py:140-199), can promise it; the attention kernel then looks up its work and starts fetching pages
+    while the previous kernel is still running.  Off by default."""
+    global _stable_metadata
+    _stable_metadata = bool(stable)
 
 
 def _require(condition: bool, message: str) -> None:
@@ -299,6 +310,8 @@ def attention(
         args.workspace_bytes = workspace.numel()
         if one_call:
             args.flags = _lib.FLAG_SERIAL_LAUNCH   # the kernel follows the memset of its own counters
+        elif _stable_metadata:
+            args.flags = _lib.FLAG_STABLE_METADATA
         args.stream = torch.cuda.current_stream(query.device).cuda_stream
         _lib.check(lib.rq_attention(ctypes.byref(args)))
 

@@ -13,6 +13,7 @@ RQ_MAX_PEERS = 8
 RQ_PEER_HANDLE_BYTES = 64
 RQ_OK = 0
 FLAG_SERIAL_LAUNCH = 1
+FLAG_STABLE_METADATA = 2
 REFERENCE_MODES = {"anchor": 0, "adjacent": 1}
 COEFFICIENTS = {"unit": 0, "norm": 1, "ls": 2}
 CHAINS = {"kernel": 0, "calibration": 1}

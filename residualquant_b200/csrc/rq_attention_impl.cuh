@@ -26,8 +26,11 @@
 //   merge: each warp folds its 8 streams, the CTA folds its 4 warps, and -- when the row has several
 //          partitions -- the LAST CTA to arrive (one atomic ticket per (row, head)) folds the partitions, adds the
 //          live token, undoes an explicit value rotation and stores bf16.  No second launch, no spin wait.
-//   launch: as a programmatic dependent of the previous kernel of the stream: the prologue and the whole page loop only
-//          read global memory and may overlap that kernel's tail; griddepcontrol.wait sits in front of the first write.
+//   launch: as a programmatic dependent of the previous kernel of the stream.  Every CTA waits for the PREVIOUS kernel
+//          to complete (griddepcontrol.wait) before it reads anything, then lets the NEXT kernel be scheduled
+//          (griddepcontrol.launch_dependents) -- so launch latency and CTA scheduling overlap the previous kernel.  When the caller promises that this call's metadata and cache pages were not written by that
+//          previous kernel (early_start), the work lookup, the page-table fetch and the first page copies run BEFORE the
+//          wait as well (through L2 only: ld.global.cg / cp.async.cg), and only the q/k/v rows are read after it.
 //
 // The query rotation (signed Walsh-Hadamard) is fused into the prologue of every CTA (128 values, one warp).
 //
@@ -568,26 +571,28 @@ __device__ __forceinline__ float wave_count(float ctas, float slots, float sms) 
 //     row r gets max(1, ceil(pages_r / c)) partitions -- proportional to its length -- and the items are laid out
 //     request by request.  c is the candidate (4, 8, ..., 1024 pages, or "never split") with the lowest modelled time;
 //     a floor on c keeps the number of items within p.capacity, which fixed the grid on the host.
-// Every lane of the warp calls this with the same arguments and gets the same result.
+// Every lane of the warp calls this with the same arguments and gets the same result.  Metadata is read through L2
+// (ld.global.cg): with early_start this runs while the previous kernel of the stream may still be executing, and an L1
+// line left over from an earlier launch must not be trusted.
 template <int P>
 __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, int lane, WorkItem& out) {
     const int num_requests = p.num_requests;
-    const int total_rows = min(__ldg(p.query_start_loc + num_requests), p.num_rows);
+    const int total_rows = min(__ldcg(p.query_start_loc + num_requests), p.num_rows);
     if (p.splits > 0) {
         const int row = item / p.splits;
         if (row >= total_rows) return false;
         // Decode batches have one row per request, so request == row is the guess; it is re-read only if wrong.
         int request = min(row, num_requests - 1);
-        const int guess_begin = __ldg(p.query_start_loc + request), guess_end = __ldg(p.query_start_loc + request + 1);
-        int seq_len = __ldg(p.seq_lens + request);
+        const int guess_begin = __ldcg(p.query_start_loc + request), guess_end = __ldcg(p.query_start_loc + request + 1);
+        int seq_len = __ldcg(p.seq_lens + request);
         if (!(guess_begin <= row && row < guess_end)) {
             int lo = 0, hi = num_requests - 1;  // largest r with query_start_loc[r] <= row
             while (lo < hi) {
                 const int mid = (lo + hi + 1) >> 1;
-                if (p.query_start_loc[mid] <= row) lo = mid; else hi = mid - 1;
+                if (__ldcg(p.query_start_loc + mid) <= row) lo = mid; else hi = mid - 1;
             }
             request = lo;
-            seq_len = p.seq_lens[request];
+            seq_len = __ldcg(p.seq_lens + request);
         }
         out.row = row;
         out.request = request;
@@ -604,9 +609,9 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     auto load_request = [&](int r, int& begin, int& rows, int& pages, int& len) {
         begin = rows = pages = len = 0;
         if (r < num_requests) {
-            len = __ldg(p.seq_lens + r);
-            begin = __ldg(p.query_start_loc + r);
-            rows = max(0, min(__ldg(p.query_start_loc + r + 1), total_rows) - begin);
+            len = __ldcg(p.seq_lens + r);
+            begin = __ldcg(p.query_start_loc + r);
+            rows = max(0, min(__ldcg(p.query_start_loc + r + 1), total_rows) - begin);
             pages = rows > 0 ? (max(len - 1, 0) + P - 1) / P : 0;
         }
     };
@@ -692,11 +697,15 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     const int heads = p.heads;
     const int head = blockIdx.x % heads;
 
-    // Let the next kernel of the stream start its own prologue and page fetches while this one runs (it was launched as
-    // a programmatic dependent; without that attribute this is a no-op).  Everything up to pdl_wait() below only READS
-    // global memory: metadata, cache pages, the q/k/v rows.  The first write (partial results, counters, output) comes
-    // after pdl_wait(), i.e. after the previous kernel of the stream has completed.
-    pdl_launch_dependents();
+    // Nothing is read before the previous kernel of the stream has completed -- unless the caller vouched for the
+    // metadata and the cache pages (early_start): then only the q/k/v rows wait, further down.  Once the wait is over
+    // the NEXT kernel of the stream may be scheduled (it waits for this grid's completion in the same way); not
+    // earlier, so that at most two kernels of a stream are ever in flight together.
+    const bool early_start = p.early_start != 0;
+    if (!early_start) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
 
     // ---- which work item: (row, partition) and the row's request ---------------------------------------
     WorkItem work;
@@ -766,7 +775,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     int my_block = 0;
     auto load_batch = [&](int base) {
         batch_base = base;
-        my_block = base + lane < warp_pages ? table[page_begin + warp + kWarps * (base + lane)] : 0;
+        my_block = base + lane < warp_pages ? __ldcg(table + page_begin + warp + kWarps * (base + lane)) : 0;
     };
     load_batch(0);
     int issued = 0;
@@ -781,6 +790,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             }
             if (!kBulkCopy) cp_async_commit();
         }
+    }
+
+    if (early_start) {
+        pdl_wait();  // the q/k/v rows usually ARE the previous kernel's output
+        pdl_launch_dependents();
     }
 
     // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
@@ -1060,10 +1074,6 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         part_l += warp_stat[2 * w + 1] * f;
         if (tid < D) value += warp_acc[w * D + tid] * f;
     }
-
-    // From here on the CTA writes global memory (partial results, counters, output rows): the previous kernel of the
-    // stream -- which may still be reading or writing the same scratch and output buffers -- has to be complete.
-    pdl_wait();
 
     // ---- several partitions: park the partial, the last CTA to arrive folds them -----------------------
     if (splits > 1) {

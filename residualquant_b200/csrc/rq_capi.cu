@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <mutex>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -102,6 +103,38 @@ bool programmatic_launch_enabled() {
         g_programmatic.store(state, std::memory_order_relaxed);
     }
     return state != 0;
+}
+
+// Which cache the most recent rq_quantize on a stream wrote.  An attention call that reads the same cache next must not
+// start its page copies early (RQ_FLAG_STABLE_METADATA): the pages may still be in flight.  Any attention call clears the
+// stream's entry, since it then is the stream's most recent kernel of this library.
+struct RecentWrite { void* stream; const void* cache; bool used; };
+std::mutex g_recent_mutex;
+RecentWrite g_recent[32];
+void note_quantize(void* stream, const void* cache) {
+    std::lock_guard<std::mutex> lock(g_recent_mutex);
+    int slot = -1;
+    for (int i = 0; i < 32; ++i) {
+        if (g_recent[i].used && g_recent[i].stream == stream) { slot = i; break; }
+        if (!g_recent[i].used && slot < 0) slot = i;
+    }
+    if (slot < 0) slot = static_cast<int>((reinterpret_cast<uintptr_t>(stream) >> 4) % 32);  // table full: evict
+    g_recent[slot] = {stream, cache, true};
+}
+// true when the stream's most recent library kernel was a quantize that wrote `cache`; forgets the entry either way
+bool take_recent_write(void* stream, const void* cache) {
+    std::lock_guard<std::mutex> lock(g_recent_mutex);
+    bool all_used = true, hit = false, known = false;
+    for (int i = 0; i < 32; ++i) {
+        all_used = all_used && g_recent[i].used;
+        if (g_recent[i].used && g_recent[i].stream == stream) {
+            known = true;
+            hit = g_recent[i].cache == cache;
+            g_recent[i].used = false;
+        }
+    }
+    // a full table may have evicted this stream's entry: be cautious then
+    return hit || (!known && all_used);
 }
 
 size_t work_items(int32_t rows, int32_t heads, int32_t num_splits) {
@@ -233,6 +266,7 @@ int32_t rq_quantize(const RqQuantizeArgs* a) {
     }
     const cudaError_t err = rq::launch_quantize(p, s.head_dim, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "quantize launch");
+    note_quantize(a->stream, a->kv_cache);
     return RQ_OK;
 }
 
@@ -421,6 +455,10 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     p.capacity = capacity;
     p.sm_count = current_sm_count();
     p.programmatic_launch = programmatic_launch_enabled() && !(a->flags & RQ_FLAG_SERIAL_LAUNCH) ? 1 : 0;
+    const bool just_written = take_recent_write(a->stream, a->kv_cache);
+    // the dense query rotation launches a kernel of its own in front: the early start would overlap THAT kernel
+    p.early_start = p.programmatic_launch && (a->flags & RQ_FLAG_STABLE_METADATA) && !just_written &&
+                    a->key_rotation.kind != RQ_ROTATION_DENSE_FP16 ? 1 : 0;
     uint8_t* base = static_cast<uint8_t*>(a->workspace);
     p.status = reinterpret_cast<int32_t*>(base);
     p.counters = reinterpret_cast<int32_t*>(base + kStatusBytes);

@@ -87,6 +87,7 @@ struct AttentionParams {
     int capacity;                // work items per head the grid and the partial-result buffer provide (splits == 0)
     int sm_count;                // multiprocessors of the device (input of the on-device partition choice)
     int programmatic_launch;     // launch with the programmatic-stream-serialization attribute
+    int early_start;             // metadata and cache pages may be read before the previous kernel of the stream completed
     int32_t* status;
     int32_t* counters;
     float* partials;

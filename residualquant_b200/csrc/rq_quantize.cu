@@ -199,6 +199,10 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         if constexpr (S::kFixed) return r == S::kAnchor ? 32 : S::kResidualGroup; else return p.group[r];
     };
     constexpr int kSlices = D / 16;
+    // Launched as a programmatic dependent of the previous kernel of the stream: the launch itself overlaps that kernel;
+    // nothing is read or written before it has completed.  After that the next kernel may be scheduled.
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = lane & 7;
     const int token = blockIdx.x * 16 + warp * 4 + (lane >> 3);
@@ -341,9 +345,6 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         float y[16], mean[16];
         if (packed_rows) unpack(words, y, true); else load_unpacked(anchor, y, true);
         if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
-        // Launched as a programmatic dependent: the loads above may have overlapped the previous kernel of the stream
-        // (an attention call that is still reading these pages); the stores below wait for it to complete.
-        pdl_wait();
         if (centered) {
             load_mean(anchor, mean);
 #pragma unroll
@@ -435,6 +436,8 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
 template <int D, int RESIDUAL_GROUP>
 __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_constant__ QuantizeParams p) {
     constexpr int kSlices = D / 16, kAnchor = 3;
+    pdl_wait();  // see quantize_kernel
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = lane & 7, record = lane >> 3;
     const int token = blockIdx.x * 4 + warp;
@@ -477,8 +480,6 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
         }
     }
     if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
-    pdl_wait();  // everything above only read; the previous kernel of the stream may still be reading these pages
-
     const int P = p.page_tokens;
     const int tok = static_cast<int>(slot % P);
     uint8_t* page = p.cache + plane * p.plane_stride + (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width;

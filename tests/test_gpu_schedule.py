@@ -81,10 +81,12 @@ def test_serial_and_programmatic_launches_agree():
         assert np.array_equal(a, b)
 
 
-def test_back_to_back_calls_share_the_workspace_safely():
+@pytest.mark.parametrize("stable_metadata", [False, True])
+def test_back_to_back_calls_share_the_workspace_safely(stable_metadata):
     """Many attention calls in a row on one stream with no host synchronization in between (the decode step's pattern):
     each call's partial results and counters live in the same scratch as its predecessor's, and a programmatic
-    dependent may start before its predecessor has finished."""
+    dependent is scheduled before its predecessor has finished.  With the caller's promise of stable metadata the
+    work lookup and the first page copies of a call also run before its predecessor has finished."""
     from residualquant_b200 import _cuda
 
     case = helpers.make_case(44, 128, 8, [2000, 1100, 64, 3], 32, 16)
@@ -100,9 +102,13 @@ def test_back_to_back_calls_share_the_workspace_safely():
     live = [(G.bf16(case.keys[loop][case.live_rows]), G.bf16(case.values[loop][case.live_rows])) for loop in range(4)]
     outs = [torch.zeros_like(q) for _ in range(24)]
     torch.cuda.synchronize()
-    for i, out in enumerate(outs):
-        k, v = live[i % 4]
-        _cuda.attention(q, k, v, cache, out, qsl, seq, table, kr, vr, None, [list(r) for r in L.records], "anchor", 3, i % 4)
+    _cuda.set_stable_metadata(stable_metadata)
+    try:
+        for i, out in enumerate(outs):
+            k, v = live[i % 4]
+            _cuda.attention(q, k, v, cache, out, qsl, seq, table, kr, vr, None, [list(r) for r in L.records], "anchor", 3, i % 4)
+    finally:
+        _cuda.set_stable_metadata(False)
     torch.cuda.synchronize()
     for loop in range(4):
         want = helpers.oracle_attention(case, cache_np, loop)
@@ -208,3 +214,35 @@ def test_peer_barrier_wait_runs_out_and_reports_it():
     assert lib.rq_peer_barrier(ctypes.byref(b)) == 0
     assert lib.rq_peer_barrier_status(state.data_ptr(), b.stream) == 0
     assert state[0].item() == 2
+
+
+def test_early_start_is_withdrawn_right_after_a_write_to_the_same_cache():
+    """quantize then attention on the SAME cache, back to back on one stream with the stable-metadata promise given: the
+    library must notice that the pages were just written and keep the attention kernel behind the quantizer."""
+    from residualquant_b200 import _cuda
+
+    case = helpers.make_case(47, 128, 4, [900, 31], 32, 16)
+    L = case.layout
+    records = [list(r) for r in L.records]
+    kr, vr = G.device_rotations(case)
+    cache_np = helpers.oracle_cache(case)
+    want = helpers.oracle_attention(case, cache_np, 2)
+    pairs = [(G.bf16(k), G.bf16(v)) for k, v in zip(case.keys, case.values)]
+    slots = torch.from_numpy(case.slots).cuda()
+    rows = len(case.seq_lens)
+    q = G.bf16(case.query)
+    k, v = G.bf16(case.keys[2][case.live_rows]), G.bf16(case.values[2][case.live_rows])
+    qsl = torch.arange(rows + 1, dtype=torch.int32, device="cuda")
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    cache = torch.full((2, case.num_blocks, case.heads, L.page_tokens, L.page_width), 0xFF, dtype=torch.uint8, device="cuda")
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    _cuda.set_stable_metadata(True)
+    try:
+        _cuda.quantize(pairs, cache, slots, kr, vr, None, records, "anchor", 3, "ls")
+        _cuda.attention(q, k, v, cache, out, qsl, seq, table, kr, vr, None, records, "anchor", 3, 2)
+    finally:
+        _cuda.set_stable_metadata(False)
+    torch.cuda.synchronize()
+    assert _inside(out.float().cpu().numpy(), want)
