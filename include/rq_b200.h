@@ -171,7 +171,8 @@ typedef struct RqAttentionArgs {
     int32_t loop_index;             /* which record of the group this layer slot reads, 0 <= loop < num_records */
     int32_t num_splits;             /* 0 = the kernel cuts every row into KV partitions in proportion to its OWN length, read
                                        on the device (the reference's per-call schedule, attention/prepare.cuh:237-386);
-                                       n > 0 = exactly n partitions for every row */
+                                       n > 0 = exactly n partitions for every row;
+                                       n < 0 = partitions of -n pages each (length-proportional, chunk size forced) */
     void* workspace;                /* rq_attention_workspace_bytes() bytes, 256-byte aligned, zeroed once with
                                        rq_attention_workspace_init() before its first use */
     size_t workspace_bytes;
@@ -204,7 +205,10 @@ int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads);
  * (attention/launch.cuh:85-98). */
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits);
 /* Zero the counters and the status word (asynchronous, on `stream`).  Needed once per workspace; every call
- * leaves the counters zero again. */
+ * leaves the counters zero again, and the counters occupy the same 64 KiB of the workspace whatever the shape, so one
+ * workspace (sized for the largest call) can serve calls of different shapes one after the other.  Only calls with more
+ * than 16384 (row, head) pairs use a larger counter region: give those a workspace of their own, or initialise again
+ * when switching. */
 int32_t rq_attention_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 /* Split-KV online-softmax decode attention over the packed pages.  One launch. */
 int32_t rq_attention(const RqAttentionArgs* args);

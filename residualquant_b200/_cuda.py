@@ -31,7 +31,7 @@ __all__ = ("attention", "quantize", "set_quantizer_chain", "set_attention_splits
 _chain = "kernel"
 _forced_splits = 0
 _stable_metadata = False
-_workspaces: Dict[int, torch.Tensor] = {}
+_workspaces: Dict[object, torch.Tensor] = {}
 _superseded: List[torch.Tensor] = []   # earlier, smaller workspaces: captured graphs may still point into them
 
 
@@ -104,9 +104,10 @@ def _rotation_arg(rotation, device, heads: int, head_dim: int, keep: list) -> _l
     return out
 
 
-def _workspace(device: torch.device, nbytes: int) -> Tuple[torch.Tensor, bool]:
-    """(scratch buffer of at least `nbytes`, True when it was created for this one call during graph capture)."""
-    key = device.index or 0
+def _workspace(device: torch.device, nbytes: int, pairs: int) -> Tuple[torch.Tensor, bool]:
+    """(scratch buffer of at least `nbytes`, True when it was created for this one call during graph capture).
+    `pairs` = rows x heads: calls beyond 16384 pairs lay the buffer out differently and get buffers of their own."""
+    key = (device.index or 0) if pairs <= 16384 else ((device.index or 0), (pairs - 1).bit_length())
     buf = _workspaces.get(key)
     if buf is not None and buf.numel() >= nbytes:
         return buf, False
@@ -304,7 +305,7 @@ def attention(
         # 0: the kernel cuts every row into partitions in proportion to its own length, read on the device
         args.num_splits = _forced_splits
         nbytes = lib.rq_attention_workspace_bytes(rows, heads, head_dim, _forced_splits)
-        workspace, one_call = _workspace(query.device, nbytes)
+        workspace, one_call = _workspace(query.device, nbytes, rows * heads)
         keep.append(workspace)
         args.workspace = workspace.data_ptr()
         args.workspace_bytes = workspace.numel()
@@ -319,8 +320,7 @@ def attention(
 def attention_status(device=None) -> None:
     """Synchronize and raise if a bounded wait inside an attention kernel ever gave up on this device."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    buf = _workspaces.get(device.index or 0)
-    if buf is None:
-        return
     with torch.cuda.device(device):
-        _lib.check(_lib.load().rq_attention_status(buf.data_ptr(), torch.cuda.current_stream(device).cuda_stream))
+        for key, buf in list(_workspaces.items()):
+            if (key if isinstance(key, int) else key[0]) == (device.index or 0):
+                _lib.check(_lib.load().rq_attention_status(buf.data_ptr(), torch.cuda.current_stream(device).cuda_stream))

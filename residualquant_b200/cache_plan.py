@@ -83,3 +83,29 @@ def looped_model_owners(layers: int, groups_per_layer: int, records, heads: int,
     records = tuple(tuple(int(v) for v in r) for r in records)
     return {f"layers.{layer}.group.{group}": OwnerSpec(heads, head_dim, block_size, records)
             for layer in range(layers) for group in range(groups_per_layer)}
+
+
+def kv_footprint(packed_groups, layers: int, loops: int, heads: int, head_dim: int) -> int:
+    """Bytes of KV per cached token of the whole model: the reference's capacity experiment compares this figure
+    between configurations (experiments/kv_memory_latency/capacity.py:33-51).  An empty `packed_groups` means native
+    bf16 KV for every (layer, loop): 2 planes x layers x loops x heads x head_dim x 2 bytes.  Otherwise the groups'
+    records, in loop order, must cover every loop exactly once; every physical layer stores one packed row of
+    `page_width` bytes per head and plane for each group."""
+    if not packed_groups:
+        return 2 * layers * loops * heads * head_dim * 2
+    records = [tuple(record) for group in packed_groups for record in group]
+    if len(records) != loops:
+        raise ValueError("Invalid precision schedule or quantization group size")
+    try:
+        stride = page_width(records, head_dim)
+    except ValueError:
+        raise ValueError("Invalid precision schedule or quantization group size") from None
+    return 2 * layers * heads * stride
+
+
+def sequences_that_fit(budget_bytes: int, context: int, bytes_per_token: int, block_size: int = 16) -> int:
+    """Whole sequences of `context` tokens a KV budget holds when memory comes in blocks of `block_size` tokens and one
+    block stays reserved as the null block."""
+    blocks_per_sequence = (context + block_size - 1) // block_size
+    blocks = budget_bytes // (bytes_per_token * block_size)
+    return max(0, (blocks - 1) // blocks_per_sequence)

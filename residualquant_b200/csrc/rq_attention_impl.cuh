@@ -567,6 +567,7 @@ __device__ __forceinline__ float wave_count(float ctas, float slots, float sms) 
 // and parks in a work list; here every CTA derives the same answer from the sequence lengths in a few warp-wide
 // steps, so there is no extra launch and no list to read back.
 //   * p.splits > 0 (forced): every row has exactly p.splits partitions.
+//   * p.splits < 0: as below with the chunk size fixed by the caller to -p.splits pages (a tuning knob).
 //   * p.splits == 0: one chunk size c (pages) is chosen for the whole call from the TOTAL number of pages of the batch,
 //     row r gets max(1, ceil(pages_r / c)) partitions -- proportional to its length -- and the items are laid out
 //     request by request.  c is the candidate (4, 8, ..., 1024 pages, or "never split") with the lowest modelled time;
@@ -647,8 +648,13 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     uint32_t key = (__float_as_uint(cost) & ~15u) | static_cast<uint32_t>(kCandidates - candidate);
     if (my_items > p.capacity) key = 0xffffffffu;  // does not fit the grid ("never split" always does)
     const int chosen = kCandidates - static_cast<int>(__reduce_min_sync(kFullMask, key) & 15u);
-    const int shift = chosen + 2;  // chunk = 1 << shift pages; chosen == kCandidates: one partition per row
-    auto parts_of = [&](int pages) { return chosen < kCandidates ? max(1, (pages + (1 << shift) - 1) >> shift) : 1; };
+    int chunk = chosen < kCandidates ? 4 << chosen : 0x40000000;  // pages; "never split" = larger than any row
+    if (p.splits < 0) {
+        // the caller fixed the chunk size (pages); it still has to fit the capacity: sum ceil(pages / c) <= T / c + rows
+        const int spare = max(1, p.capacity - total_rows);
+        chunk = max(-p.splits, (total_pages + spare - 1) / spare);
+    }
+    auto parts_of = [&](int pages) { return max(1, (pages + chunk - 1) / chunk); };
 
     // pass 2: which request owns this item
     int before = 0;

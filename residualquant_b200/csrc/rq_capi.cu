@@ -77,6 +77,15 @@ int check_rotation(const RqRotation& r, const char* name) {
 constexpr size_t kStatusBytes = 256;
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Bytes reserved for the arrival counters.  The region has the SAME size for every call of up to 16384 (row, head)
+// pairs, so that one workspace can serve calls of different shapes: a counter slot of one call is never a
+// partial-result slot of another (partial results are left behind by every call, counters must read zero on entry).
+size_t counter_bytes(int64_t rows, int64_t heads) {
+    size_t bytes = 64 * 1024;
+    while (bytes < static_cast<size_t>(rows) * heads * sizeof(int32_t)) bytes *= 2;
+    return bytes;
+}
+
 // Multiprocessors of the current device, looked up once per device and process.
 int current_sm_count() {
     static std::atomic<int> cache[64];
@@ -316,8 +325,8 @@ int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads) {
 }
 
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits) {
-    if (num_query_rows < 0 || heads < 1 || head_dim < 1 || num_splits < 0) return 0;
-    const size_t counters = round_up(static_cast<size_t>(num_query_rows) * heads * sizeof(int32_t), 256);
+    if (num_query_rows < 0 || heads < 1 || head_dim < 1 || num_splits < -65536) return 0;
+    const size_t counters = counter_bytes(num_query_rows, heads);
     const size_t partials =
         num_splits != 1 ? work_items(num_query_rows, heads, num_splits) * heads * (head_dim + 2) * sizeof(float) : 0;
     const size_t rotated_query = round_up(static_cast<size_t>(num_query_rows) * heads * head_dim * sizeof(float), 256);
@@ -404,9 +413,9 @@ int32_t rq_attention(const RqAttentionArgs* a) {
 
     // 0 = the kernel cuts every row into partitions proportional to its length; n > 0 = exactly n per row
     const int splits = a->num_splits;
-    if (splits < 0 || splits > 1024) return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside 0..1024", splits);
-    const int capacity = splits == 0 ? rq_attention_work_capacity(a->num_query_rows, s.heads) : 0;
-    if (splits == 0 && capacity < a->num_query_rows) return fail(RQ_ERR_INVALID_ARGUMENT, "too many query rows in one call");
+    if (splits < -65536 || splits > 1024) return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside -65536..1024", splits);
+    const int capacity = splits <= 0 ? rq_attention_work_capacity(a->num_query_rows, s.heads) : 0;
+    if (splits <= 0 && capacity < a->num_query_rows) return fail(RQ_ERR_INVALID_ARGUMENT, "too many query rows in one call");
     if (static_cast<int64_t>(work_items(a->num_query_rows, s.heads, splits)) * s.heads > 0x7fffffffLL)
         return fail(RQ_ERR_INVALID_ARGUMENT, "grid too large");
     const size_t need = rq_attention_workspace_bytes(a->num_query_rows, s.heads, s.head_dim, splits);
@@ -462,8 +471,7 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     uint8_t* base = static_cast<uint8_t*>(a->workspace);
     p.status = reinterpret_cast<int32_t*>(base);
     p.counters = reinterpret_cast<int32_t*>(base + kStatusBytes);
-    p.partials = reinterpret_cast<float*>(
-        base + kStatusBytes + round_up(static_cast<size_t>(a->num_query_rows) * s.heads * sizeof(int32_t), 256));
+    p.partials = reinterpret_cast<float*>(base + kStatusBytes + counter_bytes(a->num_query_rows, s.heads));
     if (a->key_rotation.kind == RQ_ROTATION_DENSE_FP16) {
         // q @ R on the tensor cores, once per call, into the tail of the workspace
         const size_t partial_bytes =
@@ -535,8 +543,8 @@ int32_t rq_attention_noalloc(const RqAttentionArgs* a) {
     if (status != RQ_OK) return status;
     if ((status = check_spec(&a->spec)) != RQ_OK) return status;  // a bad spec is reported as such, not as a size problem
     if (a->num_query_rows <= 0) return rq_attention(a);            // nothing to launch; reuse the argument checks
-    if (a->num_splits < 0 || a->num_splits > 1024)
-        return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside 0..1024", a->num_splits);
+    if (a->num_splits < -65536 || a->num_splits > 1024)
+        return fail(RQ_ERR_INVALID_ARGUMENT, "num_splits %d outside -65536..1024", a->num_splits);
     const size_t need = rq_attention_workspace_bytes(a->num_query_rows, a->spec.heads, a->spec.head_dim, a->num_splits);
     if (need == 0 || need > RQ_STATIC_SCRATCH_BYTES)
         return fail(RQ_ERR_WORKSPACE,

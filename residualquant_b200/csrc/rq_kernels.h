@@ -51,8 +51,9 @@ cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t 
 
 // Layout of the attention workspace (all offsets multiples of 256 bytes):
 //   [0, 256)                         status word (int32) + padding
-//   [256, 256 + 4*rows*heads)        arrival counters, one int32 per (row, head)
-//   [partials_offset, ...)           float [work items][heads][head_dim + 2]  (max, denominator, value sums);
+//   [256, 256 + C)                   arrival counters, one int32 per (row, head); C = 64 KiB, or the next power of two
+//                                    that holds them: the same for every shape of up to 16384 (row, head) pairs
+//   [256 + C, ...)           float [work items][heads][head_dim + 2]  (max, denominator, value sums);
 //                                    work items = rows * splits, or the capacity when the device picks the partitions
 struct AttentionParams {
     const __nv_bfloat16* query;
@@ -80,7 +81,7 @@ struct AttentionParams {
     int chain_count;             // loop_index + 1 (0 in anchor mode)
     int chain_bits[4], chain_group[4];
     int chain_offset[5];         // bytes per token before record r; [chain_count] = bytes of the staged prefix
-    // Work decomposition.  splits > 0: every row is cut into exactly `splits` partitions (grid = rows * splits * heads).
+    // Work decomposition (splits < 0: as splits == 0 with the chunk size fixed to -splits pages).  splits > 0: every row is cut into exactly `splits` partitions (grid = rows * splits * heads).
     // splits == 0: the grid is capacity * heads and every CTA derives the (row, partition) of its work item from the
     // sequence lengths on the device: partitions per row proportional to the row's pages (see find_work).
     int splits;

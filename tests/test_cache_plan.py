@@ -43,3 +43,19 @@ def test_mixed_owners_share_one_block_space():
         cp.plan_cache(owners, plan.bytes_per_block * 256, 4096)
     with pytest.raises(ValueError, match="block sizes differ"):
         cp.plan_cache({"a": cp.OwnerSpec(8, 128, 16, G32), "b": cp.OwnerSpec(8, 128, 32, G32)}, 10**9, 128)
+
+
+def test_kv_footprint_per_token():
+    """The figures of the reference's capacity experiment for the Ouro-1.4B geometry (24 layers x 4 loops, 16 x 128)."""
+    geometry = dict(layers=24, loops=4, heads=16, head_dim=128)
+    assert cp.kv_footprint([], **geometry) == 786432                     # native bf16 KV
+    packed = cp.kv_footprint([[[2, 32]] * 3 + [[4, 32]]], **geometry)
+    assert packed == 2 * 24 * 16 * 200 == 153600 and 786432 / packed == pytest.approx(5.12)
+    assert cp.kv_footprint([[[2, 16]] * 3 + [[4, 32]]], **geometry) == 2 * 24 * 16 * 224
+    with pytest.raises(ValueError):
+        cp.kv_footprint([[[2, 32]] * 3], **geometry)                    # a loop without a record
+    with pytest.raises(ValueError):
+        cp.kv_footprint([[[3, 32]] * 4], **geometry)
+    # 100 GB of KV at context 8192: 79 sequences packed against 15 native
+    assert cp.sequences_that_fit(100 * 10**9, 8192, packed) == 79
+    assert cp.sequences_that_fit(100 * 10**9, 8192, 786432) == 15

@@ -59,14 +59,17 @@ def test_workspace_size_and_split_heuristic(built_library):
     one = lib.rq_attention_workspace_bytes(64, 16, 128, 1)
     four = lib.rq_attention_workspace_bytes(64, 16, 128, 4)
     rotated_query = 64 * 16 * 128 * 4
-    assert one == 256 + 4096 + rotated_query and four == one + 64 * 16 * 4 * 130 * 4
+    assert one == 256 + 65536 + rotated_query and four == one + 64 * 16 * 4 * 130 * 4
+    # the counter region is shape-independent up to 16384 (row, head) pairs, then the next power of two
+    assert lib.rq_attention_workspace_bytes(1, 1, 128, 1) == 256 + 65536 + 512
+    assert lib.rq_attention_workspace_bytes(2048, 16, 128, 1) == 256 + 131072 + 2048 * 16 * 128 * 4
     assert four % 256 == 0
     # num_splits 0: sized for the work capacity, which depends on rows, heads and the SM count only (148 without a GPU)
     capacity = lib.rq_attention_work_capacity(64, 16)
     assert capacity == 64 + (2 * 4 * 148 + 15) // 16
     assert lib.rq_attention_workspace_bytes(64, 16, 128, 0) == one + capacity * 16 * 130 * 4
     assert lib.rq_attention_work_capacity(1, 16) == 16 and lib.rq_attention_work_capacity(0, 16) == 0
-    assert lib.rq_attention_workspace_bytes(64, 16, 128, -1) == 0
+    assert lib.rq_attention_workspace_bytes(64, 16, 128, -100000) == 0
     assert 1 <= lib.rq_attention_default_splits(1, 16, 512, 16) <= 64
     assert lib.rq_attention_default_splits(1, 16, 512, 16) >= lib.rq_attention_default_splits(64, 16, 512, 16)
     assert lib.rq_attention_default_splits(64, 16, 1, 16) == 1

@@ -246,3 +246,26 @@ def test_early_start_is_withdrawn_right_after_a_write_to_the_same_cache():
         _cuda.set_stable_metadata(False)
     torch.cuda.synchronize()
     assert _inside(out.float().cpu().numpy(), want)
+
+
+def test_one_workspace_serves_calls_of_different_shapes():
+    """Partial results that a small call leaves behind must never sit where a later, larger call keeps its arrival
+    counters (which have to read zero): alternate a few-row call that splits every row with a many-row call."""
+    from residualquant_b200 import _cuda
+
+    small = helpers.make_case(48, 128, 2, [700, 40, 333], 32, 16)
+    rng = np.random.default_rng(9)
+    large = helpers.make_case(49, 128, 8, [int(v) for v in rng.integers(2, 300, size=96)], 32, 16)
+    caches = {}
+    for name, case in (("small", small), ("large", large)):
+        cache = G.gpu_cache(case)
+        caches[name] = (cache, helpers.oracle_attention(case, cache.cpu().numpy(), 0))
+    for round_ in range(2):
+        _cuda.set_attention_splits(7)
+        try:
+            got = G.gpu_attention(small, caches["small"][0], 0).float().cpu().numpy()
+        finally:
+            _cuda.set_attention_splits(0)
+        assert _inside(got, caches["small"][1]), f"small call, round {round_}"
+        got = G.gpu_attention(large, caches["large"][0], 0).float().cpu().numpy()
+        assert _inside(got, caches["large"][1]), f"large call, round {round_}"

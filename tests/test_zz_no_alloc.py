@@ -71,6 +71,10 @@ def test_noalloc_entry_matches_regular_entry_twice(splits):
         a.workspace, a.workspace_bytes = workspace.data_ptr(), nbytes
         _lib.check(lib.rq_attention(ctypes.byref(a)))
         torch.cuda.synchronize()
+        # The documented set-up: the first call on a device looks up the built-in buffer's address, which also makes
+        # the driver materialise the library's device data (8 MiB, once per device and process).
+        setup = _args(case, cache, q, k, v, torch.zeros_like(q), qsl, seq, table, kr, vr, loop, splits)
+        _lib.check(lib.rq_attention_noalloc(ctypes.byref(setup)))
         # allocation-free entry point, two calls in a row on the shared built-in scratch
         for attempt in range(2):
             out = torch.zeros_like(q)
@@ -121,7 +125,7 @@ def test_noalloc_entry_reports_a_bad_spec_as_such():
     a.spec.heads = 0
     assert lib.rq_attention_noalloc(ctypes.byref(a)) == -1          # RQ_ERR_INVALID_ARGUMENT, not a workspace error
     a.spec.heads = 4
-    a.num_splits = -2
+    a.num_splits = -100000
     assert lib.rq_attention_noalloc(ctypes.byref(a)) == -1
 
 
