@@ -52,9 +52,18 @@ extern "C" {
  *                              still read after it.  True under a serving engine, which writes the metadata once per
  *                              step and whose previous kernel is the projection that produces q/k/v.  The library
  *                              withdraws the early start by itself when the last rq_quantize on the stream wrote the
- *                              same cache. */
+ *                              same cache.
+ * RQ_FLAG_GATHER_PUBLISH       rq_attention with num_peers > 0: the CTA that finishes the call's last output row advances
+ *                              this rank's epoch (gather_state[0]) and publishes it in slot gather_rank of every
+ *                              peer's flag array, after all of the call's peer stores (system-scope release).
+ * RQ_FLAG_GATHER_WAIT          rq_attention with num_peers > 0: before a CTA reads q/k/v it waits (bounded by
+ *                              gather_timeout_ns) until every peer has published the epoch this rank has reached, i.e.
+ *                              until the PREVIOUS call's gathered rows are complete on this GPU -- the point where a
+ *                              model's next attention call depends on them through the output projection. */
 #define RQ_FLAG_SERIAL_LAUNCH 1
 #define RQ_FLAG_STABLE_METADATA 2
+#define RQ_FLAG_GATHER_PUBLISH 4
+#define RQ_FLAG_GATHER_WAIT 8
 
 typedef enum RqStatus {
     RQ_OK = 0,
@@ -188,6 +197,14 @@ typedef struct RqAttentionArgs {
     int64_t gather_stride;           /* ELEMENTS between rows of the gathered buffers (>= total heads * head_dim) */
     void* peer_output[RQ_MAX_PEERS];
     int32_t flags;                   /* RQ_FLAG_* */
+    /* Completion signal of the fused gather (RQ_FLAG_GATHER_PUBLISH / RQ_FLAG_GATHER_WAIT): the same flag arrays and
+     * state block rq_peer_barrier uses, so that no barrier kernel is needed between calls.  peer_flags[i] is GPU i's
+     * flag array uint32 [RQ_MAX_PEERS] as mapped into this process; gather_state is this rank's own 256 bytes
+     * ([0] epoch, [1] status, [2] arrival counter), zeroed once. */
+    void* peer_flags[RQ_MAX_PEERS];
+    void* gather_state;
+    int32_t gather_rank;
+    uint64_t gather_timeout_ns;      /* 0 = 2 s */
 } RqAttentionArgs;
 
 /* A uniform partition count for callers that want to force one (num_splits > 0): what a host-side cost model picks
@@ -254,6 +271,8 @@ typedef struct RqPeerBarrierArgs {
     void* state;
     uint64_t timeout_ns;
     void* stream;
+    int32_t wait_only; /* 1: do not publish; wait until every peer has published the epoch that this rank's attention
+                          calls have reached (RQ_FLAG_GATHER_PUBLISH) -- what a consumer of the gathered rows runs */
 } RqPeerBarrierArgs;
 int32_t rq_peer_barrier(const RqPeerBarrierArgs* args);
 /* Device memory that other processes of the node can map: a plain cudaMalloc (zero-filled), exported and opened

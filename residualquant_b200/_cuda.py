@@ -292,6 +292,7 @@ def attention(
     args.value_rotation = _rotation_arg(value_rotation, query.device, heads, head_dim, keep)
     args.key_mean = key_mean.data_ptr() if key_mean is not None else None
     args.loop_index = loop_index
+    gather_flags = 0
     if gather is not None:
         _require(gather.rows >= rows and gather.local_heads == heads and gather.head_dim == head_dim,
                  "gathered output buffers do not match the query shape")
@@ -301,6 +302,13 @@ def attention(
             args.peer_output[i] = pointer
         args.gather_head_offset = gather.head_offset
         args.gather_stride = gather.heads * head_dim
+        if getattr(gather, "signalled", False):
+            # no barrier kernel between calls: this call publishes its completion and first waits for the previous one's
+            for i, pointer in enumerate(gather.flag_pointers()):
+                args.peer_flags[i] = pointer
+            args.gather_state = gather.state.data_ptr()
+            args.gather_rank = gather.rank
+            gather_flags = _lib.FLAG_GATHER_PUBLISH | _lib.FLAG_GATHER_WAIT
     with torch.cuda.device(query.device):
         # 0: the kernel cuts every row into partitions in proportion to its own length, read on the device
         args.num_splits = _forced_splits
@@ -313,6 +321,7 @@ def attention(
             args.flags = _lib.FLAG_SERIAL_LAUNCH   # the kernel follows the memset of its own counters
         elif _stable_metadata:
             args.flags = _lib.FLAG_STABLE_METADATA
+        args.flags |= gather_flags
         args.stream = torch.cuda.current_stream(query.device).cuda_stream
         _lib.check(lib.rq_attention(ctypes.byref(args)))
 

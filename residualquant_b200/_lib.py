@@ -14,6 +14,8 @@ RQ_PEER_HANDLE_BYTES = 64
 RQ_OK = 0
 FLAG_SERIAL_LAUNCH = 1
 FLAG_STABLE_METADATA = 2
+FLAG_GATHER_PUBLISH = 4
+FLAG_GATHER_WAIT = 8
 REFERENCE_MODES = {"anchor": 0, "adjacent": 1}
 COEFFICIENTS = {"unit": 0, "norm": 1, "ls": 2}
 CHAINS = {"kernel": 0, "calibration": 1}
@@ -120,6 +122,10 @@ class RqAttentionArgs(ctypes.Structure):
         ("gather_stride", ctypes.c_int64),
         ("peer_output", ctypes.c_void_p * RQ_MAX_PEERS),
         ("flags", ctypes.c_int32),
+        ("peer_flags", ctypes.c_void_p * RQ_MAX_PEERS),
+        ("gather_state", ctypes.c_void_p),
+        ("gather_rank", ctypes.c_int32),
+        ("gather_timeout_ns", ctypes.c_uint64),
     ]
 
 
@@ -131,6 +137,7 @@ class RqPeerBarrierArgs(ctypes.Structure):
         ("state", ctypes.c_void_p),
         ("timeout_ns", ctypes.c_uint64),
         ("stream", ctypes.c_void_p),
+        ("wait_only", ctypes.c_int32),
     ]
 
 

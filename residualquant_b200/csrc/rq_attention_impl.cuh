@@ -549,6 +549,7 @@ struct WorkItem {
     int row, request, seq_len;
     int part, parts;  // this CTA's partition of the row and how many the row has
     int first;        // index of the row's first work item: partial results of the row sit at items first .. first+parts-1
+    int total_rows;   // query rows of the call that are not graph padding
 };
 
 // Cost of running `items` equally sized CTAs per head, in units of (pages one CTA consumes while four share an SM):
@@ -596,6 +597,7 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
             seq_len = __ldcg(p.seq_lens + request);
         }
         out.row = row;
+        out.total_rows = total_rows;
         out.request = request;
         out.seq_len = seq_len;
         out.parts = p.splits;
@@ -676,6 +678,7 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
             const int owner_parts = __shfl_sync(kFullMask, parts, src);
             const int row_in_request = owner_parts == 1 ? local : local / owner_parts;
             out.request = base + src;
+            out.total_rows = total_rows;
             out.seq_len = __shfl_sync(kFullMask, len, src);
             out.row = __shfl_sync(kFullMask, begin, src) + row_in_request;
             out.parts = owner_parts;
@@ -686,6 +689,27 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
         before += __shfl_sync(kFullMask, upto, 31);
     }
     return false;
+}
+
+// Wait until peer `peer` has published the epoch this rank has reached (gather_state[0]: one per completed call).  Bounded
+// by the GPU's global timer and a poll count; on expiry the status word of the state block is raised and the call goes on.
+__device__ __forceinline__ void wait_for_peers(const AttentionParams& p, int peer) {
+    const uint32_t target = __ldcg(p.gather_state);
+    const uint32_t* arrival = p.gather_flags[p.gather_rank] + peer;
+    unsigned long long start = 0;
+    for (uint32_t polls = 0;; ++polls) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrival) : "memory");
+        if (static_cast<int32_t>(seen - target) >= 0) return;  // a fast peer may already be a call ahead
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (polls == 0) start = now;
+        if (polls > 64) __nanosleep(100);
+        if (polls > (1u << 26) || now - start > p.gather_timeout_ns) {
+            atomicExch(p.gather_state + 1, static_cast<uint32_t>(RQ_ERR_DEVICE_TIMEOUT));
+            return;
+        }
+    }
 }
 
 template <class C>
@@ -802,6 +826,9 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         pdl_wait();  // the q/k/v rows usually ARE the previous kernel's output
         pdl_launch_dependents();
     }
+    // Head-sharded serving: q depends, through the output projection, on the gathered rows of the previous call, so this
+    // is where the call waits for every peer's stores of that call (bounded; ordered before the barrier below).
+    if (p.gather_wait && warp == 1 && lane < p.num_peers) wait_for_peers(p, lane);
 
     // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
     float* misc = warp_stat + 8;         // [0] last-arrival flag, [1] live score, [2] max |q|
@@ -1168,6 +1195,22 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         // memory or a peer's over NVLink); a warp writes 64 contiguous bytes per peer
         const int64_t gathered = static_cast<int64_t>(row) * p.gather_stride + (p.gather_head_offset + head) * D + tid;
         for (int peer = 0; peer < p.num_peers; ++peer) p.peer_output[peer][gathered] = result;
+    }
+    if (p.gather_publish) {
+        // The CTA that finishes the call's last (row, head) tells every GPU that this rank's rows are in place.
+        __threadfence_system();  // this CTA's peer stores are performed before its ticket is taken
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t ticket = atomicAdd(p.gather_state + 2, 1u);
+            if (ticket + 1u == static_cast<uint32_t>(work.total_rows) * static_cast<uint32_t>(heads)) {
+                p.gather_state[2] = 0u;  // ready for the next call
+                __threadfence_system();  // every other CTA's stores (ordered before its ticket) before the flag
+                const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.gather_state) + 1u;
+                *reinterpret_cast<volatile uint32_t*>(p.gather_state) = epoch;
+                for (int peer = 0; peer < p.num_peers; ++peer)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather_flags[peer] + p.gather_rank), "r"(epoch) : "memory");
+            }
+        }
     }
 }
 

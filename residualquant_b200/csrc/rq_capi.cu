@@ -507,6 +507,20 @@ int32_t rq_attention(const RqAttentionArgs* a) {
         p.num_peers = a->num_peers;
         p.gather_head_offset = a->gather_head_offset;
         p.gather_stride = a->gather_stride;
+        if (a->flags & (RQ_FLAG_GATHER_PUBLISH | RQ_FLAG_GATHER_WAIT)) {
+            if (a->gather_state == nullptr || !aligned(a->gather_state, 8) || a->gather_rank < 0 || a->gather_rank >= a->num_peers)
+                return fail(RQ_ERR_INVALID_ARGUMENT, "the gather signal needs this rank's state block and a rank below num_peers");
+            for (int i = 0; i < a->num_peers; ++i) {
+                if (a->peer_flags[i] == nullptr || !aligned(a->peer_flags[i], 4))
+                    return fail(RQ_ERR_INVALID_ARGUMENT, "peer_flags[%d] must be a mapped uint32 array", i);
+                p.gather_flags[i] = static_cast<uint32_t*>(a->peer_flags[i]);
+            }
+            p.gather_state = static_cast<uint32_t*>(a->gather_state);
+            p.gather_rank = a->gather_rank;
+            p.gather_publish = (a->flags & RQ_FLAG_GATHER_PUBLISH) ? 1 : 0;
+            p.gather_wait = (a->flags & RQ_FLAG_GATHER_WAIT) ? 1 : 0;
+            p.gather_timeout_ns = a->gather_timeout_ns ? a->gather_timeout_ns : 2000000000ull;
+        }
     }
     const cudaError_t err = rq::launch_attention(v, p, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "attention launch");
@@ -587,6 +601,7 @@ int32_t rq_peer_barrier(const RqPeerBarrierArgs* a) {
     p.world = a->world;
     p.rank = a->rank;
     p.timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
+    p.wait_only = a->wait_only ? 1 : 0;
     const cudaError_t err = rq::launch_peer_barrier(p, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "peer barrier launch");
     return RQ_OK;

@@ -96,6 +96,12 @@ struct AttentionParams {
     int num_peers, gather_head_offset;
     int64_t gather_stride;
     __nv_bfloat16* peer_output[RQ_MAX_PEERS];
+    // Completion signal of the fused gather: flag arrays of every GPU, this rank's state block ([0] epoch, [1] status,
+    // [2] arrival counter), what this call does with them.
+    uint32_t* gather_flags[RQ_MAX_PEERS];
+    uint32_t* gather_state;
+    int gather_rank, gather_publish, gather_wait;
+    unsigned long long gather_timeout_ns;
 };
 
 // Node-level barrier kernel behind rq_peer_barrier.
@@ -104,6 +110,7 @@ struct PeerBarrierParams {
     uint32_t* state;  // [0] epoch, [1] status
     int world, rank;
     unsigned long long timeout_ns;
+    int wait_only;
 };
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream);
 

@@ -36,14 +36,17 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant_
     __shared__ uint32_t next_epoch;
     const int t = threadIdx.x;
     if (t == 0) {
-        next_epoch = p.state[0] + 1u;
-        p.state[0] = next_epoch;
+        // wait-only: the epoch was advanced and published by this rank's attention kernels; just wait for the peers
+        next_epoch = p.wait_only ? p.state[0] : p.state[0] + 1u;
+        if (!p.wait_only) p.state[0] = next_epoch;
     }
     __syncwarp();
     const uint32_t epoch = next_epoch;
     if (t >= p.world) return;
-    __threadfence_system();
-    store_release_system(p.flags[t] + p.rank, epoch);
+    if (!p.wait_only) {
+        __threadfence_system();
+        store_release_system(p.flags[t] + p.rank, epoch);
+    }
     const uint32_t* arrival = p.flags[p.rank] + t;
     const unsigned long long start = global_timer_ns();
     for (unsigned long long polls = 0;; ++polls) {

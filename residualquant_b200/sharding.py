@@ -107,9 +107,17 @@ class HeadGather:
     once every rank's stores have landed.  With two buffers used alternately and one barrier per call, a rank can start
     the next call while a slower peer still reads the previous result, because nobody passes barrier n before everyone
     entered it, and entering barrier n means being done with buffer n-2.
+
+    `signalled=True` drops the barrier kernel between calls: the attention kernel itself publishes "this rank's rows of
+    call n are in place" from its last CTA, and the NEXT attention call -- which in a model depends on the gathered rows
+    through the output projection -- waits for every peer's signal of call n before it reads its inputs.  The same
+    two-buffer rule holds: a rank publishes call n+1 only after its own wait for call n, so whoever has seen every
+    rank's signal n+1 knows that buffer n%2 is no longer being read.  `barrier()` then is the consumer's wait alone
+    (no publish), to be called wherever something other than the next attention call reads the gathered rows.
     """
 
-    def __init__(self, rows: int, heads: int, head_dim: int, device, buffers: int = 2):
+    def __init__(self, rows: int, heads: int, head_dim: int, device, buffers: int = 2, signalled: bool = False):
+        self.signalled = signalled
         self.lib = _lib.load()
         self.device = torch.device(device)
         self.rows, self.heads, self.head_dim, self.buffers = rows, heads, head_dim, buffers
@@ -165,9 +173,14 @@ class HeadGather:
             args.flags[i] = base + self.flag_offset
         args.state = self.state.data_ptr()
         args.timeout_ns = timeout_ns
+        args.wait_only = 1 if self.signalled else 0
         with torch.cuda.device(self.device):
             args.stream = torch.cuda.current_stream(self.device).cuda_stream
             _lib.check(self.lib.rq_peer_barrier(ctypes.byref(args)))
+
+    def flag_pointers(self) -> List[int]:
+        """Every rank's flag array as mapped into this process."""
+        return [base + self.flag_offset for base in self.bases]
 
     def check(self) -> None:
         """Synchronize the current stream and raise if a barrier ever timed out."""

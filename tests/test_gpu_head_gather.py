@@ -1,6 +1,6 @@
 """Fused head gather on one GPU: the attention kernel stores its rows into a gathered buffer at a head offset and the
-barrier kernel of a one-rank world completes (the multi-rank form needs several GPUs and is exercised by
-`bench.py --shard heads` under torchrun)."""
+barrier kernel of a one-rank world completes; the barrier-free form, in which the kernel publishes its own completion
+and the next call waits for it.  (Several ranks: tests/test_gpu_head_gather_multi.py, which needs two GPUs.)"""
 
 import numpy as np
 import pytest
@@ -78,5 +78,44 @@ def test_gather_arguments_are_checked():
                             None, None, None, [list(r) for r in case.layout.records], "anchor", 3, 0, gather=gather)
         with pytest.raises(ValueError):
             gather.peer_pointers(1)
+    finally:
+        gather.close()
+
+
+def test_kernel_published_completion_replaces_the_barrier():
+    """Signalled gather: no barrier kernel between calls.  Every call advances the epoch from inside the kernel (last CTA)
+    and publishes it; the following call waits for it before reading its inputs; the consumer-side wait at the end
+    finds the last epoch in place."""
+    from residualquant_b200 import _cuda, sharding
+
+    case = helpers.make_case(73, 128, 3, [300, 33, 1, 90], 32, 16)
+    cache = torch.from_numpy(helpers.oracle_cache(case)).cuda()
+    rows = len(case.seq_lens)
+    gather = sharding.HeadGather(rows, case.heads, 128, "cuda", buffers=2, signalled=True)
+    try:
+        L = case.layout
+        kr, vr = G.device_rotations(case)
+        q = G.bf16(case.query)
+        qsl = torch.arange(rows + 1, dtype=torch.int32, device="cuda")
+        seq = torch.from_numpy(case.seq_lens).cuda()
+        table = torch.from_numpy(case.block_table).cuda()
+        outs = []
+        for call, loop in enumerate((0, 1, 2, 3, 0, 3)):
+            k = G.bf16(case.keys[loop][case.live_rows])
+            v = G.bf16(case.values[loop][case.live_rows])
+            out = torch.zeros_like(q)
+            _cuda.attention(q, k, v, cache, out, qsl, seq, table, kr, vr, None, [list(r) for r in L.records],
+                            L.reference_mode, L.anchor_index, loop, gather=gather, gather_buffer=call % 2)
+            outs.append((loop, call % 2, out))
+        gather.barrier()         # wait only
+        gather.check()
+        torch.cuda.synchronize()
+        assert gather.state[:3].tolist() == [6, 0, 0]          # six epochs published, no timeout, counter back at zero
+        flags = gather._bytes[gather.flag_offset: gather.flag_offset + 4].view(torch.int32)
+        assert int(flags[0]) == 6
+        for loop, buffer, out in outs[-2:]:
+            assert torch.equal(gather.gathered(buffer), out)
+            want = helpers.oracle_attention(case, cache.cpu().numpy(), loop)
+            assert np.all(np.abs(out.float().cpu().numpy() - want) <= 2e-2 + 1e-2 * np.abs(want))
     finally:
         gather.close()
