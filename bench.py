@@ -679,17 +679,17 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
     shape = Shape(batch=16, context=4096, layers=32, heads=55, head_dim=96, page=16, group=32)
     local = sharding.shard_counts(shape.heads, world)[rank]
     stack = Stack(shape, device, torch, heads_here=local, seed_offset=1000 + rank)
-    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device, signalled=True)
+    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
 
     def step():
-        # Every attention call publishes its completion from inside the kernel and waits for the previous call's gather
-        # before it reads q (the dependency a model has through its output projection); one consumer-side wait at the
-        # end of the step stands for whatever reads the last gathered rows.
+        # One barrier kernel per call, launched as a programmatic dependent (resident while the attention kernel runs).
+        # The barrier-free form (HeadGather(signalled=True): the kernel's last CTA publishes, the next call waits)
+        # measured slower on two GPUs: one system-scope fence per finishing CTA costs more than the launch it saves.
         for layer in range(shape.layers):
             for loop in range(4):
                 stack.attention(layer, loop, gather=gather, gather_buffer=loop % 2)
+                gather.barrier()
             stack.quantize(layer)
-        gather.barrier()
         stack.seq_lens.add_(1)
         stack.advance()
 
@@ -708,9 +708,9 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
     flags = torch.tensor([1 if equal else 0], device=device)
     if world > 1:
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
-    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 32 write launches + 1 "
-                       "wait launch per step, INT2 g32 + INT4 g32; output rows stored into every GPU's gathered buffer by the "
-                       "attention kernel, completion published by its last CTA",
+    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 128 barrier + 32 "
+                       "write launches per step, INT2 g32 + INT4 g32; output rows stored into every GPU's gathered buffer by the "
+                       "attention kernel",
               "n": world, "heads_per_rank": sharding.shard_counts(shape.heads, world),
               "tokens_per_s": shape.batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
               "gathered_equal_nccl": bool(flags.item() == 1), "scaling": "strong"}

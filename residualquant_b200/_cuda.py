@@ -308,7 +308,8 @@ def attention(
                 args.peer_flags[i] = pointer
             args.gather_state = gather.state.data_ptr()
             args.gather_rank = gather.rank
-            gather_flags = _lib.FLAG_GATHER_PUBLISH | _lib.FLAG_GATHER_WAIT
+            gather_flags = ((_lib.FLAG_GATHER_PUBLISH if getattr(gather, "publish", True) else 0)
+                            | (_lib.FLAG_GATHER_WAIT if getattr(gather, "wait", True) else 0))
     with torch.cuda.device(query.device):
         # 0: the kernel cuts every row into partitions in proportion to its own length, read on the device
         args.num_splits = _forced_splits

@@ -1198,9 +1198,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
     if (p.gather_publish) {
         // The CTA that finishes the call's last (row, head) tells every GPU that this rank's rows are in place.
-        __threadfence_system();  // this CTA's peer stores are performed before its ticket is taken
+        // One system-scope fence per CTA, by the thread that takes the ticket, after the CTA barrier: the barrier orders
+        // every thread's peer stores before the fence, and the fence is cumulative (the pattern of a grid-wide barrier).
         __syncthreads();
         if (tid == 0) {
+            __threadfence_system();
             const uint32_t ticket = atomicAdd(p.gather_state + 2, 1u);
             if (ticket + 1u == static_cast<uint32_t>(work.total_rows) * static_cast<uint32_t>(heads)) {
                 p.gather_state[2] = 0u;  // ready for the next call

@@ -602,6 +602,7 @@ int32_t rq_peer_barrier(const RqPeerBarrierArgs* a) {
     p.rank = a->rank;
     p.timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
     p.wait_only = a->wait_only ? 1 : 0;
+    p.programmatic_launch = programmatic_launch_enabled() ? 1 : 0;
     const cudaError_t err = rq::launch_peer_barrier(p, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "peer barrier launch");
     return RQ_OK;

@@ -111,6 +111,7 @@ struct PeerBarrierParams {
     int world, rank;
     unsigned long long timeout_ns;
     int wait_only;
+    int programmatic_launch;
 };
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream);
 

@@ -11,6 +11,7 @@
 // The wait is bounded twice (global timer and a poll count).  On expiry the kernel records RQ_ERR_DEVICE_TIMEOUT and
 // returns; it never traps and never spins without limit.  Ranks wait for kernels running on OTHER GPUs only: never
 // launch two ranks of one barrier on the same GPU.
+#include "rq_common.cuh"
 #include "rq_kernels.h"
 
 namespace rq {
@@ -35,6 +36,11 @@ __device__ __forceinline__ uint32_t load_acquire_system(const uint32_t* address)
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant__ PeerBarrierParams p) {
     __shared__ uint32_t next_epoch;
     const int t = threadIdx.x;
+    // Launched as a programmatic dependent: the CTA is resident while the kernel in front of it (the attention call whose
+    // stores this barrier covers) still runs, and starts the moment that kernel has completed and flushed.  The kernel
+    // behind it may be scheduled at once; it waits for this grid's completion itself.
+    pdl_wait();
+    pdl_launch_dependents();
     if (t == 0) {
         // wait-only: the epoch was advanced and published by this rank's attention kernels; just wait for the peers
         next_epoch = p.wait_only ? p.state[0] : p.state[0] + 1u;
@@ -63,8 +69,16 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant_
 }  // namespace
 
 cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t stream) {
-    peer_barrier_kernel<<<1, 32, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(1);
+    config.blockDim = dim3(32);
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = p.programmatic_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&config, peer_barrier_kernel, p);
 }
 
 }  // namespace rq
