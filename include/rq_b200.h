@@ -92,8 +92,9 @@ typedef enum RqRotationKind {
      * set when sign[h][c] is -1.  H_128 is the Sylvester matrix, H_96 = Paley-12 (x) Sylvester-8
      * (scripts/calibration/rotation_math.py:6-32). */
     RQ_ROTATION_SIGNED_HADAMARD = 1,
-    /* dense fp16 [heads][head_dim][head_dim], y = x @ R (common/api.h:42-55): any learned rotation.  Rotated by a
-     * separate tensor-core launch (TF32 products, fp32 accumulation) into caller-provided scratch. */
+    /* dense fp16 [heads][head_dim][head_dim], y = x @ R (common/api.h:42-55): any learned rotation.  The quantizer
+     * rotates inside its own CTAs (TF32 tensor-core products, fp32 accumulation, rows staged in shared memory); the
+     * attention call rotates the query rows with one small launch in front of its kernel. */
     RQ_ROTATION_DENSE_FP16 = 2
 } RqRotationKind;
 
@@ -141,17 +142,16 @@ typedef struct RqQuantizeArgs {
     int32_t coefficient;     /* RqCoefficient */
     int32_t chain;           /* RqChain */
     void* stream;
-    void* workspace;         /* only for RQ_ROTATION_DENSE_FP16: rq_quantize_workspace_bytes() bytes, 16-byte aligned */
+    void* workspace;         /* unused: no rotation kind needs scratch (rq_quantize_workspace_bytes() is 0) */
     size_t workspace_bytes;
     int32_t flags;           /* RQ_FLAG_* */
 } RqQuantizeArgs;
 
-/* Scratch a quantize call needs: fp32 copies of the rotated rows of every plane whose rotation is dense
- * (num_records * num_tokens * heads * head_dim * 4 bytes per such plane), 0 otherwise. */
+/* Scratch a quantize call needs: always 0 (dense rotations are applied inside the quantizer's CTAs). */
 size_t rq_quantize_workspace_bytes(const RqGroupSpec* spec, int64_t num_tokens, int32_t key_rotation_kind,
                                    int32_t value_rotation_kind);
-/* Rotate, quantize and bit-pack the K/V rows of every record of a group into their pages.  One launch
- * (plus one rotation launch per plane with a dense rotation). */
+/* Rotate, quantize and bit-pack the K/V rows of every record of a group into their pages.  One launch (two for
+ * a long write in which exactly one plane has a dense rotation). */
 int32_t rq_quantize(const RqQuantizeArgs* args);
 
 typedef struct RqAttentionArgs {

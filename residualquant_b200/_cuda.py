@@ -192,13 +192,6 @@ def quantize(
     args.key_mean = key_mean.data_ptr() if key_mean is not None else None
     args.coefficient = _lib.COEFFICIENTS[coefficient_method]
     args.chain = _lib.CHAINS[_chain]
-    scratch_bytes = lib.rq_quantize_workspace_bytes(ctypes.byref(args.spec), slot_mapping.numel(), args.key_rotation.kind,
-                                                    args.value_rotation.kind)
-    if scratch_bytes:
-        scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=kv_cache.device)  # caching allocator: graph safe
-        keep.append(scratch)
-        args.workspace = scratch.data_ptr()
-        args.workspace_bytes = scratch_bytes
     with torch.cuda.device(kv_cache.device):
         args.stream = torch.cuda.current_stream(kv_cache.device).cuda_stream
         _lib.check(lib.rq_quantize(ctypes.byref(args)))

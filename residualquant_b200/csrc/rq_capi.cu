@@ -169,9 +169,9 @@ int32_t rq_record_offset(const RqGroupSpec* spec, int32_t index) {
 }
 
 size_t rq_quantize_workspace_bytes(const RqGroupSpec* spec, int64_t num_tokens, int32_t key_kind, int32_t value_kind) {
-    if (spec == nullptr || num_tokens <= 0 || spec->num_records < 1 || spec->heads < 1 || spec->head_dim < 1) return 0;
-    const size_t plane = static_cast<size_t>(spec->num_records) * num_tokens * spec->heads * spec->head_dim * sizeof(float);
-    return (key_kind == RQ_ROTATION_DENSE_FP16 ? plane : 0) + (value_kind == RQ_ROTATION_DENSE_FP16 ? plane : 0);
+    // Kept for callers written against the first version of this interface: no rotation kind needs scratch any more.
+    (void)spec; (void)num_tokens; (void)key_kind; (void)value_kind;
+    return 0;
 }
 
 int32_t rq_quantize(const RqQuantizeArgs* a) {
@@ -242,36 +242,13 @@ int32_t rq_quantize(const RqQuantizeArgs* a) {
     p.chain = a->chain;
     p.vector_loads = vector_loads ? 1 : 0;
     p.programmatic_launch = programmatic_launch_enabled() && !(a->flags & RQ_FLAG_SERIAL_LAUNCH) ? 1 : 0;
-    // Dense learned rotations: one tensor-core launch per plane writes the rotated rows to the caller's scratch.
-    const size_t need = rq_quantize_workspace_bytes(&s, a->num_tokens, a->key_rotation.kind, a->value_rotation.kind);
-    if (need > 0) {
+    // Dense learned rotations are applied inside the quantizer CTA (tensor-core product in shared memory).
+    for (int plane = 0; plane < 2; ++plane) {
+        const RqRotation& rot = plane == 0 ? a->key_rotation : a->value_rotation;
+        if (rot.kind != RQ_ROTATION_DENSE_FP16) continue;
         if (a->chain == RQ_CHAIN_CALIBRATION)
             return fail(RQ_ERR_UNSUPPORTED, "the calibration chain needs an invertible structured rotation");
-        if (a->workspace == nullptr || !aligned(a->workspace, 16) || a->workspace_bytes < need)
-            return fail(RQ_ERR_WORKSPACE, "dense rotations need %zu bytes of 16-byte aligned workspace, got %zu", need,
-                        a->workspace_bytes);
-        float* cursor = static_cast<float*>(a->workspace);
-        for (int plane = 0; plane < 2; ++plane) {
-            const RqRotation& rot = plane == 0 ? a->key_rotation : a->value_rotation;
-            if (rot.kind != RQ_ROTATION_DENSE_FP16) continue;
-            rq::RotateParams rp;
-            memset(&rp, 0, sizeof(rp));
-            for (int r = 0; r < s.num_records; ++r) {
-                rp.source[r] = plane == 0 ? p.key[r] : p.value[r];
-                rp.source_stride[r] = plane == 0 ? p.key_stride[r] : p.value_stride[r];
-            }
-            rp.num_sources = s.num_records;
-            rp.matrix = static_cast<const __half*>(rot.data);
-            rp.output = cursor;
-            rp.slots = a->slot_mapping;
-            rp.num_rows = p.num_tokens;
-            rp.heads = s.heads;
-            rp.scale = 1.f;
-            const cudaError_t rerr = rq::launch_rotate(rp, s.head_dim, static_cast<cudaStream_t>(a->stream));
-            if (rerr != cudaSuccess) return fail_cuda(rerr, "rotation launch");
-            p.rotated_rows[plane] = cursor;
-            cursor += static_cast<size_t>(s.num_records) * p.num_tokens * s.heads * s.head_dim;
-        }
+        p.dense_matrix[plane] = static_cast<const __half*>(rot.data);
     }
     const cudaError_t err = rq::launch_quantize(p, s.head_dim, static_cast<cudaStream_t>(a->stream));
     if (err != cudaSuccess) return fail_cuda(err, "quantize launch");

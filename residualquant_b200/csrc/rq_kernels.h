@@ -28,9 +28,12 @@ struct QuantizeParams {
     int num_records, anchor, mode, coefficient, chain;
     int bits[RQ_MAX_RECORDS], group[RQ_MAX_RECORDS], record_offset[RQ_MAX_RECORDS];
     int vector_loads;         // rows are 16-byte aligned
-    // Dense learned rotation: rows already rotated by rotate_rows_kernel, fp32 [records][tokens][heads][head_dim]
-    // per plane (nullptr = read the bf16 inputs and rotate with the fused Walsh-Hadamard transform, or not at all).
-    const float* rotated_rows[2];
+    // Dense learned rotation per plane: fp16 [heads][head_dim][head_dim], y = x @ R, applied inside the quantizer CTA
+    // (nullptr = rotate with the fused Walsh-Hadamard transform, or not at all).
+    const __half* dense_matrix[2];
+    int plane_first;          // a launch covers planes plane_first .. plane_first + gridDim.z - 1
+    int dense_tiles;          // tiles of 16 tokens a CTA of the fused dense kernel walks over
+    int dense_planes;         // planes its launch covers (gridDim.z)
     int programmatic_launch;  // launch with the programmatic-stream-serialization attribute
 };
 

@@ -11,6 +11,7 @@
 // Work split: a row = one (token, head, plane); 8 lanes own a row, each lane 16 consecutive channels, so a
 // warp owns 4 consecutive tokens of one head and a 128-thread CTA 16 consecutive tokens (one vLLM block when
 // the slots are contiguous).  Grid = (ceil(tokens/16), heads, 2 planes).
+#include <atomic>
 #include <type_traits>
 
 #include "rq_common.cuh"
@@ -186,8 +187,17 @@ struct Anchor2224 {
     static constexpr int kRecords = 4, kAnchor = 3, kResidualGroup = RESIDUAL_GROUP;
 };
 
-template <int D, class S>
-__global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant__ QuantizeParams p) {
+// Row stride (floats) of a tile of rotated rows in shared memory: conflict-free for the MMA fragment loads.
+template <int D>
+constexpr int kTileStride = D + 4;
+
+// Everything that happens to the rows of one (token, head, plane): the anchor record, then the residual records.
+// Eight lanes own the row (lane j: channels 16j .. 16j+15); `token` is the lane group's token.  SHARED_ROWS: the rows
+// were rotated by a dense matrix into `tile` (shared memory, fp32 [record * 16 + token % 16][kTileStride]) by
+// quantize_dense_kernel; otherwise they are read from the caller's bf16 tensors and rotated here if the plane has a
+// signed-Hadamard rotation.
+template <int D, class S, bool SHARED_ROWS>
+__device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token, int head, int plane, const float* tile) {
     // run-time values, or the schedule's constants
     const int num_records = [&] { if constexpr (S::kFixed) return S::kRecords; else return p.num_records; }();
     const int anchor = [&] { if constexpr (S::kFixed) return S::kAnchor; else return p.anchor; }();
@@ -199,14 +209,8 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
         if constexpr (S::kFixed) return r == S::kAnchor ? 32 : S::kResidualGroup; else return p.group[r];
     };
     constexpr int kSlices = D / 16;
-    // Launched as a programmatic dependent of the previous kernel of the stream: the launch itself overlaps that kernel;
-    // nothing is read or written before it has completed.  After that the next kernel may be scheduled.
-    pdl_wait();
-    pdl_launch_dependents();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
     const int j = lane & 7;
-    const int token = blockIdx.x * 16 + warp * 4 + (lane >> 3);
-    const int head = blockIdx.y, plane = blockIdx.z;
 
     int64_t slot = -1;
     if (token < p.num_tokens) slot = p.slots[token];
@@ -215,8 +219,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
 
     const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
     const int64_t* strides = plane == 0 ? p.key_stride : p.value_stride;
-    const bool rotated = p.rotation[plane] == RQ_ROTATION_SIGNED_HADAMARD;
-    const float* pre_rotated = p.rotated_rows[plane];  // dense rotation already applied by rotate_rows_kernel
+    const bool rotated = !SHARED_ROWS && p.rotation[plane] == RQ_ROTATION_SIGNED_HADAMARD;
     const float rscale = p.rscale[plane];
     uint32_t sign16 = 0;
     if (rotated && j < kSlices)
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
                     (active ? (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width : 0);
 
     // Rows of 16-byte aligned bf16 tensors are fetched as two 16-byte words per lane, one record ahead of their use.
-    const bool packed_rows = p.vector_loads && pre_rotated == nullptr;
+    const bool packed_rows = p.vector_loads && !SHARED_ROWS;
     auto fetch_packed = [&](int r, uint32_t (&w)[8]) {
         uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
         if (active) {
@@ -255,17 +258,16 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
             x[2 * i + 1] = __uint_as_float(flipped & 0xffff0000u);
         }
     };
-    // the other two sources: fp32 rows already rotated by the dense path, and bf16 rows without 16-byte alignment
+    // the other two sources: fp32 rows rotated by the dense path (shared memory), and bf16 rows without 16-byte alignment
     auto load_unpacked = [&](int r, float (&x)[16], bool flip) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = 0.f;
         if (!active) return;
-        if (pre_rotated != nullptr) {
-            const float4* src4 = reinterpret_cast<const float4*>(
-                pre_rotated + ((static_cast<int64_t>(r) * p.num_tokens + token) * p.heads + head) * D + 16 * j);
+        if constexpr (SHARED_ROWS) {
+            const float4* src4 = reinterpret_cast<const float4*>(tile + (r * 16 + (threadIdx.x >> 3)) * kTileStride<D> + 16 * j);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float4 v = __ldg(src4 + i);
+                const float4 v = src4[i];
                 x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
             }
             return;
@@ -427,6 +429,140 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
     }
 }
 
+template <int D, class S>
+__global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant__ QuantizeParams p) {
+    // Launched as a programmatic dependent of the previous kernel of the stream: the launch itself overlaps that kernel;
+    // nothing is read or written before it has completed.  After that the next kernel may be scheduled.
+    pdl_wait();
+    pdl_launch_dependents();
+    const int token = blockIdx.x * 16 + (threadIdx.x >> 3);  // a warp owns 4 consecutive tokens of one head
+    quantize_rows<D, S, false>(p, token, blockIdx.y, p.plane_first + blockIdx.z, nullptr);
+}
+
+// ---- dense (learned) rotation fused into the quantizer ------------------------------------------------------------
+// y = x @ R[h] for every record's row, on the tensor cores, inside the CTA that quantizes the rows: R[h] is staged once
+// per CTA in shared memory (fp32: bf16 inputs and fp16 matrix entries are exact in TF32, fp32 accumulation, like the
+// reference's rotation, plugins/residual_quantization/csrc/quantize/rotation.cuh:25-150), the CTA then walks over
+// kDenseTiles tiles of 16 tokens: stage the tile's records x 16 rows, rotate them in place (one 16-row MMA tile per
+// warp and record), quantize them from shared memory.  Nothing goes through global memory in between.
+constexpr int kDenseTiles = 4;  // long writes: 64 tokens per CTA, the matrix is read once per 64 tokens of a head
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int D>
+constexpr int kMatrixStride = D + 8;  // floats per row of the staged matrix: conflict-free B-fragment loads
+
+template <int D>
+size_t dense_shared_bytes(int num_records) {
+    return (static_cast<size_t>(D) * kMatrixStride<D> + static_cast<size_t>(num_records) * 16 * kTileStride<D>) * sizeof(float);
+}
+
+template <int D, class S>
+__global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_constant__ QuantizeParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float dense_shared[];
+    float* matrix = dense_shared;                      // [D][kMatrixStride]
+    float* tile = dense_shared + D * kMatrixStride<D>;  // [records * 16][kTileStride]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int head = blockIdx.y, plane = p.plane_first + blockIdx.z;
+    const int num_records = [&] { if constexpr (S::kFixed) return S::kRecords; else return p.num_records; }();
+    const int tiles = p.dense_tiles;
+    if (p.dense_matrix[plane] == nullptr) {
+        // the other plane of the same call has no dense rotation: same launch, plain path
+        for (int step = 0; step < tiles; ++step)
+            quantize_rows<D, S, false>(p, (blockIdx.x * tiles + step) * 16 + (tid >> 3), head, plane, nullptr);
+        return;
+    }
+
+    // R[h]: fp16 [D][D] -> fp32 in shared memory, 8 entries per 16-byte load
+    const uint4* r = reinterpret_cast<const uint4*>(p.dense_matrix[plane] + static_cast<int64_t>(head) * D * D);
+    for (int i = tid; i < D * D / 8; i += 128) {
+        const uint4 packed = __ldg(r + i);
+        const int k = (8 * i) / D, n = (8 * i) % D;
+        const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+        float* dst = matrix + k * kMatrixStride<D> + n;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
+            dst[2 * w] = pair.x;
+            dst[2 * w + 1] = pair.y;
+        }
+    }
+    const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
+    const int64_t* strides = plane == 0 ? p.key_stride : p.value_stride;
+
+    for (int step = 0; step < tiles; ++step) {
+        const int first = (blockIdx.x * tiles + step) * 16;
+        if (first >= p.num_tokens) break;  // uniform over the CTA
+        __syncthreads();  // the previous tile has been quantized (and, the first time, the matrix is staged below the next barrier)
+        // stage: records x 16 rows of D bf16 -> fp32; rows of padding slots or beyond the call stay zero
+        const int chunks = num_records * 16 * (D / 8);
+        for (int i = tid; i < chunks; i += 128) {
+            const int row = i / (D / 8), c8 = i % (D / 8);
+            const int record = row >> 4, token = first + (row & 15);
+            float values[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (token < p.num_tokens && p.slots[token] >= 0) {
+                const __nv_bfloat16* x = sources[record] + static_cast<int64_t>(token) * strides[record] + head * D + 8 * c8;
+                if (p.vector_loads) {
+                    const uint4 packed = __ldg(reinterpret_cast<const uint4*>(x));
+                    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        values[2 * w] = __uint_as_float(words[w] << 16);
+                        values[2 * w + 1] = __uint_as_float(words[w] & 0xffff0000u);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) values[e] = __bfloat162float(x[e]);
+                }
+            }
+            float4* dst = reinterpret_cast<float4*>(tile + row * kTileStride<D> + 8 * c8);
+            dst[0] = make_float4(values[0], values[1], values[2], values[3]);
+            dst[1] = make_float4(values[4], values[5], values[6], values[7]);
+        }
+        __syncthreads();
+        // rotate in place: warp w takes the 16-row tiles w, w + 4, ... (one per record in a four-record group)
+        const int g = lane >> 2, t = lane & 3;
+        for (int block = warp; block < num_records; block += 4) {
+            float* rows = tile + block * 16 * kTileStride<D>;
+            float acc[D / 8][4];
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+#pragma unroll 2
+            for (int k = 0; k < D; k += 8) {
+                uint32_t a[4];
+                a[0] = __float_as_uint(rows[g * kTileStride<D> + k + t]);
+                a[1] = __float_as_uint(rows[(g + 8) * kTileStride<D> + k + t]);
+                a[2] = __float_as_uint(rows[g * kTileStride<D> + k + t + 4]);
+                a[3] = __float_as_uint(rows[(g + 8) * kTileStride<D> + k + t + 4]);
+#pragma unroll
+                for (int n = 0; n < D / 8; ++n) {
+                    uint32_t b[2];
+                    b[0] = __float_as_uint(matrix[(k + t) * kMatrixStride<D> + 8 * n + g]);
+                    b[1] = __float_as_uint(matrix[(k + t + 4) * kMatrixStride<D> + 8 * n + g]);
+                    mma_tf32(acc[n], a, b);
+                }
+            }
+            __syncwarp();  // every lane has read the rows it needs before they are overwritten
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+                *reinterpret_cast<float2*>(rows + g * kTileStride<D> + 8 * n + 2 * t) = make_float2(acc[n][0], acc[n][1]);
+                *reinterpret_cast<float2*>(rows + (g + 8) * kTileStride<D> + 8 * n + 2 * t) = make_float2(acc[n][2], acc[n][3]);
+            }
+        }
+        __syncthreads();
+        quantize_rows<D, S, true>(p, first + (tid >> 3), head, plane, tile);
+    }
+}
+
 // Decode-sized writes of the headline schedule: a handful of tokens, so latency is what counts.  One warp per
 // (token, head, plane); its four 8-lane groups take the four records of the token side by side: every group loads
 // and rotates its own record at the same time, the last group's anchor is quantized and its bf16 reconstruction is
@@ -441,7 +577,7 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = lane & 7, record = lane >> 3;
     const int token = blockIdx.x * 4 + warp;
-    const int head = blockIdx.y, plane = blockIdx.z;
+    const int head = blockIdx.y, plane = p.plane_first + blockIdx.z;
     if (token >= p.num_tokens) return;
     const int64_t slot = p.slots[token];
     if (slot < 0) return;  // padding (the whole warp)
@@ -535,10 +671,11 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
 }
 
 template <class Kernel>
-cudaError_t launch_with_order(Kernel kernel, dim3 grid, const QuantizeParams& p, cudaStream_t stream) {
+cudaError_t launch_with_order(Kernel kernel, dim3 grid, size_t shared_bytes, const QuantizeParams& p, cudaStream_t stream) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = dim3(128);
+    config.dynamicSmemBytes = shared_bytes;
     config.stream = stream;
     cudaLaunchAttribute attribute;
     attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -548,34 +685,85 @@ cudaError_t launch_with_order(Kernel kernel, dim3 grid, const QuantizeParams& p,
     return cudaLaunchKernelEx(&config, kernel, p);
 }
 
+// The dense kernel needs more than the default 48 KB of dynamic shared memory: raised once per device and instantiation.
+template <class Kernel>
+cudaError_t allow_shared_bytes(Kernel kernel, size_t bytes, std::atomic<unsigned long long>& configured) {
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    const unsigned long long bit = 1ull << (device & 63);
+    if (configured.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (err == cudaSuccess) configured.fetch_or(bit, std::memory_order_release);
+    return err;
+}
+
+template <int D, class S>
+cudaError_t launch_dense(const QuantizeParams& p, cudaStream_t stream) {
+    static std::atomic<unsigned long long> configured{0ull};
+    const size_t bytes = dense_shared_bytes<D>(RQ_MAX_RECORDS);  // the attribute covers every group size
+    cudaError_t err = allow_shared_bytes(quantize_dense_kernel<D, S>, bytes, configured);
+    if (err != cudaSuccess) return err;
+    const dim3 grid((p.num_tokens + 16 * p.dense_tiles - 1) / (16 * p.dense_tiles), p.heads, p.dense_planes);
+    return launch_with_order(quantize_dense_kernel<D, S>, grid, dense_shared_bytes<D>(p.num_records), p, stream);
+}
+
+// One launch for the planes `first` .. `first + count - 1`, none of which has a dense rotation.
+cudaError_t launch_plain(QuantizeParams p, int head_dim, bool headline, int first, int count, cudaStream_t stream) {
+    p.plane_first = first;
+    const dim3 grid((p.num_tokens + 15) / 16, p.heads, count);
+    // decode-sized writes of aligned bf16 rows: one warp per token with the records side by side
+    if (headline && p.num_tokens <= 256 && p.vector_loads) {
+        const dim3 token_grid((p.num_tokens + 3) / 4, p.heads, count);
+        if (head_dim == 128 && p.group[0] == 32) return launch_with_order(quantize_token_kernel<128, 32>, token_grid, 0, p, stream);
+        if (head_dim == 128) return launch_with_order(quantize_token_kernel<128, 16>, token_grid, 0, p, stream);
+        if (p.group[0] == 32) return launch_with_order(quantize_token_kernel<96, 32>, token_grid, 0, p, stream);
+        return launch_with_order(quantize_token_kernel<96, 16>, token_grid, 0, p, stream);
+    }
+    if (headline && p.group[0] == 32) {
+        if (head_dim == 128) return launch_with_order(quantize_kernel<128, Anchor2224<32>>, grid, 0, p, stream);
+        return launch_with_order(quantize_kernel<96, Anchor2224<32>>, grid, 0, p, stream);
+    }
+    if (headline && p.group[0] == 16) {
+        if (head_dim == 128) return launch_with_order(quantize_kernel<128, Anchor2224<16>>, grid, 0, p, stream);
+        return launch_with_order(quantize_kernel<96, Anchor2224<16>>, grid, 0, p, stream);
+    }
+    if (head_dim == 128) return launch_with_order(quantize_kernel<128, AnySchedule>, grid, 0, p, stream);
+    return launch_with_order(quantize_kernel<96, AnySchedule>, grid, 0, p, stream);
+}
+
+cudaError_t launch_dense_planes(QuantizeParams p, int head_dim, bool headline, int first, int count, cudaStream_t stream) {
+    p.plane_first = first;
+    p.dense_planes = count;
+    // short (decode-sized) writes: one tile per CTA, so that the few tokens spread over as many SMs as possible
+    p.dense_tiles = p.num_tokens <= 1024 ? 1 : kDenseTiles;
+    if (headline && p.group[0] == 32)
+        return head_dim == 128 ? launch_dense<128, Anchor2224<32>>(p, stream) : launch_dense<96, Anchor2224<32>>(p, stream);
+    if (headline && p.group[0] == 16)
+        return head_dim == 128 ? launch_dense<128, Anchor2224<16>>(p, stream) : launch_dense<96, Anchor2224<16>>(p, stream);
+    return head_dim == 128 ? launch_dense<128, AnySchedule>(p, stream) : launch_dense<96, AnySchedule>(p, stream);
+}
+
 }  // namespace
 
+// Neither plane dense: one launch.  A dense plane: short (decode-sized) writes still take one launch -- the fused
+// kernel covers both planes and a plane without a dense rotation takes the plain path inside it, because there the
+// launch is what costs; long writes take one launch per plane, so that the plain plane runs at the plain kernel's
+// higher occupancy.  No scratch buffer and no separate rotation launch either way.
 cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream) {
-    const dim3 grid((p.num_tokens + 15) / 16, p.heads, 2);
     const bool headline = p.num_records == 4 && p.anchor == 3 && p.mode == RQ_REFERENCE_ANCHOR &&
                           p.coefficient == RQ_COEFF_LS && p.chain == RQ_CHAIN_KERNEL && p.bits[3] == 4 && p.group[3] == 32 &&
                           p.bits[0] == 2 && p.bits[1] == 2 && p.bits[2] == 2 && p.group[0] == p.group[1] &&
                           p.group[1] == p.group[2];
-    // decode-sized writes of aligned bf16 rows: one warp per token with the records side by side
-    const bool few_tokens = headline && p.num_tokens <= 256 && p.vector_loads && p.rotated_rows[0] == nullptr &&
-                            p.rotated_rows[1] == nullptr;
-    if (few_tokens) {
-        const dim3 token_grid((p.num_tokens + 3) / 4, p.heads, 2);
-        if (head_dim == 128 && p.group[0] == 32) return launch_with_order(quantize_token_kernel<128, 32>, token_grid, p, stream);
-        if (head_dim == 128) return launch_with_order(quantize_token_kernel<128, 16>, token_grid, p, stream);
-        if (p.group[0] == 32) return launch_with_order(quantize_token_kernel<96, 32>, token_grid, p, stream);
-        return launch_with_order(quantize_token_kernel<96, 16>, token_grid, p, stream);
+    const bool dense[2] = {p.dense_matrix[0] != nullptr, p.dense_matrix[1] != nullptr};
+    if (!dense[0] && !dense[1]) return launch_plain(p, head_dim, headline, 0, 2, stream);
+    if (p.num_tokens <= 1024 || (dense[0] && dense[1])) return launch_dense_planes(p, head_dim, headline, 0, 2, stream);
+    for (int plane = 0; plane < 2; ++plane) {
+        const cudaError_t err = dense[plane] ? launch_dense_planes(p, head_dim, headline, plane, 1, stream)
+                                             : launch_plain(p, head_dim, headline, plane, 1, stream);
+        if (err != cudaSuccess) return err;
     }
-    if (headline && p.group[0] == 32) {
-        if (head_dim == 128) return launch_with_order(quantize_kernel<128, Anchor2224<32>>, grid, p, stream);
-        return launch_with_order(quantize_kernel<96, Anchor2224<32>>, grid, p, stream);
-    }
-    if (headline && p.group[0] == 16) {
-        if (head_dim == 128) return launch_with_order(quantize_kernel<128, Anchor2224<16>>, grid, p, stream);
-        return launch_with_order(quantize_kernel<96, Anchor2224<16>>, grid, p, stream);
-    }
-    if (head_dim == 128) return launch_with_order(quantize_kernel<128, AnySchedule>, grid, p, stream);
-    return launch_with_order(quantize_kernel<96, AnySchedule>, grid, p, stream);
+    return cudaSuccess;
 }
 
 }  // namespace rq

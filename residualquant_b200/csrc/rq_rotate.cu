@@ -1,13 +1,15 @@
-// Dense rotation of bf16 rows by a learned fp16 matrix: y[t][h][:] = x[t][h][:] @ R[h]   (fp32 out).
+// Dense rotation of bf16 rows by a learned fp16 matrix: y[t][h][:] = x[t][h][:] @ R[h]   (fp32 out).  Used for the
+// query rows of an attention call (one row per request); the quantizer rotates inside its own kernel (rq_quantize.cu).
 //
-// This is the one GEMM-shaped piece of the path (the reference runs it inside its quantizer and its query
-// preparation with TF32 m16n8k8 MMAs that re-read R from global memory for every 8 tokens:
-// plugins/residual_quantization/csrc/quantize/rotation.cuh:25-150, attention/prepare.cuh:61-145).
+// The reference runs this product inside its query preparation with TF32 m16n8k8 MMAs
+// (plugins/residual_quantization/csrc/attention/prepare.cuh:61-145).
 // Here R[h] is staged once per CTA in shared memory and reused for 64 rows.  bf16 inputs and fp16 matrix entries
 // are both exactly representable in TF32, so every product is exact and the accumulation is fp32, as in the
 // reference; only the summation order differs.
 //
 // CTA = 64 rows (tokens) x 1 head x 1 source tensor, 4 warps; warp = 16 rows x all D columns.
+#include <atomic>
+
 #include "rq_common.cuh"
 #include "rq_kernels.h"
 
@@ -100,16 +102,22 @@ cudaError_t launch_rotate(const RotateParams& p, int head_dim, cudaStream_t stre
     if (p.num_rows <= 0 || p.num_sources <= 0) return cudaSuccess;
     const dim3 grid((p.num_rows + kRotateRows - 1) / kRotateRows, p.heads, p.num_sources);
     const size_t smem = rotate_shared_bytes(head_dim);
-    cudaError_t err;
-    if (head_dim == 128) {
-        err = cudaFuncSetAttribute(rotate_rows_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    // the shared-memory limit is raised once per device (bit d of the mask = device d is configured), not per launch
+    static std::atomic<unsigned long long> configured[2];
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    const unsigned long long bit = 1ull << (device & 63);
+    std::atomic<unsigned long long>& done = configured[head_dim == 128 ? 0 : 1];
+    if (!(done.load(std::memory_order_acquire) & bit)) {
+        err = head_dim == 128
+                  ? cudaFuncSetAttribute(rotate_rows_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))
+                  : cudaFuncSetAttribute(rotate_rows_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess) return err;
-        rotate_rows_kernel<128><<<grid, 128, smem, stream>>>(p);
-    } else {
-        err = cudaFuncSetAttribute(rotate_rows_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (err != cudaSuccess) return err;
-        rotate_rows_kernel<96><<<grid, 128, smem, stream>>>(p);
+        done.fetch_or(bit, std::memory_order_release);
     }
+    if (head_dim == 128) rotate_rows_kernel<128><<<grid, 128, smem, stream>>>(p);
+    else rotate_rows_kernel<96><<<grid, 128, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
