@@ -21,8 +21,9 @@ Printed JSON line:
   other_shapes  the same kernels with INT2 g16 residuals, and at 55 heads x 96 (batch 16 x 4096)
   bf16_kv_comparator  a BF16-KV decode attention (library kernel, contiguous KV) of one layer's four loops
   reference_cuda  the reference's own CUDA kernels on the same GPU, cache and inputs, when oracle/_ref holds its build
-  head_sharded  (N > 1 only) the 55 x 96 shape with the KV heads spread over the ranks and the output gather fused
-            into the attention kernel
+  head_sharded  the 55 x 96 shape with the KV heads spread over the ranks and the output gather fused into the
+            attention kernel (strong scaling; the one-GPU run gives the curve's first point)
+  config2_model_decode  a random-init Ouro-1.4B-shaped looped decoder: decode tokens/s with packed KV against BF16 KV
   cpu_baseline  the reference's PyTorch statement of the path (FP32Chain.reconstruct + probabilities + p @ V) timed on
             this machine's host cores; the numpy restatement when those files are absent
 
@@ -719,6 +720,124 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
     return result
 
 
+class LoopedDecoder:
+    """Random-init Ouro-1.4B-shaped looped decoder for the model-level comparison (BASELINE configuration 2): 24 layers
+    shared by 4 loops, hidden 2048, 16 heads x 128, SwiGLU FFN 5632, vocabulary 49152, bf16 weights N(0, 0.02).  The
+    projections are library GEMMs (they are outside the two hot paths); rotary embedding is left out (an elementwise
+    kernel that both arms would share).  Layer order and KV grouping follow the reference's adapter
+    (plugins/looped_transformers/src/looped_transformers/ouro.py:141-158, 231-241): `for loop: for layer:`, one KV group
+    of 4 loops per physical layer, written by the last loop."""
+
+    def __init__(self, torch, device, batch, layers=24, hidden=2048, heads=16, head_dim=128, ffn=5632, vocab=49152):
+        self.torch, self.device, self.batch = torch, device, batch
+        self.layers, self.hidden, self.heads, self.head_dim, self.ffn = layers, hidden, heads, head_dim, ffn
+        gen = torch.Generator(device=device)
+        gen.manual_seed(2024)
+
+        def weight(*shape):
+            return (0.02 * torch.randn(*shape, device=device, generator=gen)).bfloat16()
+
+        self.embed = weight(vocab, hidden)
+        self.lm_head = weight(hidden, vocab)
+        self.qkv = [weight(hidden, 3 * heads * head_dim) for _ in range(layers)]
+        self.out = [weight(heads * head_dim, hidden) for _ in range(layers)]
+        self.gate_up = [weight(hidden, 2 * ffn) for _ in range(layers)]
+        self.down = [weight(ffn, hidden) for _ in range(layers)]
+        self.norms = [[torch.ones(hidden, device=device, dtype=torch.bfloat16) for _ in range(3)] for _ in range(layers)]
+        self.final_norm = torch.ones(hidden, device=device, dtype=torch.bfloat16)
+        self.tokens = torch.randint(100, 10000, (batch,), device=device, generator=gen)
+
+    def weight_bytes_per_step(self, loops=4):
+        per_layer = sum(w[0].numel() for w in (self.qkv, self.out, self.gate_up, self.down)) * 2
+        return loops * self.layers * per_layer + self.lm_head.numel() * 2
+
+    def step(self, attention, end_of_layer, loops=4):
+        """One decode step.  `attention(layer, loop, q, k, v) -> [B, H, D]`; `end_of_layer(layer)` after the last loop."""
+        torch, F = self.torch, self.torch.nn.functional
+        B, H, D = self.batch, self.heads, self.head_dim
+        x = self.embed[self.tokens]
+        for loop in range(loops):
+            for layer in range(self.layers):
+                n1, n2, n3 = self.norms[layer]
+                qkv = (F.rms_norm(x, (self.hidden,), n1) @ self.qkv[layer]).view(B, 3, H, D)
+                o = attention(layer, loop, qkv[:, 0], qkv[:, 1], qkv[:, 2])
+                x = x + F.rms_norm(o.reshape(B, H * D) @ self.out[layer], (self.hidden,), n2)
+                gate_up = F.rms_norm(x, (self.hidden,), n3) @ self.gate_up[layer]
+                x = x + (F.silu(gate_up[:, : self.ffn]) * gate_up[:, self.ffn:]) @ self.down[layer]
+                if loop == loops - 1:
+                    end_of_layer(layer)
+            x = F.rms_norm(x, (self.hidden,), self.final_norm)
+        self.tokens.copy_((x @ self.lm_head).argmax(-1))
+
+
+def model_decode_figures(timer, torch, device, batch=32, prompt=2048, generated=128, steps=24):
+    """BASELINE configuration 2: decode tokens/s of the looped decoder with the packed KV path against the same decoder
+    with BF16 KV, same GPU, same GEMMs, CUDA-graph replay, prefill and the first token excluded (the reference's
+    protocol, experiments/kv_memory_latency/measure.py:347-360).  Both arms run at the mean context of the generated
+    tokens (prompt + generated / 2): the BF16 arm is a library attention call whose KV length is baked into the captured
+    graph, so neither arm's context grows during the timed steps (the packed arm's lengths are reset between replays)."""
+    from residualquant_b200 import _cuda
+
+    context = prompt + generated // 2
+    shape = Shape(batch=batch, context=context, layers=24)
+    stack = Stack(shape, device, torch, seed_offset=31)
+    model = LoopedDecoder(torch, device, batch)
+    F = torch.nn.functional
+    B, H, D = batch, shape.heads, shape.head_dim
+    _cuda.set_stable_metadata(True)
+    pending = [[] for _ in range(shape.layers)]
+    outputs = torch.zeros(shape.layers, 4, B, H, D, device=device, dtype=torch.bfloat16)
+
+    def packed_attention(layer, loop, q, k, v):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out = outputs[layer, loop]
+        _cuda.attention(q, k, v, stack.caches[layer], out, stack.qsl, stack.seq_lens, stack.block_table, stack.key_rot, None,
+                        None, stack.records, "anchor", 3, loop)
+        pending[layer].append((k, v))
+        return out
+
+    def packed_end_of_layer(layer):
+        _cuda.quantize(pending[layer], stack.caches[layer], stack.slot_mapping, stack.key_rot, None, None, stack.records,
+                       "anchor", 3, "ls")
+        pending[layer].clear()
+
+    def packed_step():
+        model.step(packed_attention, packed_end_of_layer)
+        # the next replay starts from the same context: lengths and slots are left as they are
+
+    stack.seq_lens.fill_(context)
+    stack.advance()
+    packed_ms = timer.graph_ms(packed_step, steps)
+
+    # BF16 KV: [layer][loop] K and V, contiguous [B, H, context, D]; the new token overwrites the last position
+    kv = torch.empty(shape.layers, 4, 2, B, H, context, D, device=device, dtype=torch.bfloat16)
+    for layer in range(shape.layers):
+        kv[layer].normal_()
+
+    def bf16_attention(layer, loop, q, k, v):
+        cache_k, cache_v = kv[layer, loop, 0], kv[layer, loop, 1]
+        cache_k[:, :, context - 1] = k
+        cache_v[:, :, context - 1] = v
+        return F.scaled_dot_product_attention(q.unsqueeze(2), cache_k, cache_v).squeeze(2)
+
+    bf16_ms = timer.graph_ms(lambda: model.step(bf16_attention, lambda layer: None), steps)
+    packed_kv = shape.layers * 2 * shape.heads * (context - 1) * B * (3 * (record_bytes(4, 32, D) - 2 + record_bytes(2, 32, D))
+                                                                        + record_bytes(4, 32, D) - 2)
+    figures = {
+        "model": "random-init Ouro-1.4B shape: 24 layers x 4 loops, hidden 2048, 16 heads x 128, SwiGLU 5632, vocab 49152, bf16",
+        "batch": B, "context": context, "note": f"decode at the mean context of {generated} generated tokens after a {prompt}-token "
+                                                "prompt; cuBLAS projections and torch elementwise kernels in both arms, rotary embedding omitted",
+        "packed_kv": {"ms_per_token": packed_ms, "tokens_per_s": B * 1000.0 / packed_ms, "kv_bytes_read_per_step": packed_kv},
+        "bf16_kv": {"ms_per_token": bf16_ms, "tokens_per_s": B * 1000.0 / bf16_ms,
+                    "kv_bytes_read_per_step": int(kv.numel() * 2), "attention": "torch scaled_dot_product_attention, contiguous KV"},
+        "speedup": bf16_ms / packed_ms,
+        "weight_bytes_per_step": model.weight_bytes_per_step(),
+    }
+    del kv, stack, model
+    torch.cuda.empty_cache()
+    return figures
+
+
 def run_gpu(args, shape):
     import torch
     import torch.distributed as dist
@@ -897,6 +1016,7 @@ def run_gpu(args, shape):
         extras["other_shapes"] = other
         # the one-GPU point of the head-sharded strong-scaling curve (same step, every head on this GPU)
         extras["head_sharded"] = head_sharded_figures(timer, torch, dist, device, rank, world, args.steps, args.warmup)
+        extras["config2_model_decode"] = model_decode_figures(timer, torch, device)
 
     if rank != 0:
         if world > 1:

@@ -189,7 +189,7 @@ struct Anchor2224 {
 
 // Row stride (floats) of a tile of rotated rows in shared memory: conflict-free for the MMA fragment loads.
 template <int D>
-constexpr int kTileStride = D + 4;
+constexpr int kTileStride = D + 8;
 
 // Everything that happens to the rows of one (token, head, plane): the anchor record, then the residual records.
 // Eight lanes own the row (lane j: channels 16j .. 16j+15); `token` is the lane group's token.  SHARED_ROWS: the rows
@@ -454,12 +454,17 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// The staged matrix is stored in the order the MMA's B fragments are consumed, so that a lane fetches the fragments of
+// two adjacent 8-column tiles with one 16-byte load: float4 index ((k / 8) * (D / 16) + n / 2) * 32 + lane holds
+// {R[k0][8n+g], R[k0+1][8n+g], R[k0][8(n+1)+g], R[k0+1][8(n+1)+g]} with k0 = k - k % 8 + 2 * (lane % 4), g = lane / 4.
+// (Rows k0, k0 + 1 are the k-indices "t" and "t + 4" of the MMA: the product does not care which physical row carries
+// which index as long as the A fragment uses the same assignment.)
 template <int D>
-constexpr int kMatrixStride = D + 8;  // floats per row of the staged matrix: conflict-free B-fragment loads
+constexpr int kMatrixFloats = D * D;
 
 template <int D>
 size_t dense_shared_bytes(int num_records) {
-    return (static_cast<size_t>(D) * kMatrixStride<D> + static_cast<size_t>(num_records) * 16 * kTileStride<D>) * sizeof(float);
+    return (static_cast<size_t>(kMatrixFloats<D>) + static_cast<size_t>(num_records) * 16 * kTileStride<D>) * sizeof(float);
 }
 
 template <int D, class S>
@@ -467,8 +472,8 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(16) float dense_shared[];
-    float* matrix = dense_shared;                      // [D][kMatrixStride]
-    float* tile = dense_shared + D * kMatrixStride<D>;  // [records * 16][kTileStride]
+    float* matrix = dense_shared;                     // fragment order, see kMatrixFloats
+    float* tile = dense_shared + kMatrixFloats<D>;    // [records * 16][kTileStride]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head = blockIdx.y, plane = p.plane_first + blockIdx.z;
     const int num_records = [&] { if constexpr (S::kFixed) return S::kRecords; else return p.num_records; }();
@@ -484,14 +489,16 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
     const uint4* r = reinterpret_cast<const uint4*>(p.dense_matrix[plane] + static_cast<int64_t>(head) * D * D);
     for (int i = tid; i < D * D / 8; i += 128) {
         const uint4 packed = __ldg(r + i);
-        const int k = (8 * i) / D, n = (8 * i) % D;
+        const int k = (8 * i) / D, c0 = (8 * i) % D;   // eight consecutive columns of row k: one 8-column tile
         const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
-        float* dst = matrix + k * kMatrixStride<D> + n;
+        const int tile_n = c0 >> 3, kk = k & 7;
+        // row k is k-index (kk / 2) [+ 4 when kk is odd] of its k-step: slot kk & 1 of lanes with t = kk / 2
+        float* dst = matrix + (((k >> 3) * (D / 16) + (tile_n >> 1)) * 32 + (kk >> 1)) * 4 + 2 * (tile_n & 1) + (kk & 1);
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
-            dst[2 * w] = pair.x;
-            dst[2 * w + 1] = pair.y;
+            dst[(2 * w) * 16] = pair.x;          // column g = 2w     -> lane 4g + t: 16 floats further per g
+            dst[(2 * w + 1) * 16] = pair.y;      // column g = 2w + 1
         }
     }
     const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
@@ -536,19 +543,21 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
             for (int n = 0; n < D / 8; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+            const float4* fragments = reinterpret_cast<const float4*>(matrix) + lane;
 #pragma unroll 2
             for (int k = 0; k < D; k += 8) {
-                uint32_t a[4];
-                a[0] = __float_as_uint(rows[g * kTileStride<D> + k + t]);
-                a[1] = __float_as_uint(rows[(g + 8) * kTileStride<D> + k + t]);
-                a[2] = __float_as_uint(rows[g * kTileStride<D> + k + t + 4]);
-                a[3] = __float_as_uint(rows[(g + 8) * kTileStride<D> + k + t + 4]);
+                // physical columns k + 2t, k + 2t + 1 of the rows play the k-indices t, t + 4
+                const float2 upper = *reinterpret_cast<const float2*>(rows + g * kTileStride<D> + k + 2 * t);
+                const float2 lower = *reinterpret_cast<const float2*>(rows + (g + 8) * kTileStride<D> + k + 2 * t);
+                const uint32_t a[4] = {__float_as_uint(upper.x), __float_as_uint(lower.x), __float_as_uint(upper.y),
+                                       __float_as_uint(lower.y)};
 #pragma unroll
-                for (int n = 0; n < D / 8; ++n) {
-                    uint32_t b[2];
-                    b[0] = __float_as_uint(matrix[(k + t) * kMatrixStride<D> + 8 * n + g]);
-                    b[1] = __float_as_uint(matrix[(k + t + 4) * kMatrixStride<D> + 8 * n + g]);
-                    mma_tf32(acc[n], a, b);
+                for (int n = 0; n < D / 8; n += 2) {
+                    const float4 f = fragments[((k >> 3) * (D / 16) + (n >> 1)) * 32];
+                    const uint32_t b0[2] = {__float_as_uint(f.x), __float_as_uint(f.y)};
+                    const uint32_t b1[2] = {__float_as_uint(f.z), __float_as_uint(f.w)};
+                    mma_tf32(acc[n], a, b0);
+                    mma_tf32(acc[n + 1], a, b1);
                 }
             }
             __syncwarp();  // every lane has read the rows it needs before they are overwritten
