@@ -26,29 +26,102 @@ __constant__ uint32_t kPaleyRow[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0
 __constant__ uint32_t kPaleyCol[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc,
                                        0x5b8, 0xb70, 0x6e2, 0xdc4, 0, 0, 0, 0};
 
+// ---- packed binary32 pairs ------------------------------------------------------------------------------------------
+// sm_100 issues add / mul / fma on PAIRS of binary32 values (add.f32x2, mul.f32x2, fma.f32x2): two IEEE operations with
+// round-to-nearest-even each -- the same results as two scalar instructions -- in one issue slot.  A lane's 16 channels
+// are paired as (channel i, channel i + 8), i = 0..7; every helper below keeps that pairing so that values stay in
+// the same register pairs from one operation to the next.
+__device__ __forceinline__ float2 pair_of(const float (&values)[16], int i) { return make_float2(values[i], values[i + 8]); }
+__device__ __forceinline__ void unpair(float (&values)[16], int i, float2 pair) {
+    values[i] = pair.x;
+    values[i + 8] = pair.y;
+}
+#define RQ_PAIR(array, index) pair_of(array, index)
+#define RQ_UNPAIR(array, index, pair) unpair(array, index, pair)
+// Written as PTX with an explicit rounding mode on every instruction: an instruction that names its rounding is never
+// merged with a neighbour into a fused multiply-add, which is what keeps the packed bytes reproducible.
+__device__ __forceinline__ unsigned long long pack2(float2 v) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(v.x), "f"(v.y));
+    return r;
+}
+__device__ __forceinline__ float2 unpack2(unsigned long long r) {
+    float2 v;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(v.x), "=f"(v.y) : "l"(r));
+    return v;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long c;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(c) : "l"(pack2(a)), "l"(pack2(b)));
+    return unpack2(c);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long c;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(c) : "l"(pack2(a)), "l"(pack2(b)));
+    return unpack2(c);
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)), "l"(pack2(c)));
+    return unpack2(d);
+}
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return fma2(b, make_float2(-1.f, -1.f), a); }  // RN(a - b)
+__device__ __forceinline__ float2 add2_round_up(float2 a, float2 b) {
+    unsigned long long c;
+    asm("add.rp.f32x2 %0, %1, %2;" : "=l"(c) : "l"(pack2(a)), "l"(pack2(b)));
+    return unpack2(c);
+}
+
+// Butterflies with strides 1, 2, 4, 8 over the lane's 16 values, in that order, (a, b) -> (a + b, a - b): the first three
+// stages act on both halves alike (packed), the last one crosses the halves.
+__device__ __forceinline__ void butterflies_16(float (&x)[16], bool with_stride_8) {
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if ((i & h) == 0) {
+                const float2 a = RQ_PAIR(x, i), b = RQ_PAIR(x, i + h);
+                const float2 sum = add2(a, b), difference = sub2(a, b);
+                RQ_UNPAIR(x, i, sum);
+                RQ_UNPAIR(x, i + h, difference);
+            }
+        }
+    }
+    if (with_stride_8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a = x[i], b = x[i + 8];
+            x[i] = __fadd_rn(a, b);
+            x[i + 8] = __fsub_rn(a, b);
+        }
+    }
+}
+
+// One butterfly stage between lanes `lane` and `lane ^ mask`: x <- other + x, or other - x in the lane that holds b.
+__device__ __forceinline__ void butterfly_across_lanes_16(float (&x)[16], int mask, bool upper) {
+    const float sign = upper ? -1.f : 1.f;
+    const float2 signs = make_float2(sign, sign);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 other = make_float2(__shfl_xor_sync(kFullMask, x[i], mask), __shfl_xor_sync(kFullMask, x[i + 8], mask));
+        const float2 v = fma2(signs, RQ_PAIR(x, i), other);  // one rounding either way
+        RQ_UNPAIR(x, i, v);
+    }
+}
+
 // Forward: y = ((sign * x) H) * rscale.  Inverse: x = ((y H^T) * rscale) * sign.
 // `j` is the lane's slice (channels 16j .. 16j+15) inside its 8-lane row group.
 template <int D, bool INVERSE>
 __device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign16, float rscale) {
     // forward: the sign diagonal has already been applied when the row was loaded
     if (D == 128) {
-        butterflies_in_lane<16>(x);
-        butterfly_across_lanes<16>(x, 1, (j & 1) != 0);
-        butterfly_across_lanes<16>(x, 2, (j & 2) != 0);
-        butterfly_across_lanes<16>(x, 4, (j & 4) != 0);
+        butterflies_16(x, true);
+        butterfly_across_lanes_16(x, 1, (j & 1) != 0);
+        butterfly_across_lanes_16(x, 2, (j & 2) != 0);
+        butterfly_across_lanes_16(x, 4, (j & 4) != 0);
     } else {
         // Sylvester-8 inside each block of 8 channels (two blocks per lane) ...
-#pragma unroll
-        for (int h = 1; h < 8; h <<= 1) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                if ((i & h) == 0) {
-                    const float a = x[i], b = x[i + h];
-                    x[i] = __fadd_rn(a, b);
-                    x[i + h] = __fsub_rn(a, b);
-                }
-            }
-        }
+        butterflies_16(x, false);
         // ... then the 12-point Paley transform across blocks: out[a'] = sum_a s(a, a') t[a], a = 0..11.
         const int lane = threadIdx.x & 31;
         const int group_base = lane & 24;
@@ -75,8 +148,12 @@ __device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign1
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = j < 6 ? out[i] : 0.f;
     }
+    const float2 rscale2 = make_float2(rscale, rscale);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) x[i] = __fmul_rn(x[i], rscale);
+    for (int i = 0; i < 8; ++i) {
+        const float2 v = mul2(RQ_PAIR(x, i), rscale2);
+        RQ_UNPAIR(x, i, v);
+    }
     if (INVERSE) {
 #pragma unroll
         for (int i = 0; i < 16; ++i)
@@ -85,7 +162,8 @@ __device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign1
 }
 
 // sum over the row of a[c]*b[c]: 16 sequential (product rounded, then added) terms per lane, then the
-// lanes combine as ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)).
+// lanes combine as ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)).  Scalar on purpose: a packed multiply feeding a packed add
+// was observed to come out as one fused multiply-add (a single rounding), which no longer is the stated arithmetic.
 __device__ __forceinline__ float row_dot(const float (&a)[16], const float (&b)[16]) {
     float acc = 0.f;
 #pragma unroll
@@ -152,14 +230,22 @@ __device__ __forceinline__ GroupCode group_quantize(const float (&z)[16], int gr
     // adding 2^23 rounding upwards then leaves ceil(t) in the low significand bits.  A zero scale gives r = 0,
     // n = 0 and code 0, as the reference stores; a NaN loses the first max() and also becomes code 0.
     const float r = scale > 0.f ? __frcp_rn(scale) : 0.f;
+    const float2 offset2 = make_float2(offset, offset), minus_scale = make_float2(-scale, -scale);
+    const float2 r2 = make_float2(r, r), minus_half = make_float2(-0.5f, -0.5f), magic = make_float2(8388608.f, 8388608.f);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float d = __fsub_rn(z[i], offset);
-        const float q0 = __fmul_rn(d, r);
-        const float e = __fmaf_rn(-q0, scale, d);
-        const float n = __fmaf_rn(e, r, q0);
-        const float t = fminf(fmaxf(__fsub_rn(n, 0.5f), 0.f), kLevels);
-        out.magic[i] = __float_as_uint(__fadd_ru(t, 8388608.f));
+    for (int i = 0; i < 8; ++i) {
+        // z - offset as a fused multiply-add with multiplier -1: z may itself be the product that ended a rotation, and a
+        // plain packed add behind a packed multiply is liable to be merged with it into one rounding
+        const float2 d = sub2(RQ_PAIR(z, i), offset2);
+        const float2 q0 = mul2(d, r2);
+        const float2 e = fma2(q0, minus_scale, d);            // d - q0 * scale, exact
+        const float2 n = fma2(e, r2, q0);
+        float2 t = add2(n, minus_half);
+        t.x = fminf(fmaxf(t.x, 0.f), kLevels);
+        t.y = fminf(fmaxf(t.y, 0.f), kLevels);
+        const float2 rounded = add2_round_up(t, magic);
+        out.magic[i] = __float_as_uint(rounded.x);
+        out.magic[i + 8] = __float_as_uint(rounded.y);
     }
     return out;
 }
@@ -393,8 +479,12 @@ __device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token
             const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref, den));
             alpha_bits = __bfloat16_as_ushort(stored);
             const float alpha = __bfloat162float(stored);
+            const float2 minus_alpha = make_float2(-alpha, -alpha);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = __fmaf_rn(-ref[i], alpha, y[i]);
+            for (int i = 0; i < 8; ++i) {
+                const float2 v = fma2(RQ_PAIR(ref, i), minus_alpha, RQ_PAIR(y, i));  // y - ref * alpha, one rounding
+                RQ_UNPAIR(y, i, v);
+            }
         } else {
             const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref, den));
             alpha_bits = __bfloat16_as_ushort(stored);
@@ -410,7 +500,10 @@ __device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token
         if (centered) {
             load_mean(r, mean);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = __fsub_rn(y[i], mean[i]);
+            for (int i = 0; i < 8; ++i) {
+                const float2 v = sub2(RQ_PAIR(y, i), RQ_PAIR(mean, i));
+                RQ_UNPAIR(y, i, v);
+            }
         }
         const GroupCode q = commit(r, y, alpha_bits);
         if (mode == RQ_REFERENCE_ADJACENT) {
@@ -667,10 +760,12 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
     const float den = row_dot(ref, ref);
     const __nv_bfloat16 stored = __float2bfloat16_rn(__fdiv_rn(row_dot(y, ref), fmaxf(den, 1e-12f)));
     const float alpha = __bfloat162float(stored);
+    const float2 minus_alpha = make_float2(-alpha, -alpha);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        y[i] = __fmaf_rn(-ref[i], alpha, y[i]);
-        if (centered) y[i] = __fsub_rn(y[i], mean[i]);
+    for (int i = 0; i < 8; ++i) {
+        float2 v = fma2(RQ_PAIR(ref, i), minus_alpha, RQ_PAIR(y, i));
+        if (centered) v = sub2(v, RQ_PAIR(mean, i));
+        RQ_UNPAIR(y, i, v);
     }
     const GroupCode q = group_quantize<2>(y, RESIDUAL_GROUP);
     if (record != kAnchor && owner) {
