@@ -94,7 +94,8 @@ struct Config {
     static constexpr int kOffWarpAcc = kOffQuery + D * 4;                  // float[kWarps][D]
     static constexpr int kOffWarpStat = kOffWarpAcc + kWarps * D * 4;      // float[kWarps][2] + float misc[8]
     static constexpr int kOffBarriers = kOffWarpStat + 64;                 // uint64[kWarps][kStages]
-    static constexpr int kSmemBytes = kOffBarriers + kWarps * kStages * 8;
+    static constexpr int kOffWork = kOffBarriers + kWarps * kStages * 8;   // the CTA's WorkItem (6 ints)
+    static constexpr int kSmemBytes = kOffWork + 32;
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -549,7 +550,6 @@ struct WorkItem {
     int row, request, seq_len;
     int part, parts;  // this CTA's partition of the row and how many the row has
     int first;        // index of the row's first work item: partial results of the row sit at items first .. first+parts-1
-    int total_rows;   // query rows of the call that are not graph padding
 };
 
 // Cost of running `items` equally sized CTAs per head, in units of (pages one CTA consumes while four share an SM):
@@ -597,7 +597,6 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
             seq_len = __ldcg(p.seq_lens + request);
         }
         out.row = row;
-        out.total_rows = total_rows;
         out.request = request;
         out.seq_len = seq_len;
         out.parts = p.splits;
@@ -609,29 +608,49 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
 
     constexpr int kCandidates = 9;          // chunk sizes 4 << k pages, k = 0..8; candidate 9 = one partition per row
     constexpr float kOverhead = 256.f / P;  // fixed cost of a CTA (prologue, first fetch, fold), in pages
-    auto load_request = [&](int r, int& begin, int& rows, int& pages, int& len) {
-        begin = rows = pages = len = 0;
-        if (r < num_requests) {
-            len = __ldcg(p.seq_lens + r);
-            begin = __ldcg(p.query_start_loc + r);
-            rows = max(0, min(__ldcg(p.query_start_loc + r + 1), total_rows) - begin);
-            pages = rows > 0 ? (max(len - 1, 0) + P - 1) / P : 0;
+    // A sweep covers 64 requests: lane L holds request base + L and request base + 32 + L.  All six loads of a sweep
+    // are independent, so a batch of up to 64 requests costs one round trip to L2, and its values stay in registers
+    // for the second pass.
+    struct Request { int begin, rows, pages, len; };
+    auto load_sweep = [&](int base, Request (&q)[2]) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int r = base + 32 * u + lane;
+            q[u].begin = q[u].rows = q[u].pages = q[u].len = 0;
+            if (r < num_requests) {
+                q[u].len = __ldcg(p.seq_lens + r);
+                q[u].begin = __ldcg(p.query_start_loc + r);
+                q[u].rows = max(0, min(__ldcg(p.query_start_loc + r + 1), total_rows) - q[u].begin);
+                q[u].pages = q[u].rows > 0 ? (max(q[u].len - 1, 0) + P - 1) / P : 0;
+            }
         }
     };
     // pass 1: pages of the whole batch, and how many items each candidate chunk size would make
+    Request first[2];
+    load_sweep(0, first);
     int total_pages = 0, longest = 0;
     int counts[kCandidates];
 #pragma unroll
     for (int k = 0; k < kCandidates; ++k) counts[k] = 0;
-    for (int base = 0; base < num_requests; base += 32) {
-        int begin, rows, pages, len;
-        load_request(base + lane, begin, rows, pages, len);
-        total_pages += rows * pages;
-        longest = max(longest, pages);
+    auto tally = [&](const Request (&q)[2]) {
 #pragma unroll
-        for (int k = 0; k < kCandidates; ++k) counts[k] += rows * max(1, (pages + (4 << k) - 1) >> (k + 2));
+        for (int u = 0; u < 2; ++u) {
+            total_pages += q[u].rows * q[u].pages;
+            longest = max(longest, q[u].pages);
+#pragma unroll
+            for (int k = 0; k < kCandidates; ++k) counts[k] += q[u].rows * max(1, (q[u].pages + (4 << k) - 1) >> (k + 2));
+        }
+    };
+    tally(first);
+    for (int base = 64; base < num_requests; base += 64) {
+        Request more[2];
+        load_sweep(base, more);
+        tally(more);
     }
     total_pages = __reduce_add_sync(kFullMask, total_pages);
+    // No chunk is smaller than four pages, so the call never has more than rows + pages / 4 items: the spare CTAs
+    // beyond that leave here, before the partition choice.
+    if (item >= total_rows + (total_pages >> 2) && p.splits == 0) return false;
     longest = __reduce_max_sync(kFullMask, longest);
     int my_items = total_rows;  // lanes >= kCandidates stand for "never split"
 #pragma unroll
@@ -658,35 +677,37 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     }
     auto parts_of = [&](int pages) { return max(1, (pages + chunk - 1) / chunk); };
 
-    // pass 2: which request owns this item
+    // pass 2: which request owns this item.  Requests are numbered sweep by sweep, first half (lanes 0..31) then second.
     int before = 0;
-    for (int base = 0; base < num_requests; base += 32) {
-        int begin, rows, pages, len;
-        load_request(base + lane, begin, rows, pages, len);
-        const int parts = parts_of(pages);
-        const int mine = rows * parts;
-        int upto = mine;  // inclusive prefix sum over the lanes
+    for (int base = 0; base < num_requests; base += 64) {
+        Request q[2];
+        if (base == 0) { q[0] = first[0]; q[1] = first[1]; } else load_sweep(base, q);
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int v = __shfl_up_sync(kFullMask, upto, d);
-            if (lane >= d) upto += v;
+        for (int u = 0; u < 2; ++u) {
+            const int parts = parts_of(q[u].pages);
+            const int mine = q[u].rows * parts;
+            int upto = mine;  // inclusive prefix sum over the lanes
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int v = __shfl_up_sync(kFullMask, upto, d);
+                if (lane >= d) upto += v;
+            }
+            const uint32_t owners = __ballot_sync(kFullMask, item < before + upto);
+            if (owners != 0u) {
+                const int src = __ffs(owners) - 1;
+                const int local = item - before - (__shfl_sync(kFullMask, upto, src) - __shfl_sync(kFullMask, mine, src));
+                const int owner_parts = __shfl_sync(kFullMask, parts, src);
+                const int row_in_request = owner_parts == 1 ? local : local / owner_parts;
+                out.request = base + 32 * u + src;
+                out.seq_len = __shfl_sync(kFullMask, q[u].len, src);
+                out.row = __shfl_sync(kFullMask, q[u].begin, src) + row_in_request;
+                out.parts = owner_parts;
+                out.part = local - row_in_request * owner_parts;
+                out.first = item - out.part;
+                return true;
+            }
+            before += __shfl_sync(kFullMask, upto, 31);
         }
-        const uint32_t owners = __ballot_sync(kFullMask, item < before + upto);
-        if (owners != 0u) {
-            const int src = __ffs(owners) - 1;
-            const int local = item - before - (__shfl_sync(kFullMask, upto, src) - __shfl_sync(kFullMask, mine, src));
-            const int owner_parts = __shfl_sync(kFullMask, parts, src);
-            const int row_in_request = owner_parts == 1 ? local : local / owner_parts;
-            out.request = base + src;
-            out.total_rows = total_rows;
-            out.seq_len = __shfl_sync(kFullMask, len, src);
-            out.row = __shfl_sync(kFullMask, begin, src) + row_in_request;
-            out.parts = owner_parts;
-            out.part = local - row_in_request * owner_parts;
-            out.first = item - out.part;
-            return true;
-        }
-        before += __shfl_sync(kFullMask, upto, 31);
     }
     return false;
 }
@@ -738,8 +759,16 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
 
     // ---- which work item: (row, partition) and the row's request ---------------------------------------
-    WorkItem work;
-    if (!find_work<P>(p, blockIdx.x / heads, lane, work)) return;  // graph padding or spare capacity: nothing to do
+    // Warp 0 looks it up (the lookup is warp-wide work that every warp would repeat) and shares the answer.
+    WorkItem* shared_work = reinterpret_cast<WorkItem*>(smem + C::kOffWork);
+    if (warp == 0) {
+        WorkItem mine;
+        if (!find_work<P>(p, blockIdx.x / heads, lane, mine)) mine.row = -1;  // graph padding or spare capacity
+        if (lane == 0) *shared_work = mine;
+    }
+    __syncthreads();
+    const WorkItem work = *shared_work;
+    if (work.row < 0) return;  // nothing to do
     const int row = work.row, request = work.request, split = work.part, splits = work.parts;
     const int history = max(0, work.seq_len - 1);
     const int pages = (history + P - 1) / P;
@@ -891,8 +920,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     const int slot = lane >> 2;          // token slot 0..7 inside a warp step
     float carry = 1.f;                   // factor the fp32 sums still have to be multiplied by (deferred rescale)
 
-    bool heavy = false;  // the page held a token with more than half of its stream's mass so far
-    int pages_since_flush = 0;
+    int pages_to_flush = kFlushPages;  // counts down; a token with more than half of its stream's mass so far zeroes it
     // half2 partial sums -> fp32 sums, every 8 tokens of a lane
     auto flush = [&]() {
         if (__any_sync(kFullMask, carry != 1.f)) {
@@ -1000,8 +1028,9 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             }
             // A token that holds a large share of its stream's softmax mass leaves half-precision sums of the size of
             // its own value row behind; every later add would be rounded at THAT magnitude (an 11-bit significand: a
-            // value of 30 costs 0.007 per add).  Such tokens are rare; the page loop moves the sums to fp32 after one.
-            heavy = heavy || prob > 0.5f * l;
+            // value of 30 costs 0.007 per add).  Such tokens are rare; the page loop moves the sums to fp32 right after
+            // the page of one.
+            if (prob > 0.5f * l) pages_to_flush = 0;
         }
     };
 
@@ -1034,10 +1063,9 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                 absorb_token(std::true_type{}, k_anchor, sub * 8 + slot, sub * 8 + slot < valid, scores[sub]);
         }
 
-        if (__any_sync(kFullMask, heavy) || ++pages_since_flush == kFlushPages) {
+        if (__any_sync(kFullMask, --pages_to_flush <= 0)) {
             flush();
-            heavy = false;
-            pages_since_flush = 0;
+            pages_to_flush = kFlushPages;
         }
         __syncwarp();  // every lane has finished reading this stage
         if (issued < warp_pages) {
@@ -1204,7 +1232,8 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         if (tid == 0) {
             __threadfence_system();
             const uint32_t ticket = atomicAdd(p.gather_state + 2, 1u);
-            if (ticket + 1u == static_cast<uint32_t>(work.total_rows) * static_cast<uint32_t>(heads)) {
+            const uint32_t total_rows = static_cast<uint32_t>(min(__ldcg(p.query_start_loc + p.num_requests), p.num_rows));
+            if (ticket + 1u == total_rows * static_cast<uint32_t>(heads)) {
                 p.gather_state[2] = 0u;  // ready for the next call
                 __threadfence_system();  // every other CTA's stores (ordered before its ticket) before the flag
                 const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.gather_state) + 1u;

@@ -289,12 +289,13 @@ int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32
 
 int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads) {
     if (num_query_rows < 1 || heads < 1) return 0;
-    // Every row is one work item; the spare items are what long rows can be cut into.  Two waves of resident CTAs
-    // (four per multiprocessor) is as many as the partition choice on the device ever asks for, fifteen spare items per
-    // row is the reference's ceiling (attention/launch.cuh:70-80: sixteen partitions per request), and a single long
-    // row among short ones can always have its sixteen.
+    // Every row is one work item; the spare items are what long rows can be cut into.  One wave of resident CTAs
+    // (four per multiprocessor) on top of the rows is as many as the partition choice on the device asks for (CTAs
+    // without work still cost a launch slot and a schedule lookup each), fifteen spare items per row is the
+    // reference's ceiling (attention/launch.cuh:70-80: sixteen partitions per request), and a single long row among
+    // short ones can always have its sixteen.
     const int64_t slots = 4LL * current_sm_count();
-    int64_t spare = (2 * slots + heads - 1) / heads;
+    int64_t spare = (slots + heads - 1) / heads;
     if (spare > 15LL * num_query_rows) spare = 15LL * num_query_rows;
     if (spare < 15) spare = 15;
     const int64_t capacity = num_query_rows + spare;
