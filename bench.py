@@ -574,11 +574,25 @@ def ragged_figures(timer, stack, peak, reps, uniform_us):
     starts = torch.arange(65, dtype=torch.int32, device=stack.device)
     history = int((lengths - 1).sum())
     out = {"rows": 64, "lengths": f"{shape.context} + 63 rows of 17..600 (seed 7), {history} cached tokens in all"}
+    from residualquant_b200 import _cuda, _lib
+
+    uniform = _lib.load().rq_attention_default_splits(64, shape.heads, stack.block_table.shape[1], shape.page)
+    out["uniform_rule_partitions"] = int(uniform)
     for name, loop in (("residual_loop", 0), ("anchor_loop", 3)):
-        ms = timer.graph_ms(lambda: [stack.attention(layer, loop, 64, lens, starts) for layer in range(shape.layers)],
-                            reps) / shape.layers
+        def layers():
+            for layer in range(shape.layers):
+                stack.attention(layer, loop, 64, lens, starts)
+        ms = timer.graph_ms(layers, reps) / shape.layers
+        # the same call with one partition count for every row, chosen from the widest row (the rule a host-side schedule
+        # has to use when the grid must not depend on the lengths)
+        _cuda.set_attention_splits(uniform)
+        try:
+            uniform_ms = timer.graph_ms(layers, reps) / shape.layers
+        finally:
+            _cuda.set_attention_splits(0)
         implied = uniform_us[name] * history / (64 * (shape.context - 1))
-        out[name] = {"us": round(1000 * ms, 2), "implied_us": round(implied, 2), "ratio": round(1000 * ms / implied, 3),
+        out[name] = {"us": round(1000 * ms, 2), "uniform_rule_us": round(1000 * uniform_ms, 2),
+                     "implied_us": round(implied, 2), "ratio": round(1000 * ms / implied, 3),
                      "frac": round(attention_bytes(history, 64, shape, loop == 3) / (ms * 1e-3) / 1e9 / peak, 4)}
     return out
 
@@ -642,21 +656,33 @@ def reference_cuda_figures(timer, stack):
                "note": "us per call under CUDA-graph replay; the caches of consecutive replays are the same, larger than L2 "
                        "for batch >= 8"}
 
-    def attention_of(module, rotation, out, loop):
-        return lambda: module.attention(q, k, v, cache, out, stack.qsl, stack.seq_lens, stack.block_table, rotation, None,
-                                        None, stack.records, "anchor", 3, loop)
+    def attention_of(module, rotation, out, loop, rows=B, lens=None):
+        lens = stack.seq_lens[:rows] if lens is None else lens
+        return lambda: module.attention(q[:rows], k[:rows], v[:rows], cache, out[:rows], stack.qsl[:rows + 1], lens,
+                                        stack.block_table[:rows], rotation, None, None, stack.records, "anchor", 3, loop)
+
+    def three_ways(loop, rows=B, lens=None, reps=5):
+        return {"reference": round(1000 * timer.graph_ms(attention_of(reference, dense, out_ref, loop, rows, lens), reps), 2),
+                "this_dense": round(1000 * timer.graph_ms(attention_of(_cuda, dense, out_ours, loop, rows, lens), reps), 2),
+                "this_fwht": round(1000 * timer.graph_ms(attention_of(_cuda, stack.key_rot, out_ours, loop, rows, lens), reps), 2)}
 
     def quantize_of(module, rotation, pairs, slots):
         return lambda: module.quantize(pairs, scratch, slots, rotation, None, None, stack.records, "anchor", 3, "ls")
 
     try:
         for name, loop in (("attention_residual_us", 0), ("attention_anchor_us", 3)):
-            figures[name] = {
-                "reference": round(1000 * timer.graph_ms(attention_of(reference, dense, out_ref, loop), 5), 2),
-                "this_dense": round(1000 * timer.graph_ms(attention_of(_cuda, dense, out_ours, loop), 5), 2),
-                "this_fwht": round(1000 * timer.graph_ms(attention_of(_cuda, stack.key_rot, out_ours, loop), 5), 2),
-            }
+            figures[name] = three_ways(loop)
             figures[name]["outputs_rms_difference"] = float((out_ref.float() - out_ours.float()).pow(2).mean().sqrt())
+        # small batches (latency regime) and a ragged batch (one full-context row among short ones), residual loop
+        for rows in (1, 8):
+            if rows < B:
+                figures[f"attention_residual_batch{rows}_us"] = three_ways(0, rows, reps=20)
+        if B >= 64:
+            rng = np.random.default_rng(7)
+            lengths = np.concatenate([[shape.context], rng.integers(17, 601, size=63)]).astype(np.int32)
+            ragged = torch.from_numpy(lengths).to(stack.device)
+            figures["attention_residual_ragged_us"] = three_ways(0, 64, ragged, reps=20)
+            figures["attention_residual_ragged_us"]["lengths"] = f"{shape.context} + 63 rows of 17..600 (seed 7)"
         for name, pairs, slots in (("quantize_decode_us", live_pairs, stack.slot_mapping),
                                    ("quantize_prefill_us", prompt_pairs, prompt_slots)):
             figures[name] = {
