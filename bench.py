@@ -90,9 +90,10 @@ def parse_args():
     p.add_argument("--shard", default="sequences", choices=["sequences", "heads"],
                    help="sequences: every rank owns its own batch (weak scaling, no collective); heads: every rank holds "
                         "all sequences but only its KV heads and all-gathers the attention output (strong scaling)")
-    p.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+    p.add_argument("--gather", default="fused", choices=["fused", "barrier", "nccl"],
                    help="with --shard heads: fused = the attention kernel stores into every GPU's gathered output over "
-                        "NVLink (captured in the graph); nccl = one all-gather per call, eager")
+                        "NVLink and ends only when every rank's rows have arrived (captured in the graph); barrier = the "
+                        "same stores followed by a barrier kernel per call; nccl = one all-gather per call, eager")
     p.add_argument("--splits", type=int, default=0,
                    help="force the number of KV partitions per row (0 = the kernel picks them per row from the lengths)")
     p.add_argument("--quick", action="store_true",
@@ -280,7 +281,7 @@ def workload_config(args, shape):
                     f"block {shape.page}, CUDA-graph decode step (4 attention + 1 quantize launch per layer)"
                     + ("" if args.shard != "heads" else
                        "; KV heads sharded over the ranks, output rows stored into every GPU's gathered buffer by the attention "
-                       "kernel, captured in the graph" if args.gather == "fused" else
+                       "kernel, captured in the graph" if args.gather != "nccl" else
                        "; KV heads sharded over the ranks, one NCCL all-gather of the output per attention call, eager step"),
         "batch_per_gpu": shape.batch,
         "sharding": args.shard,
@@ -706,42 +707,51 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
     shape = Shape(batch=16, context=4096, layers=32, heads=55, head_dim=96, page=16, group=32)
     local = sharding.shard_counts(shape.heads, world)[rank]
     stack = Stack(shape, device, torch, heads_here=local, seed_offset=1000 + rank)
-    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
+    def measure(gather):
+        def step():
+            # complete form: every attention call ends only when all ranks' rows of that call are in this GPU's gathered
+            # buffer (its last CTA publishes and waits), so nothing sits between the calls.  barrier form: one barrier
+            # kernel per call, launched as a programmatic dependent.
+            for layer in range(shape.layers):
+                for loop in range(4):
+                    stack.attention(layer, loop, gather=gather, gather_buffer=loop % 2)
+                    gather.barrier()
+                stack.quantize(layer)
+            stack.seq_lens.add_(1)
+            stack.advance()
 
-    def step():
-        # One barrier kernel per call, launched as a programmatic dependent (resident while the attention kernel runs).
-        # The barrier-free form (HeadGather(signalled=True): the kernel's last CTA publishes, the next call waits)
-        # measured slower on two GPUs: one system-scope fence per finishing CTA costs more than the launch it saves.
-        for layer in range(shape.layers):
-            for loop in range(4):
-                stack.attention(layer, loop, gather=gather, gather_buffer=loop % 2)
-                gather.barrier()
-            stack.quantize(layer)
-        stack.seq_lens.add_(1)
+        stack.seq_lens.fill_(shape.context - 1)
         stack.advance()
+        graph = timer.capture(step)    # one eager step, then the capture
+        stack.seq_lens.fill_(shape.context)
+        stack.advance()
+        timer.join_default_stream()
+        with torch.cuda.stream(timer.stream):
+            for _ in range(warmup):
+                graph.replay()
+        ms = timer.timed(graph.replay, steps)
+        gather.check()
+        expected = sharding.gather_heads(stack.out[shape.layers - 1, 3], shape.heads)
+        equal = bool(torch.equal(gather.gathered(3 % 2), expected))
+        flags = torch.tensor([1 if equal else 0], device=device)
+        if world > 1:
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        del graph
+        return ms, bool(flags.item() == 1)
 
-    stack.advance()
-    graph = timer.capture(step)
-    stack.seq_lens.fill_(shape.context)
-    stack.advance()
-    timer.join_default_stream()
-    with torch.cuda.stream(timer.stream):
-        for _ in range(warmup):
-            graph.replay()
-    ms = timer.timed(graph.replay, steps)
-    gather.check()
-    expected = sharding.gather_heads(stack.out[shape.layers - 1, 3], shape.heads)
-    equal = bool(torch.equal(gather.gathered(3 % 2), expected))
-    flags = torch.tensor([1 if equal else 0], device=device)
-    if world > 1:
-        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
-    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 128 barrier + 32 "
+    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device, complete=True)
+    ms, equal = measure(gather)
+    with_barrier = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
+    barrier_ms, barrier_equal = measure(with_barrier)
+    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 32 "
                        "write launches per step, INT2 g32 + INT4 g32; output rows stored into every GPU's gathered buffer by the "
-                       "attention kernel",
+                       "attention kernel, whose last CTA publishes and waits for every rank (no barrier launch)",
               "n": world, "heads_per_rank": sharding.shard_counts(shape.heads, world),
               "tokens_per_s": shape.batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
-              "gathered_equal_nccl": bool(flags.item() == 1), "scaling": "strong"}
-    del stack, gather
+              "gathered_equal_nccl": equal, "scaling": "strong",
+              "barrier_form": {"ms_per_step": barrier_ms / steps, "gathered_equal_nccl": barrier_equal,
+                               "launches": "128 attention + 128 barrier + 32 write"}}
+    del stack, gather, with_barrier
     torch.cuda.empty_cache()
     return result
 
@@ -902,7 +912,8 @@ def run_gpu(args, shape):
     gathered = [None]
     # Head sharding: the output projection needs every head.  "fused": the attention kernel stores its rows into every
     # GPU's gathered buffer over NVLink (graph capturable); "nccl": one all-gather per call.
-    fused_gather = sharding.HeadGather(B, shape.heads, shape.head_dim, device) if shard_heads and args.gather == "fused" else None
+    fused_gather = (sharding.HeadGather(B, shape.heads, shape.head_dim, device, complete=args.gather == "fused")
+                    if shard_heads and args.gather != "nccl" else None)
 
     def hot_path():
         for layer in range(layers):
@@ -947,7 +958,7 @@ def run_gpu(args, shape):
         graph = timer.capture(step_body)
     rewind()
     torch.cuda.synchronize(device)
-    launches_per_step = layers * (9 if fused_gather is not None else 5)
+    launches_per_step = layers * (9 if fused_gather is not None and not fused_gather.complete else 5)
 
     sampler = ClockSampler(local_rank)
     # ---------------- device-resident throughput ----------------

@@ -59,11 +59,17 @@ extern "C" {
  * RQ_FLAG_GATHER_WAIT          rq_attention with num_peers > 0: before a CTA reads q/k/v it waits (bounded by
  *                              gather_timeout_ns) until every peer has published the epoch this rank has reached, i.e.
  *                              until the PREVIOUS call's gathered rows are complete on this GPU -- the point where a
- *                              model's next attention call depends on them through the output projection. */
+ *                              model's next attention call depends on them through the output projection.
+ * RQ_FLAG_GATHER_COMPLETE      rq_attention with num_peers > 0 (implies RQ_FLAG_GATHER_PUBLISH): the CTA that published
+ *                              then waits (bounded by gather_timeout_ns) until every peer's signal of the SAME call has
+ *                              arrived, so the launch does not end before this GPU's gathered buffer holds every
+ *                              rank's rows: whatever follows on the stream -- a library GEMM included -- may read them,
+ *                              and no barrier kernel is needed.  Every rank must issue the same sequence of calls. */
 #define RQ_FLAG_SERIAL_LAUNCH 1
 #define RQ_FLAG_STABLE_METADATA 2
 #define RQ_FLAG_GATHER_PUBLISH 4
 #define RQ_FLAG_GATHER_WAIT 8
+#define RQ_FLAG_GATHER_COMPLETE 16
 
 typedef enum RqStatus {
     RQ_OK = 0,
@@ -197,7 +203,7 @@ typedef struct RqAttentionArgs {
     int64_t gather_stride;           /* ELEMENTS between rows of the gathered buffers (>= total heads * head_dim) */
     void* peer_output[RQ_MAX_PEERS];
     int32_t flags;                   /* RQ_FLAG_* */
-    /* Completion signal of the fused gather (RQ_FLAG_GATHER_PUBLISH / RQ_FLAG_GATHER_WAIT): the same flag arrays and
+    /* Completion signal of the fused gather (RQ_FLAG_GATHER_PUBLISH / _WAIT / _COMPLETE): the same flag arrays and
      * state block rq_peer_barrier uses, so that no barrier kernel is needed between calls.  peer_flags[i] is GPU i's
      * flag array uint32 [RQ_MAX_PEERS] as mapped into this process; gather_state is this rank's own 256 bytes
      * ([0] epoch, [1] status, [2] arrival counter), zeroed once. */

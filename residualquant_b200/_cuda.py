@@ -222,7 +222,8 @@ def attention(
 
     `gather` (not part of the reference signature) is a `sharding.HeadGather`: when the KV heads are sharded over the
     GPUs of a node, the kernel also stores every finished row into buffer `gather_buffer` of every GPU's gathered
-    output; call `gather.barrier()` afterwards, before anything reads the gathered rows."""
+    output; call `gather.barrier()` afterwards, before anything reads the gathered rows (a no-op for
+    `HeadGather(complete=True)`, where the call itself ends only when every rank's rows have arrived)."""
     lib = _lib.load()
     records = [list(r) for r in records]
     _validate_bf16_token_tensor(query)
@@ -295,14 +296,20 @@ def attention(
             args.peer_output[i] = pointer
         args.gather_head_offset = gather.head_offset
         args.gather_stride = gather.heads * head_dim
-        if getattr(gather, "signalled", False):
-            # no barrier kernel between calls: this call publishes its completion and first waits for the previous one's
+        complete, signalled = getattr(gather, "complete", False), getattr(gather, "signalled", False)
+        if complete or signalled:
+            # no barrier kernel between calls.  complete: the call itself ends only when every rank's rows have arrived.
+            # signalled: this call publishes its completion and first waits for the previous one's
             for i, pointer in enumerate(gather.flag_pointers()):
                 args.peer_flags[i] = pointer
             args.gather_state = gather.state.data_ptr()
             args.gather_rank = gather.rank
-            gather_flags = ((_lib.FLAG_GATHER_PUBLISH if getattr(gather, "publish", True) else 0)
-                            | (_lib.FLAG_GATHER_WAIT if getattr(gather, "wait", True) else 0))
+            args.gather_timeout_ns = int(getattr(gather, "timeout_ns", 0))   # 0: the library's 2 s
+            if complete:
+                gather_flags = _lib.FLAG_GATHER_COMPLETE
+            else:
+                gather_flags = ((_lib.FLAG_GATHER_PUBLISH if getattr(gather, "publish", True) else 0)
+                                | (_lib.FLAG_GATHER_WAIT if getattr(gather, "wait", True) else 0))
     with torch.cuda.device(query.device):
         # 0: the kernel cuts every row into partitions in proportion to its own length, read on the device
         args.num_splits = _forced_splits

@@ -16,6 +16,7 @@ FLAG_SERIAL_LAUNCH = 1
 FLAG_STABLE_METADATA = 2
 FLAG_GATHER_PUBLISH = 4
 FLAG_GATHER_WAIT = 8
+FLAG_GATHER_COMPLETE = 16
 REFERENCE_MODES = {"anchor": 0, "adjacent": 1}
 COEFFICIENTS = {"unit": 0, "norm": 1, "ls": 2}
 CHAINS = {"kernel": 0, "calibration": 1}

@@ -571,8 +571,9 @@ __device__ __forceinline__ float wave_count(float ctas, float slots, float sms) 
 //   * p.splits < 0: as below with the chunk size fixed by the caller to -p.splits pages (a tuning knob).
 //   * p.splits == 0: one chunk size c (pages) is chosen for the whole call from the TOTAL number of pages of the batch,
 //     row r gets max(1, ceil(pages_r / c)) partitions -- proportional to its length -- and the items are laid out
-//     request by request.  c is the candidate (4, 8, ..., 1024 pages, or "never split") with the lowest modelled time;
-//     a floor on c keeps the number of items within p.capacity, which fixed the grid on the host.
+//     request by request.  c is the candidate (4, 8, ..., 1024 pages, or "never split"; for a batch of equal lengths:
+//     the row cut into 1..32 equal partitions) with the lowest modelled time among those whose item count fits
+//     p.capacity, which fixed the grid on the host.
 // Every lane of the warp calls this with the same arguments and gets the same result.  Metadata is read through L2
 // (ld.global.cg): with early_start this runs while the previous kernel of the stream may still be executing, and an L1
 // line left over from an earlier launch must not be trusted.
@@ -628,7 +629,7 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     // pass 1: pages of the whole batch, and how many items each candidate chunk size would make
     Request first[2];
     load_sweep(0, first);
-    int total_pages = 0, longest = 0;
+    int total_pages = 0, longest = 0, shortest = 0x7fffffff;
     int counts[kCandidates];
 #pragma unroll
     for (int k = 0; k < kCandidates; ++k) counts[k] = 0;
@@ -637,6 +638,7 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
         for (int u = 0; u < 2; ++u) {
             total_pages += q[u].rows * q[u].pages;
             longest = max(longest, q[u].pages);
+            if (q[u].rows > 0) shortest = min(shortest, q[u].pages);
 #pragma unroll
             for (int k = 0; k < kCandidates; ++k) counts[k] += q[u].rows * max(1, (q[u].pages + (4 << k) - 1) >> (k + 2));
         }
@@ -652,24 +654,43 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     // beyond that leave here, before the partition choice.
     if (item >= total_rows + (total_pages >> 2) && p.splits == 0) return false;
     longest = __reduce_max_sync(kFullMask, longest);
-    int my_items = total_rows;  // lanes >= kCandidates stand for "never split"
-#pragma unroll
-    for (int k = 0; k < kCandidates; ++k) {
-        const int sum = __reduce_add_sync(kFullMask, counts[k]);
-        if (lane == k) my_items = sum;
-    }
-    const int candidate = min(lane, kCandidates);
+    shortest = __reduce_min_sync(kFullMask, shortest);
     const float sms = static_cast<float>(p.sm_count), slots = sms * 4.f;  // four CTAs of this kernel fit on an SM
-    const float items = static_cast<float>(max(my_items, 1));
-    const float largest = candidate < kCandidates ? fminf(static_cast<float>(4 << candidate), static_cast<float>(longest))
-                                                  : static_cast<float>(longest);
-    float cost = wave_count(items * p.heads, slots, sms) * (static_cast<float>(total_pages) / items + kOverhead);
-    cost = fmaxf(cost, (0.25f / 0.45f) * (largest + kOverhead));  // the largest item alone on an SM is the floor
-    cost *= 1.f + 0.01f * static_cast<float>(kCandidates - candidate);  // near ties go to fewer partitions
-    uint32_t key = (__float_as_uint(cost) & ~15u) | static_cast<uint32_t>(kCandidates - candidate);
-    if (my_items > p.capacity) key = 0xffffffffu;  // does not fit the grid ("never split" always does)
-    const int chosen = kCandidates - static_cast<int>(__reduce_min_sync(kFullMask, key) & 15u);
-    int chunk = chosen < kCandidates ? 4 << chosen : 0x40000000;  // pages; "never split" = larger than any row
+    // modelled time of `items` items per head whose largest spans `largest` pages
+    auto cost_of = [&](int items_in, float largest) {
+        const float items = static_cast<float>(max(items_in, 1));
+        const float cost = wave_count(items * p.heads, slots, sms) * (static_cast<float>(total_pages) / items + kOverhead);
+        return fmaxf(cost, (0.25f / 0.45f) * (largest + kOverhead));  // the largest item alone on an SM is the floor
+    };
+    int chunk;
+    if (shortest == longest) {
+        // Every row spans the same number of pages (a decode batch of equal lengths, one request): the item count of a
+        // chunk size needs no sum over the requests, so every lane tries its own partition count 1..32.
+        const int mine = max(4, (longest + lane) / (lane + 1));
+        const int parts = max(1, (longest + mine - 1) / mine);
+        float cost = cost_of(total_rows * parts, static_cast<float>(min(mine, longest)));
+        cost *= 1.f + 0.01f * __log2f(static_cast<float>(parts));  // near ties go to fewer partitions
+        uint32_t key = (__float_as_uint(cost) & ~31u) | static_cast<uint32_t>(lane);
+        if (total_rows * parts > p.capacity && lane > 0) key = 0xffffffffu;  // does not fit the grid (one partition always does)
+        const int chosen = static_cast<int>(__reduce_min_sync(kFullMask, key) & 31u);
+        chunk = max(4, (longest + chosen) / (chosen + 1));
+    } else {
+        int my_items = total_rows;  // lanes >= kCandidates stand for "never split"
+#pragma unroll
+        for (int k = 0; k < kCandidates; ++k) {
+            const int sum = __reduce_add_sync(kFullMask, counts[k]);
+            if (lane == k) my_items = sum;
+        }
+        const int candidate = min(lane, kCandidates);
+        const float largest = candidate < kCandidates ? fminf(static_cast<float>(4 << candidate), static_cast<float>(longest))
+                                                      : static_cast<float>(longest);
+        float cost = cost_of(my_items, largest);
+        cost *= 1.f + 0.01f * static_cast<float>(kCandidates - candidate);  // near ties go to fewer partitions
+        uint32_t key = (__float_as_uint(cost) & ~15u) | static_cast<uint32_t>(kCandidates - candidate);
+        if (my_items > p.capacity) key = 0xffffffffu;  // does not fit the grid ("never split" always does)
+        const int chosen = kCandidates - static_cast<int>(__reduce_min_sync(kFullMask, key) & 15u);
+        chunk = chosen < kCandidates ? 4 << chosen : 0x40000000;  // pages; "never split" = larger than any row
+    }
     if (p.splits < 0) {
         // the caller fixed the chunk size (pages); it still has to fit the capacity: sum ceil(pages / c) <= T / c + rows
         const int spare = max(1, p.capacity - total_rows);
@@ -712,10 +733,9 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     return false;
 }
 
-// Wait until peer `peer` has published the epoch this rank has reached (gather_state[0]: one per completed call).  Bounded
-// by the GPU's global timer and a poll count; on expiry the status word of the state block is raised and the call goes on.
-__device__ __forceinline__ void wait_for_peers(const AttentionParams& p, int peer) {
-    const uint32_t target = __ldcg(p.gather_state);
+// Wait until peer `peer` has published epoch `target` (one epoch per completed call).  Bounded by the GPU's global timer
+// and a poll count; on expiry the status word of the state block is raised and the call goes on.
+__device__ __forceinline__ void wait_for_peers(const AttentionParams& p, int peer, uint32_t target) {
     const uint32_t* arrival = p.gather_flags[p.gather_rank] + peer;
     unsigned long long start = 0;
     for (uint32_t polls = 0;; ++polls) {
@@ -857,7 +877,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
     // Head-sharded serving: q depends, through the output projection, on the gathered rows of the previous call, so this
     // is where the call waits for every peer's stores of that call (bounded; ordered before the barrier below).
-    if (p.gather_wait && warp == 1 && lane < p.num_peers) wait_for_peers(p, lane);
+    if (p.gather_wait && warp == 1 && lane < p.num_peers) wait_for_peers(p, lane, __ldcg(p.gather_state));
 
     // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
     float* misc = warp_stat + 8;         // [0] last-arrival flag, [1] live score, [2] max |q|
@@ -1226,21 +1246,34 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
     if (p.gather_publish) {
         // The CTA that finishes the call's last (row, head) tells every GPU that this rank's rows are in place.
-        // One system-scope fence per CTA, by the thread that takes the ticket, after the CTA barrier: the barrier orders
-        // every thread's peer stores before the fence, and the fence is cumulative (the pattern of a grid-wide barrier).
+        // Every CTA: barrier (orders all of its threads' peer stores before thread 0's fence), a device-scope fence, a
+        // ticket.  The CTA that draws the last ticket has thereby observed every other CTA's fence; its own system-scope
+        // fence followed by the release stores of the flag extends that order to the peers (causality order composes
+        // across scopes), so a peer that has acquired the flag sees every row of the call.
+        uint32_t* published = reinterpret_cast<uint32_t*>(misc);  // [0]: the epoch this CTA published, 0 if it was not the last
         __syncthreads();
         if (tid == 0) {
-            __threadfence_system();
+            __threadfence();
             const uint32_t ticket = atomicAdd(p.gather_state + 2, 1u);
             const uint32_t total_rows = static_cast<uint32_t>(min(__ldcg(p.query_start_loc + p.num_requests), p.num_rows));
+            uint32_t epoch = 0u;
             if (ticket + 1u == total_rows * static_cast<uint32_t>(heads)) {
                 p.gather_state[2] = 0u;  // ready for the next call
-                __threadfence_system();  // every other CTA's stores (ordered before its ticket) before the flag
-                const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.gather_state) + 1u;
+                __threadfence_system();
+                epoch = *reinterpret_cast<volatile uint32_t*>(p.gather_state) + 1u;
                 *reinterpret_cast<volatile uint32_t*>(p.gather_state) = epoch;
                 for (int peer = 0; peer < p.num_peers; ++peer)
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather_flags[peer] + p.gather_rank), "r"(epoch) : "memory");
             }
+            published[0] = epoch;
+        }
+        if (p.gather_complete) {
+            // ... and stays until every peer's signal of the same call is here: the launch then ends only when this GPU's
+            // gathered buffer is complete.  The peers' kernels run on their own GPUs whatever this one does, so the wait
+            // cannot block them; it is bounded all the same.
+            __syncthreads();
+            const uint32_t epoch = published[0];
+            if (epoch != 0u && warp == 0 && lane < p.num_peers) wait_for_peers(p, lane, epoch);
         }
     }
 }

@@ -485,7 +485,7 @@ int32_t rq_attention(const RqAttentionArgs* a) {
         p.num_peers = a->num_peers;
         p.gather_head_offset = a->gather_head_offset;
         p.gather_stride = a->gather_stride;
-        if (a->flags & (RQ_FLAG_GATHER_PUBLISH | RQ_FLAG_GATHER_WAIT)) {
+        if (a->flags & (RQ_FLAG_GATHER_PUBLISH | RQ_FLAG_GATHER_WAIT | RQ_FLAG_GATHER_COMPLETE)) {
             if (a->gather_state == nullptr || !aligned(a->gather_state, 8) || a->gather_rank < 0 || a->gather_rank >= a->num_peers)
                 return fail(RQ_ERR_INVALID_ARGUMENT, "the gather signal needs this rank's state block and a rank below num_peers");
             for (int i = 0; i < a->num_peers; ++i) {
@@ -495,7 +495,8 @@ int32_t rq_attention(const RqAttentionArgs* a) {
             }
             p.gather_state = static_cast<uint32_t*>(a->gather_state);
             p.gather_rank = a->gather_rank;
-            p.gather_publish = (a->flags & RQ_FLAG_GATHER_PUBLISH) ? 1 : 0;
+            p.gather_complete = (a->flags & RQ_FLAG_GATHER_COMPLETE) ? 1 : 0;
+            p.gather_publish = (a->flags & (RQ_FLAG_GATHER_PUBLISH | RQ_FLAG_GATHER_COMPLETE)) ? 1 : 0;
             p.gather_wait = (a->flags & RQ_FLAG_GATHER_WAIT) ? 1 : 0;
             p.gather_timeout_ns = a->gather_timeout_ns ? a->gather_timeout_ns : 2000000000ull;
         }

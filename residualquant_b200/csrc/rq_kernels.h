@@ -103,7 +103,7 @@ struct AttentionParams {
     // [2] arrival counter), what this call does with them.
     uint32_t* gather_flags[RQ_MAX_PEERS];
     uint32_t* gather_state;
-    int gather_rank, gather_publish, gather_wait;
+    int gather_rank, gather_publish, gather_wait, gather_complete;
     unsigned long long gather_timeout_ns;
 };
 

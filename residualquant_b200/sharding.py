@@ -114,10 +114,17 @@ class HeadGather:
     two-buffer rule holds: a rank publishes call n+1 only after its own wait for call n, so whoever has seen every
     rank's signal n+1 knows that buffer n%2 is no longer being read.  `barrier()` then is the consumer's wait alone
     (no publish), to be called wherever something other than the next attention call reads the gathered rows.
+
+    `complete=True` needs no barrier at all: the attention kernel's last CTA publishes and then stays until every peer's
+    signal of the same call has arrived, so the call ends only when this GPU's gathered buffer is complete and any
+    kernel that follows on the stream may read it.  `barrier()` does nothing in this form.
     """
 
-    def __init__(self, rows: int, heads: int, head_dim: int, device, buffers: int = 2, signalled: bool = False):
-        self.signalled = signalled
+    def __init__(self, rows: int, heads: int, head_dim: int, device, buffers: int = 2, signalled: bool = False,
+                 complete: bool = False):
+        if signalled and complete:
+            raise ValueError("choose one of signalled and complete")
+        self.signalled, self.complete = signalled, complete
         self.lib = _lib.load()
         self.device = torch.device(device)
         self.rows, self.heads, self.head_dim, self.buffers = rows, heads, head_dim, buffers
@@ -167,6 +174,8 @@ class HeadGather:
         return flat.view(self.rows, self.heads, self.head_dim)
 
     def barrier(self, timeout_ns: int = 0) -> None:
+        if self.complete:
+            return
         args = _lib.RqPeerBarrierArgs()
         args.world, args.rank = self.world, self.rank
         for i, base in enumerate(self.bases):

@@ -1,9 +1,11 @@
 """One rank of the two-GPU head-gather test (launched by tests/test_gpu_head_gather_multi.py under torchrun).
 
-KV heads are split unevenly over the ranks (5 = 3 + 2).  Both forms of the fused gather run several calls with the two
-gathered buffers alternating: the barrier form (`HeadGather.barrier()` after every call) and the signalled form (the
-kernel publishes, the next call waits).  After every form the gathered rows must equal an NCCL all-gather of the ranks'
-own outputs bit for bit, and the state block must show no timeout.  Peer stores are plain stores; no multicast."""
+KV heads are split unevenly over the ranks (5 = 3 + 2).  All three forms of the fused gather run several calls with the two
+gathered buffers alternating: the barrier form (`HeadGather.barrier()` after every call), the signalled form (the
+kernel publishes, the next call waits) and the complete form (the kernel publishes and stays until every rank has).
+After every form the gathered rows must equal an NCCL all-gather of the ranks' own outputs bit for bit, the state block
+must show no timeout, and in the barrier and complete forms a copy queued right behind every call must already hold
+every rank's rows of that call.  Peer stores are plain stores; no multicast."""
 
 import os
 import sys
@@ -40,33 +42,41 @@ def main():
     table = torch.from_numpy(full.block_table).to(device)
     records = [list(r) for r in full.layout.records]
     failures = []
-    for signalled in (False, True):
-        gather = sharding.HeadGather(rows, heads, 128, device, buffers=2, signalled=signalled)
-        outs = []
+    for form in ("barrier", "signalled", "complete"):
+        gather = sharding.HeadGather(rows, heads, 128, device, buffers=2, signalled=form == "signalled",
+                                     complete=form == "complete")
+        outs, snapshots = [], []
         for call, loop in enumerate((0, 1, 2, 3, 1, 0, 3)):
             k = G.bf16(full.keys[loop][full.live_rows][:, begin:end], device)
             v = G.bf16(full.values[loop][full.live_rows][:, begin:end], device)
             out = torch.zeros_like(q)
             _cuda.attention(q, k, v, cache, out, qsl, seq, table, kr, vr, None, records, "anchor", 3, loop,
                             gather=gather, gather_buffer=call % 2)
-            if not signalled:
+            if form == "barrier":
                 gather.barrier()
+            if form != "signalled":
+                # what a consumer queued right behind the call (and its barrier) reads: every rank's rows of THIS call
+                snapshots.append(gather.gathered(call % 2).clone())
             outs.append((loop, call % 2, out))
-        if signalled:
+        if form == "signalled":
             gather.barrier()     # the consumer's wait
         gather.check()
         torch.cuda.synchronize(device)
-        for loop, buffer, out in outs[-2:]:
+        for index, (loop, buffer, out) in enumerate(outs):
             expected = sharding.gather_heads(out, heads)
+            if snapshots and not torch.equal(snapshots[index], expected):
+                failures.append(f"{form} call {index}: the rows read behind the call differ from the all-gather")
+            if index < len(outs) - 2:
+                continue
             if not torch.equal(gather.gathered(buffer), expected):
-                failures.append(f"signalled={signalled} loop {loop}: gathered rows differ from the all-gather")
+                failures.append(f"{form} loop {loop}: gathered rows differ from the all-gather")
             want = helpers.oracle_attention(full, helpers.oracle_cache(full), loop)
             got = expected.float().cpu().numpy()
             if not np.all(np.abs(got - want) <= 2e-2 + 1e-2 * np.abs(want)):
-                failures.append(f"signalled={signalled} loop {loop}: outside the tolerance of the oracle")
+                failures.append(f"{form} loop {loop}: outside the tolerance of the oracle")
         state = gather.state[:3].tolist()
         if state[1] != 0 or state[0] != 7:
-            failures.append(f"signalled={signalled}: state {state}")
+            failures.append(f"{form}: state {state}")
         gather.close()
     flag = torch.tensor([len(failures)], device=device)
     dist.all_reduce(flag)
