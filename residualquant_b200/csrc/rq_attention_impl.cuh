@@ -249,16 +249,21 @@ struct QueryOperands {
 template <int BITS>
 __device__ __forceinline__ void build_operands(const float* qslice, bool slice_ok, float qmax, QueryOperands<BITS>& out) {
     constexpr float kLevels = BITS == 4 ? 1900.f : 8191.f;
-    const float to_int = qmax > 0.f ? kLevels / qmax : 0.f, unit = qmax / kLevels;
+    const float to_int = (slice_ok && qmax > 0.f) ? kLevels / qmax : 0.f, unit = qmax / kLevels;
+    // Round to the nearest integer by adding 1.5 * 2^23: the integer sits in the low significand bits (round half to even,
+    // like a float-to-int conversion), and neither the rounding nor the sums below touch the conversion unit, which the
+    // four warps of a CTA would otherwise queue on right after the query arrives.
+    constexpr float kMagic = 12582912.f;
+    constexpr int kMagicBits = 0x4B400000;
     int iq[32];
-    float s0 = 0.f, s1 = 0.f;
+    int s0 = 0, s1 = 0;
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
-        iq[c] = slice_ok ? __float2int_rn(qslice[c] * to_int) : 0;
-        if (c < 16) s0 += static_cast<float>(iq[c]); else s1 += static_cast<float>(iq[c]);
+        iq[c] = __float_as_int(__fmaf_rn(qslice[c], to_int, kMagic)) - kMagicBits;
+        if (c < 16) s0 += iq[c]; else s1 += iq[c];
     }
-    out.sum0 = s0 * unit;
-    out.sum1 = s1 * unit;
+    out.sum0 = static_cast<float>(s0) * unit;
+    out.sum1 = static_cast<float>(s1) * unit;
     if (BITS == 4) {
         out.dot_unit = unit * 0.0625f;  // the integer dot product carries a factor 16
 #pragma unroll
@@ -555,10 +560,17 @@ struct WorkItem {
 // Cost of running `items` equally sized CTAs per head, in units of (pages one CTA consumes while four share an SM):
 // full waves of `slots` CTAs plus a tail wave in which an SM holding 1/2/3/4 CTAs delivers 0.45/0.85/0.92/1 of its
 // throughput (fitted to measurements on B200: the kernel is bound by instruction issue).
+// (a + b - 1) / b for 0 <= a < 2^21, 0 < b: the quotient of the approximate division is within 2 ulp, far inside the
+// half-unit margin that a + 0.5 leaves on either side of an integer.  An integer division costs a few hundred cycles of
+// dependent instructions, and the work lookup sits in front of everything a CTA does.
+__device__ __forceinline__ int ceil_div_small(int a, int b) {
+    return static_cast<int>(__fdividef(static_cast<float>(a + b - 1) + 0.5f, static_cast<float>(b)));
+}
+
 __device__ __forceinline__ float wave_count(float ctas, float slots, float sms) {
-    const float full = floorf(ctas / slots);
+    const float full = floorf(__fdividef(ctas + 0.5f, slots));   // ctas and slots are integers
     const float rest = ctas - full * slots;
-    const int per_sm = static_cast<int>(ceilf(rest / sms));
+    const int per_sm = static_cast<int>(ceilf(__fdividef(rest - 0.5f, sms)));
     const float tail = per_sm <= 0 ? 0.f : per_sm == 1 ? 1.f / 0.45f : per_sm == 2 ? 2.f / 0.85f : per_sm == 3 ? 3.f / 0.92f : 4.f;
     return full + 0.25f * tail;
 }
@@ -659,21 +671,21 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
     // modelled time of `items` items per head whose largest spans `largest` pages
     auto cost_of = [&](int items_in, float largest) {
         const float items = static_cast<float>(max(items_in, 1));
-        const float cost = wave_count(items * p.heads, slots, sms) * (static_cast<float>(total_pages) / items + kOverhead);
+        const float cost = wave_count(items * p.heads, slots, sms) * (__fdividef(static_cast<float>(total_pages), items) + kOverhead);
         return fmaxf(cost, (0.25f / 0.45f) * (largest + kOverhead));  // the largest item alone on an SM is the floor
     };
     int chunk;
     if (shortest == longest) {
         // Every row spans the same number of pages (a decode batch of equal lengths, one request): the item count of a
         // chunk size needs no sum over the requests, so every lane tries its own partition count 1..32.
-        const int mine = max(4, (longest + lane) / (lane + 1));
-        const int parts = max(1, (longest + mine - 1) / mine);
+        const int mine = max(4, ceil_div_small(longest, lane + 1));
+        const int parts = max(1, ceil_div_small(longest, mine));
         float cost = cost_of(total_rows * parts, static_cast<float>(min(mine, longest)));
         cost *= 1.f + 0.01f * __log2f(static_cast<float>(parts));  // near ties go to fewer partitions
         uint32_t key = (__float_as_uint(cost) & ~31u) | static_cast<uint32_t>(lane);
         if (total_rows * parts > p.capacity && lane > 0) key = 0xffffffffu;  // does not fit the grid (one partition always does)
         const int chosen = static_cast<int>(__reduce_min_sync(kFullMask, key) & 31u);
-        chunk = max(4, (longest + chosen) / (chosen + 1));
+        chunk = max(4, __shfl_sync(kFullMask, mine, chosen));
     } else {
         int my_items = total_rows;  // lanes >= kCandidates stand for "never split"
 #pragma unroll
@@ -1173,28 +1185,53 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         float* mine = p.partials + (static_cast<int64_t>(work.first + split) * heads + head) * (D + 2);
         if (tid == 0) { mine[0] = part_m; mine[1] = part_l; }
         if (tid < D) mine[2 + tid] = value;
-        __threadfence();
+        // Release: the barrier orders every thread's stores before thread 0's fence, which is cumulative; the ticket follows
+        // it.  Acquire: the thread that drew the last ticket fences again before the barrier that lets the others read
+        // (through L2: ld.global.cg).  One thread fences instead of all of them.
         __syncthreads();
         if (tid == 0) {
+            __threadfence();
             const int ticket = atomicAdd(p.counters + row * heads + head, 1);
-            misc[0] = ticket == splits - 1 ? 1.f : 0.f;
-            if (ticket == splits - 1) p.counters[row * heads + head] = 0;  // ready for the next call
+            const bool last = ticket == splits - 1;
+            if (last) {
+                p.counters[row * heads + head] = 0;  // ready for the next call
+                __threadfence();
+            }
+            misc[0] = last ? 1.f : 0.f;
         }
         __syncthreads();
         if (misc[0] == 0.f) return;
-        __threadfence();
         const float* all = p.partials + (static_cast<int64_t>(work.first) * heads + head) * (D + 2);
+        // One pass, eight partitions' (max, denominator, value) loads in flight at a time; the partitions are merged like
+        // the tokens of the page loop, by rescaling the running sums when the reference exponent moves.
         part_m = kNever;
-#pragma unroll 8
-        for (int s = 0; s < splits; ++s) part_m = fmaxf(part_m, __ldcg(all + s * item_stride));
         part_l = 0.f;
         value = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < splits; ++s) {
-            const float ms = __ldcg(all + s * item_stride);
-            const float f = fast_exp2(ms - part_m);
-            part_l += __ldcg(all + s * item_stride + 1) * f;
-            if (tid < D) value += __ldcg(all + s * item_stride + 2 + tid) * f;
+        for (int base = 0; base < splits; base += 8) {
+            float ms[8], ls[8], vs[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float* one = all + min(base + u, splits - 1) * item_stride;   // clamped: a repeated load, not a branch
+                ms[u] = __ldcg(one);
+                ls[u] = __ldcg(one + 1);
+                vs[u] = tid < D ? __ldcg(one + 2 + tid) : 0.f;
+            }
+            float batch_m = part_m;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (base + u < splits) batch_m = fmaxf(batch_m, ms[u]);
+            const float keep = fast_exp2(part_m - batch_m);   // kNever - kNever = 0 the first time: the sums are zero anyway
+            part_l *= keep;
+            value *= keep;
+            part_m = batch_m;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (base + u < splits) {
+                    const float f = fast_exp2(ms[u] - part_m);
+                    part_l += ls[u] * f;
+                    value += vs[u] * f;
+                }
+            }
         }
     }
 
