@@ -90,10 +90,11 @@ def parse_args():
     p.add_argument("--shard", default="sequences", choices=["sequences", "heads"],
                    help="sequences: every rank owns its own batch (weak scaling, no collective); heads: every rank holds "
                         "all sequences but only its KV heads and all-gathers the attention output (strong scaling)")
-    p.add_argument("--gather", default="fused", choices=["fused", "barrier", "nccl"],
+    p.add_argument("--gather", default="fused", choices=["fused", "complete", "nccl"],
                    help="with --shard heads: fused = the attention kernel stores into every GPU's gathered output over "
-                        "NVLink and ends only when every rank's rows have arrived (captured in the graph); barrier = the "
-                        "same stores followed by a barrier kernel per call; nccl = one all-gather per call, eager")
+                        "NVLink, followed by a barrier kernel per call (captured in the graph); complete = the same stores, "
+                        "the kernel itself ends only when every rank's rows have arrived (no barrier launch); nccl = one "
+                        "all-gather per call, eager")
     p.add_argument("--splits", type=int, default=0,
                    help="force the number of KV partitions per row (0 = the kernel picks them per row from the lengths)")
     p.add_argument("--quick", action="store_true",
@@ -709,11 +710,14 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
     stack = Stack(shape, device, torch, heads_here=local, seed_offset=1000 + rank)
     def measure(gather):
         def step():
-            # complete form: every attention call ends only when all ranks' rows of that call are in this GPU's gathered
-            # buffer (its last CTA publishes and waits), so nothing sits between the calls.  barrier form: one barrier
-            # kernel per call, launched as a programmatic dependent.
+            # barrier form: one barrier kernel per call, launched as a programmatic dependent.  complete form: every
+            # attention call ends only when all ranks' rows of that call are in this GPU's gathered buffer (its last CTA
+            # publishes and waits), so nothing sits between the calls.  No gather at all: what the rank's own work costs.
             for layer in range(shape.layers):
                 for loop in range(4):
+                    if gather is None:
+                        stack.attention(layer, loop)
+                        continue
                     stack.attention(layer, loop, gather=gather, gather_buffer=loop % 2)
                     gather.barrier()
                 stack.quantize(layer)
@@ -730,6 +734,9 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
             for _ in range(warmup):
                 graph.replay()
         ms = timer.timed(graph.replay, steps)
+        if gather is None:
+            del graph
+            return ms, True
         gather.check()
         expected = sharding.gather_heads(stack.out[shape.layers - 1, 3], shape.heads)
         equal = bool(torch.equal(gather.gathered(3 % 2), expected))
@@ -739,19 +746,23 @@ def head_sharded_figures(timer, torch, dist, device, rank, world, steps, warmup)
         del graph
         return ms, bool(flags.item() == 1)
 
-    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device, complete=True)
+    gather = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
     ms, equal = measure(gather)
-    with_barrier = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device)
-    barrier_ms, barrier_equal = measure(with_barrier)
-    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 32 "
+    complete = sharding.HeadGather(shape.batch, shape.heads, shape.head_dim, device, complete=True)
+    complete_ms, complete_equal = measure(complete)
+    alone_ms, _ = measure(None)
+    result = {"shape": "55 heads x 96, batch 16 x context 4096, 32 (layer, group) caches, 128 attention + 128 barrier + 32 "
                        "write launches per step, INT2 g32 + INT4 g32; output rows stored into every GPU's gathered buffer by the "
-                       "attention kernel, whose last CTA publishes and waits for every rank (no barrier launch)",
+                       "attention kernel, one barrier kernel per call (programmatic dependent)",
               "n": world, "heads_per_rank": sharding.shard_counts(shape.heads, world),
               "tokens_per_s": shape.batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
               "gathered_equal_nccl": equal, "scaling": "strong",
-              "barrier_form": {"ms_per_step": barrier_ms / steps, "gathered_equal_nccl": barrier_equal,
-                               "launches": "128 attention + 128 barrier + 32 write"}}
-    del stack, gather, with_barrier
+              # the same step with the barrier folded into the attention kernel (its last CTA publishes and waits for
+              # every rank), and with no gather at all (this rank's share of the work alone: the bound of the scaling)
+              "complete_form": {"ms_per_step": complete_ms / steps, "gathered_equal_nccl": complete_equal,
+                                "launches": "128 attention + 32 write"},
+              "without_gather_ms_per_step": alone_ms / steps}
+    del stack, gather, complete
     torch.cuda.empty_cache()
     return result
 
@@ -912,7 +923,7 @@ def run_gpu(args, shape):
     gathered = [None]
     # Head sharding: the output projection needs every head.  "fused": the attention kernel stores its rows into every
     # GPU's gathered buffer over NVLink (graph capturable); "nccl": one all-gather per call.
-    fused_gather = (sharding.HeadGather(B, shape.heads, shape.head_dim, device, complete=args.gather == "fused")
+    fused_gather = (sharding.HeadGather(B, shape.heads, shape.head_dim, device, complete=args.gather == "complete")
                     if shard_heads and args.gather != "nccl" else None)
 
     def hot_path():

@@ -26,6 +26,20 @@ __constant__ uint32_t kPaleyRow[16] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0
 __constant__ uint32_t kPaleyCol[16] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc,
                                        0x5b8, 0xb70, 0x6e2, 0xdc4, 0, 0, 0, 0};
 
+// The same masks for code whose indices are compile-time constants (the unrolled 12-point stage of a row in shared memory).
+__host__ __device__ constexpr uint32_t paley_row_mask(int i) {
+    constexpr uint32_t rows[12] = {0x0, 0x476, 0x8ec, 0x1da, 0x3b4, 0x768, 0xed0, 0xda2, 0xb46, 0x68e, 0xd1c, 0xa3a};
+    return rows[i];
+}
+__host__ __device__ constexpr uint32_t paley_col_mask(int j) {
+    constexpr uint32_t cols[12] = {0x0, 0xb8a, 0x716, 0xe2c, 0xc5a, 0x8b6, 0x16e, 0x2dc, 0x5b8, 0xb70, 0x6e2, 0xdc4};
+    return cols[j];
+}
+// head_dim 96: the 12-point stage runs through shared memory, one scratch row of 96 floats per row of the warp.  The
+// stride keeps the four rows of a warp on different banks when 32 lanes read (row, position) columns.
+constexpr int kPaleyStride = 104;
+constexpr int kPaleyWarpFloats = 4 * kPaleyStride;
+
 // ---- packed binary32 pairs ------------------------------------------------------------------------------------------
 // sm_100 issues add / mul / fma on PAIRS of binary32 values (add.f32x2, mul.f32x2, fma.f32x2): two IEEE operations with
 // round-to-nearest-even each -- the same results as two scalar instructions -- in one issue slot.  A lane's 16 channels
@@ -111,8 +125,9 @@ __device__ __forceinline__ void butterfly_across_lanes_16(float (&x)[16], int ma
 
 // Forward: y = ((sign * x) H) * rscale.  Inverse: x = ((y H^T) * rscale) * sign.
 // `j` is the lane's slice (channels 16j .. 16j+15) inside its 8-lane row group.
+// `scratch`: head_dim 96 only, kPaleyWarpFloats floats of shared memory owned by the calling warp.
 template <int D, bool INVERSE>
-__device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign16, float rscale) {
+__device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign16, float rscale, float* scratch) {
     // forward: the sign diagonal has already been applied when the row was loaded
     if (D == 128) {
         butterflies_16(x, true);
@@ -122,31 +137,38 @@ __device__ __forceinline__ void rotate_row(float (&x)[16], int j, uint32_t sign1
     } else {
         // Sylvester-8 inside each block of 8 channels (two blocks per lane) ...
         butterflies_16(x, false);
-        // ... then the 12-point Paley transform across blocks: out[a'] = sum_a s(a, a') t[a], a = 0..11.
+        // ... then the 12-point Paley transform across the row's 12 blocks: out[a'] = sum_a s(a, a') t[a], a = 0..11, added
+        // in that order.  The warp's four rows go to shared memory; lane (row, b) then owns position b of every block of
+        // its row -- one column of 12 values -- and forms the 12 outputs from registers with compile-time signs: 12 loads
+        // and 132 additions per lane and record instead of 96 shuffles and 192 additions with run-time signs.
         const int lane = threadIdx.x & 31;
-        const int group_base = lane & 24;
-        const uint32_t mask0 = INVERSE ? kPaleyRow[(2 * j) & 15] : kPaleyCol[(2 * j) & 15];
-        const uint32_t mask1 = INVERSE ? kPaleyRow[(2 * j + 1) & 15] : kPaleyCol[(2 * j + 1) & 15];
-        float out[16];
+        float* row = scratch + (lane >> 3) * kPaleyStride;
+        __syncwarp();  // the previous record's readers are done with the scratch rows
+        if (j < 6) {
 #pragma unroll
-        for (int a = 0; a < 12; ++a) {
-            const bool neg0 = (mask0 >> a) & 1u, neg1 = (mask1 >> a) & 1u;
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                const float v = __shfl_sync(kFullMask, x[8 * (a & 1) + b], group_base + (a >> 1));
-                const float t0 = neg0 ? -v : v, t1 = neg1 ? -v : v;
-                if (a == 0) {
-                    out[b] = t0;
-                    out[8 + b] = t1;
-                } else {
-                    out[b] = __fadd_rn(out[b], t0);
-                    out[8 + b] = __fadd_rn(out[8 + b], t1);
-                }
-            }
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<float4*>(row + 16 * j + 4 * i) = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
         }
+        __syncwarp();
+        float t[12], out[12];
+#pragma unroll
+        for (int a = 0; a < 12; ++a) t[a] = row[8 * a + j];   // j = lane & 7 is the position inside a block here
+#pragma unroll
+        for (int to = 0; to < 12; ++to) {
+            const uint32_t mask = INVERSE ? paley_row_mask(to) : paley_col_mask(to);
+            out[to] = (mask & 1u) ? -t[0] : t[0];
+#pragma unroll
+            for (int a = 1; a < 12; ++a) out[to] = ((mask >> a) & 1u) ? __fsub_rn(out[to], t[a]) : __fadd_rn(out[to], t[a]);
+        }
+#pragma unroll
+        for (int to = 0; to < 12; ++to) row[8 * to + j] = out[to];   // only this lane reads or writes its column
+        __syncwarp();
         // lanes 6 and 7 of a row group own no channels: keep them at zero so that row sums ignore them
 #pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = j < 6 ? out[i] : 0.f;
+        for (int i = 0; i < 4; ++i) {
+            const float4 v = j < 6 ? *reinterpret_cast<const float4*>(row + 16 * j + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+        }
     }
     const float2 rscale2 = make_float2(rscale, rscale);
 #pragma unroll
@@ -283,7 +305,8 @@ constexpr int kTileStride = D + 8;
 // quantize_dense_kernel; otherwise they are read from the caller's bf16 tensors and rotated here if the plane has a
 // signed-Hadamard rotation.
 template <int D, class S, bool SHARED_ROWS>
-__device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token, int head, int plane, const float* tile) {
+__device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token, int head, int plane, const float* tile,
+                                              float* scratch) {
     // run-time values, or the schedule's constants
     const int num_records = [&] { if constexpr (S::kFixed) return S::kRecords; else return p.num_records; }();
     const int anchor = [&] { if constexpr (S::kFixed) return S::kAnchor; else return p.anchor; }();
@@ -432,7 +455,7 @@ __device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token
     {
         float y[16], mean[16];
         if (packed_rows) unpack(words, y, true); else load_unpacked(anchor, y, true);
-        if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+        if (rotated) rotate_row<D, false>(y, j, sign16, rscale, scratch);
         if (centered) {
             load_mean(anchor, mean);
 #pragma unroll
@@ -453,7 +476,7 @@ __device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token
                 ref[i] = __fmaf_rn(code_value(q.magic[i]), scale, offset);
                 if (centered) ref[i] = __fadd_rn(ref[i], mean[i]);
             }
-            if (rotated) rotate_row<D, true>(ref, j, sign16, rscale);
+            if (rotated) rotate_row<D, true>(ref, j, sign16, rscale, scratch);
 #pragma unroll
             for (int i = 0; i < 16; ++i) ref[i] = bf16_round(ref[i]);
         }
@@ -475,7 +498,7 @@ __device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token
         }
         uint16_t alpha_bits;
         if (chain == RQ_CHAIN_KERNEL) {
-            if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+            if (rotated) rotate_row<D, false>(y, j, sign16, rscale, scratch);
             const __nv_bfloat16 stored = __float2bfloat16_rn(coefficient(y, ref, den));
             alpha_bits = __bfloat16_as_ushort(stored);
             const float alpha = __bfloat162float(stored);
@@ -495,7 +518,7 @@ __device__ __forceinline__ void quantize_rows(const QuantizeParams& p, int token
                 const float target = bf16_round(__fsub_rn(y[i], prediction));
                 y[i] = ((sign16 >> i) & 1u) ? -target : target;  // sign diagonal of the forward rotation
             }
-            if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+            if (rotated) rotate_row<D, false>(y, j, sign16, rscale, scratch);
         }
         if (centered) {
             load_mean(r, mean);
@@ -528,8 +551,10 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
     // nothing is read or written before it has completed.  After that the next kernel may be scheduled.
     pdl_wait();
     pdl_launch_dependents();
+    __shared__ __align__(16) float paley[D == 96 ? 4 * kPaleyWarpFloats : 4];  // head_dim 96: the rotation's 12-point stage
     const int token = blockIdx.x * 16 + (threadIdx.x >> 3);  // a warp owns 4 consecutive tokens of one head
-    quantize_rows<D, S, false>(p, token, blockIdx.y, p.plane_first + blockIdx.z, nullptr);
+    quantize_rows<D, S, false>(p, token, blockIdx.y, p.plane_first + blockIdx.z, nullptr,
+                               paley + (D == 96 ? (threadIdx.x >> 5) * kPaleyWarpFloats : 0));
 }
 
 // ---- dense (learned) rotation fused into the quantizer ------------------------------------------------------------
@@ -573,8 +598,9 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
     const int tiles = p.dense_tiles;
     if (p.dense_matrix[plane] == nullptr) {
         // the other plane of the same call has no dense rotation: same launch, plain path
-        for (int step = 0; step < tiles; ++step)
-            quantize_rows<D, S, false>(p, (blockIdx.x * tiles + step) * 16 + (tid >> 3), head, plane, nullptr);
+        for (int step = 0; step < tiles; ++step)   // the tile area is free here: it serves as the rotation's scratch
+            quantize_rows<D, S, false>(p, (blockIdx.x * tiles + step) * 16 + (tid >> 3), head, plane, nullptr,
+                                       tile + warp * kPaleyWarpFloats);
         return;
     }
 
@@ -661,7 +687,7 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
             }
         }
         __syncthreads();
-        quantize_rows<D, S, true>(p, first + (tid >> 3), head, plane, tile);
+        quantize_rows<D, S, true>(p, first + (tid >> 3), head, plane, tile, nullptr);
     }
 }
 
@@ -676,7 +702,9 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
     constexpr int kSlices = D / 16, kAnchor = 3;
     pdl_wait();  // see quantize_kernel
     pdl_launch_dependents();
+    __shared__ __align__(16) float paley[D == 96 ? 4 * kPaleyWarpFloats : 4];  // head_dim 96: the rotation's 12-point stage
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* scratch = paley + (D == 96 ? warp * kPaleyWarpFloats : 0);
     const int j = lane & 7, record = lane >> 3;
     const int token = blockIdx.x * 4 + warp;
     const int head = blockIdx.y, plane = p.plane_first + blockIdx.z;
@@ -717,7 +745,7 @@ __global__ void __launch_bounds__(128) quantize_token_kernel(const __grid_consta
             }
         }
     }
-    if (rotated) rotate_row<D, false>(y, j, sign16, rscale);
+    if (rotated) rotate_row<D, false>(y, j, sign16, rscale, scratch);
     const int P = p.page_tokens;
     const int tok = static_cast<int>(slot % P);
     uint8_t* page = p.cache + plane * p.plane_stride + (slot / P * p.heads + head) * static_cast<int64_t>(P) * p.page_width;
