@@ -49,10 +49,9 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant_
     __syncwarp();
     const uint32_t epoch = next_epoch;
     if (t >= p.world) return;
-    if (!p.wait_only) {
-        __threadfence_system();
-        store_release_system(p.flags[t] + p.rank, epoch);
-    }
+    // The release store is itself a system-scope fence followed by the store; what it has to cover -- the rows the
+    // previous kernel stored into the peers' buffers -- was completed by that kernel's end, which this kernel waited for.
+    if (!p.wait_only) store_release_system(p.flags[t] + p.rank, epoch);
     const uint32_t* arrival = p.flags[p.rank] + t;
     const unsigned long long start = global_timer_ns();
     for (unsigned long long polls = 0;; ++polls) {
