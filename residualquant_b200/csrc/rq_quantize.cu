@@ -563,7 +563,7 @@ __global__ void __launch_bounds__(128, 5) quantize_kernel(const __grid_constant_
 // reference's rotation, plugins/residual_quantization/csrc/quantize/rotation.cuh:25-150), the CTA then walks over
 // kDenseTiles tiles of 16 tokens: stage the tile's records x 16 rows, rotate them in place (one 16-row MMA tile per
 // warp and record), quantize them from shared memory.  Nothing goes through global memory in between.
-constexpr int kDenseTiles = 4;  // long writes: 64 tokens per CTA, the matrix is read once per 64 tokens of a head
+constexpr int kDenseTiles = 4;  // long writes: 64 (or 128) tokens per CTA, the matrix is staged once per CTA
 
 __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile(
@@ -604,54 +604,77 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
         return;
     }
 
-    // R[h]: fp16 [D][D] -> fp32 in shared memory, 8 entries per 16-byte load
-    const uint4* r = reinterpret_cast<const uint4*>(p.dense_matrix[plane] + static_cast<int64_t>(head) * D * D);
-    for (int i = tid; i < D * D / 8; i += 128) {
-        const uint4 packed = __ldg(r + i);
-        const int k = (8 * i) / D, c0 = (8 * i) % D;   // eight consecutive columns of row k: one 8-column tile
-        const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
-        const int tile_n = c0 >> 3, kk = k & 7;
-        // row k is k-index (kk / 2) [+ 4 when kk is odd] of its k-step: slot kk & 1 of lanes with t = kk / 2
-        float* dst = matrix + (((k >> 3) * (D / 16) + (tile_n >> 1)) * 32 + (kk >> 1)) * 4 + 2 * (tile_n & 1) + (kk & 1);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
-            dst[(2 * w) * 16] = pair.x;          // column g = 2w     -> lane 4g + t: 16 floats further per g
-            dst[(2 * w + 1) * 16] = pair.y;      // column g = 2w + 1
+    // R[h]: fp16 [D][D] -> fp32 in shared memory, in fragment order.  A warp fills one block of 32 float4 (the B fragments
+    // of one k-step and one pair of 8-column tiles) per round: every lane gathers its own four entries -- two rows, two
+    // column tiles -- and stores one float4, so the stores are contiguous over the warp (no bank conflict); the 2-byte
+    // gathers hit L1/L2, every CTA of the head reads the same 2 D^2 bytes.
+    {
+        const unsigned short* r = reinterpret_cast<const unsigned short*>(p.dense_matrix[plane]) + static_cast<int64_t>(head) * D * D;
+        const int g = lane >> 2, t = lane & 3;
+        constexpr int kBlocks = (D / 8) * (D / 16);
+#pragma unroll 4
+        for (int block = warp; block < kBlocks; block += 4) {
+            const int ks = block / (D / 16), pair = block % (D / 16);
+            const unsigned short* from = r + (8 * ks + 2 * t) * D + 16 * pair + g;
+            const unsigned short a0 = __ldg(from), a1 = __ldg(from + D), b0 = __ldg(from + 8), b1 = __ldg(from + D + 8);
+            reinterpret_cast<float4*>(matrix)[block * 32 + lane] =
+                make_float4(__half2float(__ushort_as_half(a0)), __half2float(__ushort_as_half(a1)),
+                            __half2float(__ushort_as_half(b0)), __half2float(__ushort_as_half(b1)));
         }
     }
     const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
     const int64_t* strides = plane == 0 ? p.key_stride : p.value_stride;
 
+    // A thread's share of a tile: chunk i = tid + 128 u is eight channels (16 bytes) of row i / (D/8) of the tile.  The
+    // rows of the NEXT tile are fetched into registers before the current tile is rotated and quantized, so that their
+    // latency is covered by that work instead of standing in front of the next staging step.
+    constexpr int kChunks = 4 * 16 * (D / 8) / 128;   // per thread, for the largest group (four records)
+    uint4 fetched[kChunks];
+    auto fetch = [&](int first) {
+        const int chunks = num_records * 16 * (D / 8);
+#pragma unroll
+        for (int u = 0; u < kChunks; ++u) {
+            const int i = tid + 128 * u;
+            const int row = i / (D / 8), c8 = i % (D / 8);
+            const int record = row >> 4, token = first + (row & 15);
+            fetched[u] = make_uint4(0u, 0u, 0u, 0u);   // rows of padding slots or beyond the call stay zero
+            if (i < chunks && token < p.num_tokens && p.slots[token] >= 0) {
+                const __nv_bfloat16* x = sources[record] + static_cast<int64_t>(token) * strides[record] + head * D + 8 * c8;
+                if (p.vector_loads) {
+                    fetched[u] = __ldg(reinterpret_cast<const uint4*>(x));
+                } else {
+                    const unsigned short* h = reinterpret_cast<const unsigned short*>(x);
+                    fetched[u] = make_uint4(h[0] | (static_cast<uint32_t>(h[1]) << 16), h[2] | (static_cast<uint32_t>(h[3]) << 16),
+                                            h[4] | (static_cast<uint32_t>(h[5]) << 16), h[6] | (static_cast<uint32_t>(h[7]) << 16));
+                }
+            }
+        }
+    };
+    const int first_tile = blockIdx.x * tiles * 16;
+    if (first_tile < p.num_tokens) fetch(first_tile);
+
     for (int step = 0; step < tiles; ++step) {
         const int first = (blockIdx.x * tiles + step) * 16;
         if (first >= p.num_tokens) break;  // uniform over the CTA
         __syncthreads();  // the previous tile has been quantized (and, the first time, the matrix is staged below the next barrier)
-        // stage: records x 16 rows of D bf16 -> fp32; rows of padding slots or beyond the call stay zero
-        const int chunks = num_records * 16 * (D / 8);
-        for (int i = tid; i < chunks; i += 128) {
-            const int row = i / (D / 8), c8 = i % (D / 8);
-            const int record = row >> 4, token = first + (row & 15);
-            float values[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (token < p.num_tokens && p.slots[token] >= 0) {
-                const __nv_bfloat16* x = sources[record] + static_cast<int64_t>(token) * strides[record] + head * D + 8 * c8;
-                if (p.vector_loads) {
-                    const uint4 packed = __ldg(reinterpret_cast<const uint4*>(x));
-                    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+        // stage: the fetched bf16 rows -> fp32
+        {
+            const int chunks = num_records * 16 * (D / 8);
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        values[2 * w] = __uint_as_float(words[w] << 16);
-                        values[2 * w + 1] = __uint_as_float(words[w] & 0xffff0000u);
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) values[e] = __bfloat162float(x[e]);
+            for (int u = 0; u < kChunks; ++u) {
+                const int i = tid + 128 * u;
+                if (i < chunks) {
+                    const int row = i / (D / 8), c8 = i % (D / 8);
+                    const uint32_t words[4] = {fetched[u].x, fetched[u].y, fetched[u].z, fetched[u].w};
+                    float4* dst = reinterpret_cast<float4*>(tile + row * kTileStride<D> + 8 * c8);
+                    dst[0] = make_float4(__uint_as_float(words[0] << 16), __uint_as_float(words[0] & 0xffff0000u),
+                                         __uint_as_float(words[1] << 16), __uint_as_float(words[1] & 0xffff0000u));
+                    dst[1] = make_float4(__uint_as_float(words[2] << 16), __uint_as_float(words[2] & 0xffff0000u),
+                                         __uint_as_float(words[3] << 16), __uint_as_float(words[3] & 0xffff0000u));
                 }
             }
-            float4* dst = reinterpret_cast<float4*>(tile + row * kTileStride<D> + 8 * c8);
-            dst[0] = make_float4(values[0], values[1], values[2], values[3]);
-            dst[1] = make_float4(values[4], values[5], values[6], values[7]);
         }
+        if (step + 1 < tiles && first + 16 < p.num_tokens) fetch(first + 16);
         __syncthreads();
         // rotate in place: warp w takes the 16-row tiles w, w + 4, ... (one per record in a four-record group)
         const int g = lane >> 2, t = lane & 3;
@@ -868,7 +891,8 @@ cudaError_t launch_dense_planes(QuantizeParams p, int head_dim, bool headline, i
     p.plane_first = first;
     p.dense_planes = count;
     // short (decode-sized) writes: one tile per CTA, so that the few tokens spread over as many SMs as possible
-    p.dense_tiles = p.num_tokens <= 1024 ? 1 : kDenseTiles;
+    // long writes: the matrix is staged once per CTA, so more tiles per CTA as long as the grid keeps several waves
+    p.dense_tiles = p.num_tokens <= 1024 ? 1 : p.num_tokens <= 4096 ? kDenseTiles : 2 * kDenseTiles;
     if (headline && p.group[0] == 32)
         return head_dim == 128 ? launch_dense<128, Anchor2224<32>>(p, stream) : launch_dense<96, Anchor2224<32>>(p, stream);
     if (headline && p.group[0] == 16)
