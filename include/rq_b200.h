@@ -223,7 +223,7 @@ int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32
  * sizes its work list the same way). */
 int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads);
 /* Bytes of scratch one rq_attention call needs: per-work-item (max, denominator, value sums), one arrival
- * counter per (row, head), a status word and room for the densely rotated query rows.  num_splits as in
+ * counter per (row, head) and a status word.  num_splits as in
  * RqAttentionArgs (0 = sized for rq_attention_work_capacity()).  The reference allocates the equivalent per call
  * (attention/launch.cuh:85-98). */
 size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32_t head_dim, int32_t num_splits);

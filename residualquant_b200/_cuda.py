@@ -86,7 +86,7 @@ def _rotation_arg(rotation, device, heads: int, head_dim: int, keep: list) -> _l
         )
         structured = lookup(rotation)
         if structured is None:
-            # an arbitrary learned rotation: rotated by a tensor-core launch from the dense matrix
+            # an arbitrary learned rotation: the kernels rotate with the dense matrix itself (fused, no extra launch)
             _require(rotation.data_ptr() % 16 == 0, "16-byte aligned rotation required")
             keep.append(rotation)
             out.kind = _lib.ROTATION_DENSE_FP16

@@ -27,7 +27,6 @@ UNITS = {
     "rq_attention.cu": [],
     "rq_attention_d128.cu": [],
     "rq_attention_d96.cu": [],
-    "rq_rotate.cu": [],
     "rq_peer.cu": [],
     "rq_capi.cu": [],
 }

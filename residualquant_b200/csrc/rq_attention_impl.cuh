@@ -414,14 +414,43 @@ __device__ __forceinline__ void accumulate_record(uint32_t base, int t, int js, 
     }
 }
 
+// Dense learned key rotation: this warp's share of q @ R[head] for the CTA's query row -- k in [warp D/4, (warp + 1) D/4),
+// lane L owning output channels 4L .. 4L+3 -- into parts[warp][D].  bf16 query entries times fp16 matrix entries are
+// exact in binary32 and the sums are binary32, like the reference's TF32 product with fp32 accumulation
+// (plugins/residual_quantization/csrc/attention/prepare.cuh:61-145); only the order of the sum differs.  A row of R[head]
+// is D contiguous halves, so each of the D/4 loads of a warp is one coalesced 2D-byte line from L2 (every CTA of the
+// head reads the same matrix); no separate rotation launch, no scratch.
+template <int D>
+__device__ __forceinline__ void rotate_query_dense(const AttentionParams& p, int row, int head, float* parts) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kShare = D / kWarps;   // 32 or 24 values of k per warp
+    const __nv_bfloat16* q = p.query + static_cast<int64_t>(row) * p.query_stride + head * D + warp * kShare;
+    const float mine = lane < kShare ? __bfloat162float(q[lane]) : 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool owner = 4 * lane < D;
+    const __half* r = p.query_matrix + (static_cast<int64_t>(head) * D + warp * kShare) * D + (owner ? 4 * lane : 0);
+#pragma unroll 8
+    for (int k = 0; k < kShare; ++k) {
+        const float qk = __shfl_sync(kFullMask, mine, k);   // every lane takes part in the shuffle
+        if (owner) {
+            const uint2 packed = __ldg(reinterpret_cast<const uint2*>(r + k * D));
+            const float2 lo = __half22float2(as_half2(packed.x)), hi = __half22float2(as_half2(packed.y));
+            acc[0] += qk * lo.x; acc[1] += qk * lo.y; acc[2] += qk * hi.x; acc[3] += qk * hi.y;
+        }
+    }
+    if (owner) *reinterpret_cast<float4*>(parts + warp * D + 4 * lane) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 // Rotated, pre-scaled query of this (row, head) into shared memory: qs[c] = (q @ R)[c] * D^-1/2 * log2(e).
 // Executed by warp 0; lane L owns channels 4L .. 4L+3.
 // Also computes the score of the live token (its K row is the raw bf16 input, original coordinates):
 // live = q.k * D^-1/2 * log2(e) - sum_c qs[c] * mean[loop][c]; the history scores leave out the same q.mean[loop]
 // constant (reference: prepare.cuh:229).
+// `dense_parts`: with a dense key rotation, the four warps' partial sums of q @ R (float [kWarps][D], see
+// rotate_query_dense) that this warp adds up.
 template <int D, bool MEAN>
 __device__ __forceinline__ void prepare_query(const AttentionParams& p, int row, int head, float* qs, float* qmax_out,
-                                              float* live_out) {
+                                              float* live_out, const float* dense_parts) {
     const int lane = threadIdx.x & 31;
     float x[4] = {0.f, 0.f, 0.f, 0.f};
     float live_dot = 0.f;
@@ -439,12 +468,16 @@ __device__ __forceinline__ void prepare_query(const AttentionParams& p, int row,
                    x[2] * bf16_bits_to_float(live.y & 0xffffu) + x[3] * bf16_bits_to_float(live.y >> 16);
     }
     float scale = rsqrtf(static_cast<float>(D)) * kLog2e;
-    if (p.rotated_query != nullptr) {
-        // dense learned rotation: q @ R was computed by rotate_rows_kernel
+    if (p.query_matrix != nullptr) {
+        // dense learned rotation: the CTA's warps each summed a quarter of the k range
         if (owner) {
-            const float4 v = *reinterpret_cast<const float4*>(
-                p.rotated_query + (static_cast<int64_t>(row) * p.heads + head) * D + 4 * lane);
-            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[i] = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float4 v = *reinterpret_cast<const float4*>(dense_parts + w * D + 4 * lane);
+                x[0] += v.x; x[1] += v.y; x[2] += v.z; x[3] += v.w;
+            }
         }
     } else if (p.key_sign != nullptr) {
         if (owner) {
@@ -893,7 +926,11 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
 
     // ---- query: rotate + scale (warp 0), then every lane takes its 32-channel slice -------------------
     float* misc = warp_stat + 8;         // [0] last-arrival flag, [1] live score, [2] max |q|
-    if (warp == 0) prepare_query<D, C::kMean>(p, row, head, qs, misc + 2, misc + 1);
+    if (p.query_matrix != nullptr) {
+        rotate_query_dense<D>(p, row, head, warp_acc);   // all four warps; warp_acc is free until the warp fold
+        __syncthreads();
+    }
+    if (warp == 0) prepare_query<D, C::kMean>(p, row, head, qs, misc + 2, misc + 1, warp_acc);
     if (warp == 1 && lane < D / 64) {
         // the live token's V row is read at the very end of the CTA: have it in L2 by then
         const __nv_bfloat16* v_row = p.value + static_cast<int64_t>(row) * p.value_stride + head * D + 64 * lane;
@@ -1287,14 +1324,15 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         // ticket.  The CTA that draws the last ticket has thereby observed every other CTA's fence; its own system-scope
         // fence followed by the release stores of the flag extends that order to the peers (causality order composes
         // across scopes), so a peer that has acquired the flag sees every row of the call.
-        uint32_t* published = reinterpret_cast<uint32_t*>(misc);  // [0]: the epoch this CTA published, 0 if it was not the last
+        uint32_t* published = reinterpret_cast<uint32_t*>(misc);  // [0]: the epoch this CTA published, [3]: whether it did
         __syncthreads();
         if (tid == 0) {
             __threadfence();
             const uint32_t ticket = atomicAdd(p.gather_state + 2, 1u);
             const uint32_t total_rows = static_cast<uint32_t>(min(__ldcg(p.query_start_loc + p.num_requests), p.num_rows));
             uint32_t epoch = 0u;
-            if (ticket + 1u == total_rows * static_cast<uint32_t>(heads)) {
+            const bool last = ticket + 1u == total_rows * static_cast<uint32_t>(heads);
+            if (last) {
                 p.gather_state[2] = 0u;  // ready for the next call
                 __threadfence_system();
                 epoch = *reinterpret_cast<volatile uint32_t*>(p.gather_state) + 1u;
@@ -1303,14 +1341,14 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather_flags[peer] + p.gather_rank), "r"(epoch) : "memory");
             }
             published[0] = epoch;
+            published[3] = last ? 1u : 0u;
         }
         if (p.gather_complete) {
             // ... and stays until every peer's signal of the same call is here: the launch then ends only when this GPU's
             // gathered buffer is complete.  The peers' kernels run on their own GPUs whatever this one does, so the wait
             // cannot block them; it is bounded all the same.
             __syncthreads();
-            const uint32_t epoch = published[0];
-            if (epoch != 0u && warp == 0 && lane < p.num_peers) wait_for_peers(p, lane, epoch);
+            if (published[3] != 0u && warp == 0 && lane < p.num_peers) wait_for_peers(p, lane, published[0]);
         }
     }
 }

@@ -307,8 +307,7 @@ size_t rq_attention_workspace_bytes(int32_t num_query_rows, int32_t heads, int32
     const size_t counters = counter_bytes(num_query_rows, heads);
     const size_t partials =
         num_splits != 1 ? work_items(num_query_rows, heads, num_splits) * heads * (head_dim + 2) * sizeof(float) : 0;
-    const size_t rotated_query = round_up(static_cast<size_t>(num_query_rows) * heads * head_dim * sizeof(float), 256);
-    return kStatusBytes + counters + round_up(partials, 256) + rotated_query;
+    return kStatusBytes + counters + round_up(partials, 256);
 }
 
 int32_t rq_attention_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -443,33 +442,13 @@ int32_t rq_attention(const RqAttentionArgs* a) {
     p.sm_count = current_sm_count();
     p.programmatic_launch = programmatic_launch_enabled() && !(a->flags & RQ_FLAG_SERIAL_LAUNCH) ? 1 : 0;
     const bool just_written = take_recent_write(a->stream, a->kv_cache);
-    // the dense query rotation launches a kernel of its own in front: the early start would overlap THAT kernel
-    p.early_start = p.programmatic_launch && (a->flags & RQ_FLAG_STABLE_METADATA) && !just_written &&
-                    a->key_rotation.kind != RQ_ROTATION_DENSE_FP16 ? 1 : 0;
+    p.early_start = p.programmatic_launch && (a->flags & RQ_FLAG_STABLE_METADATA) && !just_written ? 1 : 0;
     uint8_t* base = static_cast<uint8_t*>(a->workspace);
     p.status = reinterpret_cast<int32_t*>(base);
     p.counters = reinterpret_cast<int32_t*>(base + kStatusBytes);
     p.partials = reinterpret_cast<float*>(base + kStatusBytes + counter_bytes(a->num_query_rows, s.heads));
-    if (a->key_rotation.kind == RQ_ROTATION_DENSE_FP16) {
-        // q @ R on the tensor cores, once per call, into the tail of the workspace
-        const size_t partial_bytes =
-            splits != 1 ? work_items(a->num_query_rows, s.heads, splits) * s.heads * (s.head_dim + 2) * sizeof(float) : 0;
-        float* rotated = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.partials) + round_up(partial_bytes, 256));
-        rq::RotateParams rp;
-        memset(&rp, 0, sizeof(rp));
-        rp.source[0] = p.query;
-        rp.source_stride[0] = p.query_stride;
-        rp.num_sources = 1;
-        rp.matrix = static_cast<const __half*>(a->key_rotation.data);
-        rp.output = rotated;
-        rp.slots = nullptr;
-        rp.num_rows = a->num_query_rows;
-        rp.heads = s.heads;
-        rp.scale = 1.f;
-        const cudaError_t rerr = rq::launch_rotate(rp, s.head_dim, static_cast<cudaStream_t>(a->stream));
-        if (rerr != cudaSuccess) return fail_cuda(rerr, "query rotation launch");
-        p.rotated_query = rotated;
-    }
+    // a dense key rotation is applied to the query row inside the attention kernel's prologue
+    if (a->key_rotation.kind == RQ_ROTATION_DENSE_FP16) p.query_matrix = static_cast<const __half*>(a->key_rotation.data);
     if (a->value_rotation.kind == RQ_ROTATION_DENSE_FP16) p.value_matrix = static_cast<const __half*>(a->value_rotation.data);
     if (a->num_peers != 0) {
         if (a->num_peers < 0 || a->num_peers > RQ_MAX_PEERS)

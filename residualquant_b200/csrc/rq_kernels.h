@@ -37,19 +37,6 @@ struct QuantizeParams {
     int programmatic_launch;  // launch with the programmatic-stream-serialization attribute
 };
 
-// y = x @ R for bf16 rows and a dense fp16 matrix per head (TF32 tensor-core products, fp32 accumulation).
-struct RotateParams {
-    const __nv_bfloat16* source[RQ_MAX_RECORDS];
-    int64_t source_stride[RQ_MAX_RECORDS];
-    int num_sources;
-    const __half* matrix;     // [heads][head_dim][head_dim]
-    float* output;            // [num_sources][num_rows][heads][head_dim]
-    const int64_t* slots;     // optional [num_rows]: rows with a negative slot are not read (output zeros)
-    int num_rows, heads;
-    float scale;
-};
-cudaError_t launch_rotate(const RotateParams& p, int head_dim, cudaStream_t stream);
-
 cudaError_t launch_quantize(const QuantizeParams& p, int head_dim, cudaStream_t stream);
 
 // Layout of the attention workspace (all offsets multiples of 256 bytes):
@@ -73,7 +60,7 @@ struct AttentionParams {
     const uint32_t* key_sign;    // signed-Hadamard key rotation or nullptr
     const uint32_t* value_sign;  // explicit value rotation (undone on the history sum) or nullptr
     float key_rscale, value_rscale;
-    const float* rotated_query;  // dense key rotation: q @ R already computed, fp32 [rows][heads][head_dim]; else nullptr
+    const __half* query_matrix;  // dense key rotation: fp16 [heads][head_dim][head_dim], q @ R is formed in the prologue; else nullptr
     const __half* value_matrix;  // dense explicit value rotation [heads][head_dim][head_dim]; else nullptr
     const float* mean;           // [records][heads][head_dim] or nullptr
     int heads, page_width;

@@ -58,11 +58,10 @@ def test_workspace_size_and_split_heuristic(built_library):
     lib = _lib.load()
     one = lib.rq_attention_workspace_bytes(64, 16, 128, 1)
     four = lib.rq_attention_workspace_bytes(64, 16, 128, 4)
-    rotated_query = 64 * 16 * 128 * 4
-    assert one == 256 + 65536 + rotated_query and four == one + 64 * 16 * 4 * 130 * 4
+    assert one == 256 + 65536 and four == one + 64 * 16 * 4 * 130 * 4
     # the counter region is shape-independent up to 16384 (row, head) pairs, then the next power of two
-    assert lib.rq_attention_workspace_bytes(1, 1, 128, 1) == 256 + 65536 + 512
-    assert lib.rq_attention_workspace_bytes(2048, 16, 128, 1) == 256 + 131072 + 2048 * 16 * 128 * 4
+    assert lib.rq_attention_workspace_bytes(1, 1, 128, 1) == 256 + 65536
+    assert lib.rq_attention_workspace_bytes(2048, 16, 128, 1) == 256 + 131072
     assert four % 256 == 0
     # num_splits 0: sized for the work capacity, which depends on rows, heads and the SM count only (148 without a GPU)
     capacity = lib.rq_attention_work_capacity(64, 16)

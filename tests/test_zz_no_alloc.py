@@ -130,7 +130,7 @@ def test_noalloc_entry_reports_a_bad_spec_as_such():
 
 
 def test_noalloc_entry_with_a_dense_key_rotation():
-    """A dense (learned) key rotation makes the call use the tail of the built-in buffer for the rotated query rows."""
+    """A dense (learned) key rotation: the query row is rotated inside the attention kernel, no extra scratch."""
     from residualquant_b200 import _lib
 
     lib = _lib.load()
