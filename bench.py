@@ -51,6 +51,7 @@ import numpy as np  # noqa: E402
 METRIC = "decode_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+DENSE_ROTATION = False   # --dense-rotation: the stacks hand the operators a dense fp16 matrix
 REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 
 
@@ -97,6 +98,9 @@ def parse_args():
                         "all-gather per call, eager")
     p.add_argument("--splits", type=int, default=0,
                    help="force the number of KV partitions per row (0 = the kernel picks them per row from the lengths)")
+    p.add_argument("--dense-rotation", action="store_true",
+                   help="give the operators the key rotation as a dense fp16 matrix (the path of a learned rotation) "
+                        "instead of the registered signed-Hadamard structure")
     p.add_argument("--quick", action="store_true",
                    help="only the headline numbers: no sweep, other shapes, comparators or CPU baseline")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -280,6 +284,7 @@ def workload_config(args, shape):
         "workload": f"config1 kernel sweep point: batch {shape.batch} x context {shape.context}, INT2 g{shape.group} "
                     f"residuals + INT4 g32 anchor, {shape.layers} layers x 4 loops, {shape.heads} heads x {shape.head_dim}, "
                     f"block {shape.page}, CUDA-graph decode step (4 attention + 1 quantize launch per layer)"
+                    + ("; key rotation given as a dense fp16 matrix" if args.dense_rotation else "")
                     + ("" if args.shard != "heads" else
                        "; KV heads sharded over the ranks, output rows stored into every GPU's gathered buffer by the attention "
                        "kernel, captured in the graph" if args.gather != "nccl" else
@@ -363,6 +368,9 @@ class Stack:
         pool = rng.permutation(num_blocks - 1) + 1          # block 0 stays unused, like vLLM's null block
         self.block_table = torch.from_numpy(pool.reshape(shape.batch, blocks_per_seq).astype(np.int32)).to(device)
         self.key_rot = rotation.signed_hadamard(synth.signs(rng, heads, D), float(synth.fp16_rsqrt(D)), device)
+        # what the operators are given: the registered structure (fused Walsh-Hadamard transform), or with --dense-rotation
+        # the same rotation as a plain fp16 [heads, D, D] matrix, which takes the learned-rotation path of both kernels
+        self.rotation = self.key_rot.dense() if DENSE_ROTATION else self.key_rot
 
         gen = torch.Generator(device=device)
         gen.manual_seed(99 + seed_offset)
@@ -387,7 +395,7 @@ class Stack:
             k, v = rows(shape.context), rows(shape.context)
             # The model's weights absorb the value rotation in the served configuration (weights.py:9-37 of the
             # reference), so the kernels see value_rotation=None and V arrives rotated.
-            _cuda.quantize(list(zip(k, v)), self.caches[0], slots, self.key_rot, None, None, self.records, "anchor", 3, "ls")
+            _cuda.quantize(list(zip(k, v)), self.caches[0], slots, self.rotation, None, None, self.records, "anchor", 3, "ls")
         torch.cuda.synchronize(device)
         for _ in range(1, shape.layers):
             self.caches.append(self.caches[0].clone())
@@ -416,14 +424,14 @@ class Stack:
         rows = self.shape.batch if rows is None else rows
         _cuda.attention(self.q[layer, loop, :rows], self.k_live[layer, loop, :rows], self.v_live[layer, loop, :rows],
                         self.caches[layer], self.out[layer, loop, :rows], self.qsl if qsl is None else qsl,
-                        self.seq_lens if seq_lens is None else seq_lens, self.block_table[:rows], self.key_rot, None, None,
+                        self.seq_lens if seq_lens is None else seq_lens, self.block_table[:rows], self.rotation, None, None,
                         self.records, "anchor", 3, loop, **extra)
 
     def quantize(self, layer):
         from residualquant_b200 import _cuda
 
         _cuda.quantize([(self.k_live[layer, i], self.v_live[layer, i]) for i in range(4)], self.caches[layer],
-                       self.slot_mapping, self.key_rot, None, None, self.records, "anchor", 3, "ls")
+                       self.slot_mapping, self.rotation, None, None, self.records, "anchor", 3, "ls")
 
 
 class Timer:
@@ -508,7 +516,7 @@ def kernel_figures(timer, stack, peak, reps):
     positions = torch.arange(shape.context, device=stack.device)
     slots = torch.cat([stack.block_table[b, positions // shape.page].long() * shape.page + positions % shape.page
                        for b in range(prompts)])
-    ms = timer.graph_ms(lambda: _cuda.quantize(list(zip(pk, pv)), stack.caches[0], slots, stack.key_rot, None, None,
+    ms = timer.graph_ms(lambda: _cuda.quantize(list(zip(pk, pv)), stack.caches[0], slots, stack.rotation, None, None,
                                                stack.records, "anchor", 3, "ls"), 5)
     nbytes = quantize_bytes(tokens, sized)
     out["quantize_prefill_write"] = {"tokens": tokens, "us_per_launch": 1000 * ms, "achieved": nbytes / (ms * 1e-3) / 1e9,
@@ -557,7 +565,7 @@ def decode_step_figures(timer, stack, reps):
                 for loop in range(4):
                     stack.attention(layer, loop, 1, lens, starts)
                 _cuda.quantize([(stack.k_live[layer, i, :1], stack.v_live[layer, i, :1]) for i in range(4)],
-                               stack.caches[layer], slot, stack.key_rot, None, None, stack.records, "anchor", 3, "ls")
+                               stack.caches[layer], slot, stack.rotation, None, None, stack.records, "anchor", 3, "ls")
         ms = timer.graph_ms(step, reps)
         out.append({"batch": 1, "context": context, "ms_per_step": round(ms, 4), "tokens_per_s": round(1000.0 / ms, 1),
                     "launches": 5 * shape.layers})
@@ -838,13 +846,13 @@ def model_decode_figures(timer, torch, device, batch=32, prompt=2048, generated=
     def packed_attention(layer, loop, q, k, v):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         out = outputs[layer, loop]
-        _cuda.attention(q, k, v, stack.caches[layer], out, stack.qsl, stack.seq_lens, stack.block_table, stack.key_rot, None,
+        _cuda.attention(q, k, v, stack.caches[layer], out, stack.qsl, stack.seq_lens, stack.block_table, stack.rotation, None,
                         None, stack.records, "anchor", 3, loop)
         pending[layer].append((k, v))
         return out
 
     def packed_end_of_layer(layer):
-        _cuda.quantize(pending[layer], stack.caches[layer], stack.slot_mapping, stack.key_rot, None, None, stack.records,
+        _cuda.quantize(pending[layer], stack.caches[layer], stack.slot_mapping, stack.rotation, None, None, stack.records,
                        "anchor", 3, "ls")
         pending[layer].clear()
 
@@ -1125,8 +1133,9 @@ def emit(line: dict) -> None:
 
 
 def main():
-    global _result_stream
+    global _result_stream, DENSE_ROTATION
     args = parse_args()
+    DENSE_ROTATION = args.dense_rotation
     shape = Shape(batch=args.batch, context=args.context, layers=args.layers, heads=args.heads, head_dim=args.head_dim,
                   page=args.page, group=args.group)
     # Libraries print to file descriptor 1 on their own (NCCL announces its version there): keep the real standard
