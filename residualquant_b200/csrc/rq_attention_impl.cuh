@@ -714,7 +714,7 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
         const int mine = max(4, ceil_div_small(longest, lane + 1));
         const int parts = max(1, ceil_div_small(longest, mine));
         float cost = cost_of(total_rows * parts, static_cast<float>(min(mine, longest)));
-        cost *= 1.f + 0.01f * __log2f(static_cast<float>(parts));  // near ties go to fewer partitions
+        cost *= 1.f + 0.04f * __log2f(static_cast<float>(parts));  // near ties go to fewer partitions (measured: they win them)
         uint32_t key = (__float_as_uint(cost) & ~31u) | static_cast<uint32_t>(lane);
         if (total_rows * parts > p.capacity && lane > 0) key = 0xffffffffu;  // does not fit the grid (one partition always does)
         const int chosen = static_cast<int>(__reduce_min_sync(kFullMask, key) & 31u);
@@ -1067,6 +1067,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
                 if (raise) m_biased = score - kWeightBits;
             }
             const float prob = live_token ? fast_exp2(score - m_biased) : 0.f;
+            const float l_before = l;
             l += prob;
 
             // ---------------- V: accumulate prob * V_hat[t] over the slice ----------------
@@ -1099,7 +1100,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             // its own value row behind; every later add would be rounded at THAT magnitude (an 11-bit significand: a
             // value of 30 costs 0.007 per add).  Such tokens are rare; the page loop moves the sums to fp32 right after
             // the page of one.
-            if (prob > 0.5f * l) pages_to_flush = 0;
+            if (prob > l_before) pages_to_flush = 0;   // more than half of the stream's mass so far
         }
     };
 
