@@ -269,3 +269,50 @@ def test_one_workspace_serves_calls_of_different_shapes():
         assert _inside(got, caches["small"][1]), f"small call, round {round_}"
         got = G.gpu_attention(large, caches["large"][0], 0).float().cpu().numpy()
         assert _inside(got, caches["large"][1]), f"large call, round {round_}"
+
+
+@pytest.mark.parametrize("seed,requests,equal", [(1, 7, False), (2, 70, False), (3, 150, False), (4, 33, True), (5, 130, True)])
+def test_random_batches_with_several_rows_per_request(seed, requests, equal):
+    """The work lookup on batches the other tests do not reach: 0 to 3 query rows per request (a request without rows must
+    cost no work item, several rows share their request's history), more than 64 and more than 128 requests (second and
+    third sweep of the lookup), and batches of equal lengths (the partition count is then chosen without sums over the
+    requests).  Every row must come out as with one forced partition per row, which the other tests pin to the oracle."""
+    from residualquant_b200 import _cuda
+
+    rng = np.random.default_rng(100 + seed)
+    if equal:
+        lengths = [int(rng.integers(40, 900))] * requests
+    else:
+        lengths = [int(v) for v in rng.integers(1, 500, size=requests)]
+        lengths[int(rng.integers(requests))] = 3000
+    case = helpers.make_case(60 + seed, 128, 2, lengths, 32, 16)
+    cache = torch.from_numpy(helpers.oracle_cache(case)).cuda()
+    rows_of = rng.integers(0, 4, size=requests) if not equal else np.full(requests, 2)
+    rows_of[0] = max(rows_of[0], 1)
+    starts = np.concatenate([[0], np.cumsum(rows_of)]).astype(np.int32)
+    total = int(starts[-1])
+    L = case.layout
+    kr, vr = G.device_rotations(case)
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(total, 2, 128, device="cuda", generator=gen).bfloat16()
+    k = torch.randn(total, 2, 128, device="cuda", generator=gen).bfloat16()
+    v = torch.randn(total, 2, 128, device="cuda", generator=gen).bfloat16()
+    qsl = torch.from_numpy(starts).cuda()
+    seq = torch.from_numpy(case.seq_lens).cuda()
+    table = torch.from_numpy(case.block_table).cuda()
+    outputs = {}
+    for splits in (0, 1, -8):
+        _cuda.set_attention_splits(splits)
+        try:
+            out = torch.full_like(q, 768.0)
+            _cuda.attention(q, k, v, cache, out, qsl, seq, table, kr, vr, None, [list(r) for r in L.records],
+                            L.reference_mode, L.anchor_index, 1)
+            torch.cuda.synchronize()
+            _cuda.attention_status("cuda")
+            outputs[splits] = out.float().cpu().numpy()
+        finally:
+            _cuda.set_attention_splits(0)
+    want = outputs[1]
+    assert np.all(np.abs(want) < 700.0), "every row was written"
+    for splits in (0, -8):
+        assert _inside(outputs[splits], want), f"num_splits {splits}: {np.abs(outputs[splits] - want).max()}"
