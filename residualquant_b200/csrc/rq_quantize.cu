@@ -573,25 +573,27 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
 }
 
 // The staged matrix is stored in the order the MMA's B fragments are consumed, so that a lane fetches the fragments of
-// two adjacent 8-column tiles with one 16-byte load: float4 index ((k / 8) * (D / 16) + n / 2) * 32 + lane holds
+// two adjacent 8-column tiles with one 8-byte load: entry ((k / 8) * (D / 16) + n / 2) * 32 + lane holds the four halves
 // {R[k0][8n+g], R[k0+1][8n+g], R[k0][8(n+1)+g], R[k0+1][8(n+1)+g]} with k0 = k - k % 8 + 2 * (lane % 4), g = lane / 4.
 // (Rows k0, k0 + 1 are the k-indices "t" and "t + 4" of the MMA: the product does not care which physical row carries
-// which index as long as the A fragment uses the same assignment.)
+// which index as long as the A fragment uses the same assignment.)  It stays fp16 in shared memory -- half the bytes of
+// a binary32 copy, which is what lets three CTAs share an SM instead of two -- and is widened (exactly) when a fragment
+// is loaded: two conversions per MMA on a kernel whose issue slots are two thirds idle.
 template <int D>
-constexpr int kMatrixFloats = D * D;
+constexpr int kMatrixFloats = D * D;   // entries
 
 template <int D>
 size_t dense_shared_bytes(int num_records) {
-    return (static_cast<size_t>(kMatrixFloats<D>) + static_cast<size_t>(num_records) * 16 * kTileStride<D>) * sizeof(float);
+    return static_cast<size_t>(kMatrixFloats<D>) * sizeof(__half) + static_cast<size_t>(num_records) * 16 * kTileStride<D> * sizeof(float);
 }
 
 template <int D, class S>
-__global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_constant__ QuantizeParams p) {
+__global__ void __launch_bounds__(128, 3) quantize_dense_kernel(const __grid_constant__ QuantizeParams p) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(16) float dense_shared[];
-    float* matrix = dense_shared;                     // fragment order, see kMatrixFloats
-    float* tile = dense_shared + kMatrixFloats<D>;    // [records * 16][kTileStride]
+    uint2* matrix = reinterpret_cast<uint2*>(dense_shared);   // fp16, fragment order, see kMatrixFloats
+    float* tile = dense_shared + kMatrixFloats<D> / 2;        // [records * 16][kTileStride]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head = blockIdx.y, plane = p.plane_first + blockIdx.z;
     const int num_records = [&] { if constexpr (S::kFixed) return S::kRecords; else return p.num_records; }();
@@ -604,9 +606,9 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
         return;
     }
 
-    // R[h]: fp16 [D][D] -> fp32 in shared memory, in fragment order.  A warp fills one block of 32 float4 (the B fragments
-    // of one k-step and one pair of 8-column tiles) per round: every lane gathers its own four entries -- two rows, two
-    // column tiles -- and stores one float4, so the stores are contiguous over the warp (no bank conflict); the 2-byte
+    // R[h]: fp16 [D][D] -> shared memory, in fragment order.  A warp fills one block of 32 entries (the B fragments of one
+    // k-step and one pair of 8-column tiles) per round: every lane gathers its own four halves -- two rows, two column
+    // tiles -- and stores them as 8 bytes, so the stores are contiguous over the warp (no bank conflict); the 2-byte
     // gathers hit L1/L2, every CTA of the head reads the same 2 D^2 bytes.
     {
         const unsigned short* r = reinterpret_cast<const unsigned short*>(p.dense_matrix[plane]) + static_cast<int64_t>(head) * D * D;
@@ -617,9 +619,7 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
             const int ks = block / (D / 16), pair = block % (D / 16);
             const unsigned short* from = r + (8 * ks + 2 * t) * D + 16 * pair + g;
             const unsigned short a0 = __ldg(from), a1 = __ldg(from + D), b0 = __ldg(from + 8), b1 = __ldg(from + D + 8);
-            reinterpret_cast<float4*>(matrix)[block * 32 + lane] =
-                make_float4(__half2float(__ushort_as_half(a0)), __half2float(__ushort_as_half(a1)),
-                            __half2float(__ushort_as_half(b0)), __half2float(__ushort_as_half(b1)));
+            matrix[block * 32 + lane] = make_uint2(a0 | (static_cast<uint32_t>(a1) << 16), b0 | (static_cast<uint32_t>(b1) << 16));
         }
     }
     const __nv_bfloat16* const* sources = plane == 0 ? p.key : p.value;
@@ -685,7 +685,7 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
             for (int n = 0; n < D / 8; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-            const float4* fragments = reinterpret_cast<const float4*>(matrix) + lane;
+            const uint2* fragments = matrix + lane;
 #pragma unroll 2
             for (int k = 0; k < D; k += 8) {
                 // physical columns k + 2t, k + 2t + 1 of the rows play the k-indices t, t + 4
@@ -695,9 +695,11 @@ __global__ void __launch_bounds__(128, 2) quantize_dense_kernel(const __grid_con
                                        __float_as_uint(lower.y)};
 #pragma unroll
                 for (int n = 0; n < D / 8; n += 2) {
-                    const float4 f = fragments[((k >> 3) * (D / 16) + (n >> 1)) * 32];
-                    const uint32_t b0[2] = {__float_as_uint(f.x), __float_as_uint(f.y)};
-                    const uint32_t b1[2] = {__float_as_uint(f.z), __float_as_uint(f.w)};
+                    const uint2 packed = fragments[((k >> 3) * (D / 16) + (n >> 1)) * 32];
+                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&packed.x));
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&packed.y));
+                    const uint32_t b0[2] = {__float_as_uint(f0.x), __float_as_uint(f0.y)};
+                    const uint32_t b1[2] = {__float_as_uint(f1.x), __float_as_uint(f1.y)};
                     mma_tf32(acc[n], a, b0);
                     mma_tf32(acc[n + 1], a, b1);
                 }
