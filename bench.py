@@ -249,8 +249,12 @@ def cpu_port(shape: Shape, sample_context=1024, seed=0):
 
 
 def cpu_baseline(shape: Shape, steps=3, warmup=1):
+    """The reference's own PyTorch statement when its files are there (and run); else the numpy port."""
     if reference_python_available():
-        return cpu_reference(shape, steps, warmup)
+        try:
+            return cpu_reference(shape, steps, warmup)
+        except Exception as error:   # noqa: BLE001 -- e.g. the files do not import under this torch: time the port instead
+            print(f"reference PyTorch path failed ({type(error).__name__}: {error}); timing the numpy port", file=sys.stderr)
     return cpu_port(shape)
 
 
@@ -1035,22 +1039,34 @@ def run_gpu(args, shape):
     _cuda.attention_status(device)
 
     extras = {}
+
+    def side(name, measure):
+        """A side measurement must never cost the result line: on an error its entry says what went wrong."""
+        try:
+            figures = measure()
+        except Exception as error:   # noqa: BLE001 -- anything: the headline figures above are already measured
+            figures = {"error": f"{type(error).__name__}: {error}"[:300]}
+            try:
+                torch.cuda.synchronize(device)
+            except Exception as later:   # noqa: BLE001
+                figures["error"] += f"; then {later}"[:200]
+        if figures is not None:
+            extras[name] = figures
+
     full = not args.quick and not shard_heads
     if full and rank == 0 and world == 1:
         # Only the single-GPU run carries the side measurements; a multi-GPU launch reports scaling.
-        extras["sweep"] = sweep_figures(timer, stack, peak, reps)
-        extras["decode_step_batch1"] = decode_step_figures(timer, stack, reps)
-        ragged = ragged_figures(timer, stack, peak, reps, {"residual_loop": residual["us_per_launch"],
-                                                            "anchor_loop": anchor["us_per_launch"]})
-        if ragged is not None:
-            extras["ragged"] = ragged
+        side("sweep", lambda: sweep_figures(timer, stack, peak, reps))
+        side("decode_step_batch1", lambda: decode_step_figures(timer, stack, reps))
+        side("ragged", lambda: ragged_figures(timer, stack, peak, reps, {"residual_loop": residual["us_per_launch"],
+                                                                        "anchor_loop": anchor["us_per_launch"]}))
         packed_layer_ms = (3 * residual["us_per_launch"] + anchor["us_per_launch"]
                            + kernels["quantize_decode_write"]["us_per_launch"]) / 1000.0
-        extras["reference_cuda"] = reference_cuda_figures(timer, stack)
+        side("reference_cuda", lambda: reference_cuda_figures(timer, stack))
         if shape.batch * shape.heads * shape.context * shape.head_dim * 16 < 40e9:
-            extras["bf16_kv_comparator"] = bf16_comparator(timer, stack, packed_layer_ms)
+            side("bf16_kv_comparator", lambda: bf16_comparator(timer, stack, packed_layer_ms))
     if full and world > 1:
-        # every rank takes part; rank 0 reports
+        # every rank takes part; rank 0 reports.  (Not wrapped: a rank that skipped a collective would hang the others.)
         del stack
         stack = None
         torch.cuda.empty_cache()
@@ -1059,20 +1075,23 @@ def run_gpu(args, shape):
         del stack
         stack = None
         torch.cuda.empty_cache()
-        other = {}
-        for name, variant in (("g16", replace(shape, group=16, layers=min(4, layers))),
-                              ("huginn_55x96", Shape(batch=16, context=4096, layers=8, heads=55, head_dim=96, page=16, group=32))):
-            s = Stack(variant, device, torch, seed_offset=17)
-            figures = kernel_figures(timer, s, peak, 3)
-            figures["shape"] = (f"batch {variant.batch} x context {variant.context}, {variant.heads} heads x "
-                                f"{variant.head_dim}, g{variant.group}, {variant.layers} layers")
-            other[name] = figures
-            del s
-            torch.cuda.empty_cache()
-        extras["other_shapes"] = other
+        def other_shapes():
+            other = {}
+            for name, variant in (("g16", replace(shape, group=16, layers=min(4, layers))),
+                                  ("huginn_55x96", Shape(batch=16, context=4096, layers=8, heads=55, head_dim=96, page=16, group=32))):
+                s = Stack(variant, device, torch, seed_offset=17)
+                figures = kernel_figures(timer, s, peak, 3)
+                figures["shape"] = (f"batch {variant.batch} x context {variant.context}, {variant.heads} heads x "
+                                    f"{variant.head_dim}, g{variant.group}, {variant.layers} layers")
+                other[name] = figures
+                del s
+                torch.cuda.empty_cache()
+            return other
+
+        side("other_shapes", other_shapes)
         # the one-GPU point of the head-sharded strong-scaling curve (same step, every head on this GPU)
-        extras["head_sharded"] = head_sharded_figures(timer, torch, dist, device, rank, world, args.steps, args.warmup)
-        extras["config2_model_decode"] = model_decode_figures(timer, torch, device)
+        side("head_sharded", lambda: head_sharded_figures(timer, torch, dist, device, rank, world, args.steps, args.warmup))
+        side("config2_model_decode", lambda: model_decode_figures(timer, torch, device))
 
     if rank != 0:
         if world > 1:
@@ -1113,7 +1132,10 @@ def run_gpu(args, shape):
     }
     line.update(extras)
     if not args.no_cpu_baseline and not args.quick:
-        _, line["cpu_baseline"], _ = cpu_baseline(shape)
+        try:
+            _, line["cpu_baseline"], _ = cpu_baseline(shape)
+        except Exception as error:   # noqa: BLE001 -- the line is printed whatever happens to the host-side leg
+            line["cpu_baseline"] = {"error": f"{type(error).__name__}: {error}"[:300]}
     emit(line)
     if world > 1:
         dist.destroy_process_group()
