@@ -6,7 +6,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIBRARY_PATH = os.path.join(HERE, "librq_b200.so")
+# RQ_B200_LIBRARY: another build of the same library (e.g. librq_b200_timeline.so, see build.py)
+LIBRARY_PATH = os.environ.get("RQ_B200_LIBRARY") or os.path.join(HERE, "librq_b200.so")
 
 RQ_MAX_RECORDS = 8
 RQ_MAX_PEERS = 8

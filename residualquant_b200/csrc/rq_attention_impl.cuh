@@ -582,6 +582,40 @@ __device__ __forceinline__ void unrotate_history(const AttentionParams& p, int h
     }
 }
 
+// ---- phase timestamps (build flag RQ_ATTENTION_TIMELINE=1; compiled out otherwise) ---------------------------
+// Where a small call's time goes cannot be read off a profiler's per-kernel counters: it is a chain of latencies inside
+// each CTA.  In a timeline build thread 0 of every CTA records clock64() at the phase boundaries below (and the global
+// timer at entry and exit) into a device array that rq_timeline_d128 / rq_timeline_d96 copy out; launches alternate
+// between two halves of the array by loop_index & 1, so that two consecutive launches can be laid side by side.
+// `python -m residualquant_b200.timeline` drives it.  The regular build has no trace of it.
+#ifndef RQ_ATTENTION_TIMELINE
+#define RQ_ATTENTION_TIMELINE 0
+#endif
+enum TimelineSlot {
+    kAtEntryGlobalNs = 0, kAtEntry, kAfterLookup, kAfterStaging, kAfterWait, kAfterQuery, kAfterPages, kAfterWarpFold,
+    kAfterTicket, kAfterPartitions, kAtExit, kAtExitGlobalNs, kLookupLoadsIssued, kLookupLoadsArrived, kLookupChosen,
+    kQueryRotated, kQueryShared, kTimelineSlots
+};
+constexpr int kTimelineCtas = 4096;
+#if RQ_ATTENTION_TIMELINE
+__device__ unsigned long long g_timeline[2][kTimelineCtas][kTimelineSlots];
+#define RQ_STAMP(slot)                                                                               \
+    do {                                                                                             \
+        if (threadIdx.x == 0 && blockIdx.x < kTimelineCtas) g_timeline[p.loop_index & 1][blockIdx.x][slot] = clock64(); \
+    } while (0)
+#define RQ_STAMP_GLOBAL(slot)                                                                        \
+    do {                                                                                             \
+        if (threadIdx.x == 0 && blockIdx.x < kTimelineCtas) {                                        \
+            unsigned long long now_ns;                                                               \
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now_ns));                                \
+            g_timeline[p.loop_index & 1][blockIdx.x][slot] = now_ns;                                 \
+        }                                                                                            \
+    } while (0)
+#else
+#define RQ_STAMP(slot) do {} while (0)
+#define RQ_STAMP_GLOBAL(slot) do {} while (0)
+#endif
+
 // ---- work decomposition ------------------------------------------------------------------------------------
 // A work item is one KV partition of one query row (all heads of it: the CTA index is item * heads + head).
 struct WorkItem {
@@ -688,6 +722,11 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
             for (int k = 0; k < kCandidates; ++k) counts[k] += q[u].rows * max(1, (q[u].pages + (4 << k) - 1) >> (k + 2));
         }
     };
+    RQ_STAMP(kLookupLoadsIssued);
+#if RQ_ATTENTION_TIMELINE
+    if (first[0].len + first[1].len + total_rows == -12345) return false;   // a use of the loaded values: they have arrived
+#endif
+    RQ_STAMP(kLookupLoadsArrived);
     tally(first);
     for (int base = 64; base < num_requests; base += 64) {
         Request more[2];
@@ -741,6 +780,10 @@ __device__ __forceinline__ bool find_work(const AttentionParams& p, int item, in
         const int spare = max(1, p.capacity - total_rows);
         chunk = max(-p.splits, (total_pages + spare - 1) / spare);
     }
+#if RQ_ATTENTION_TIMELINE
+    if (chunk == -777) return false;   // a use of the choice
+#endif
+    RQ_STAMP(kLookupChosen);
     auto parts_of = [&](int pages) { return max(1, (pages + chunk - 1) / chunk); };
 
     // pass 2: which request owns this item.  Requests are numbered sweep by sweep, first half (lanes 0..31) then second.
@@ -818,10 +861,16 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     // the NEXT kernel of the stream may be scheduled (it waits for this grid's completion in the same way); not
     // earlier, so that at most two kernels of a stream are ever in flight together.
     const bool early_start = p.early_start != 0;
+#if RQ_ATTENTION_TIMELINE
+    if (threadIdx.x == 0 && blockIdx.x < kTimelineCtas)
+        for (int i = 0; i < kTimelineSlots; ++i) g_timeline[p.loop_index & 1][blockIdx.x][i] = 0ull;
+#endif
+    RQ_STAMP_GLOBAL(kAtEntryGlobalNs);
     if (!early_start) {
         pdl_wait();
         pdl_launch_dependents();
     }
+    RQ_STAMP(kAtEntry);   // without the early start: after the wait, so that the phases below are the kernel's own time
 
     // ---- which work item: (row, partition) and the row's request ---------------------------------------
     // Warp 0 looks it up (the lookup is warp-wide work that every warp would repeat) and shares the answer.
@@ -833,6 +882,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
     __syncthreads();
     const WorkItem work = *shared_work;
+    RQ_STAMP(kAfterLookup);
     if (work.row < 0) return;  // nothing to do
     const int row = work.row, request = work.request, split = work.part, splits = work.parts;
     const int history = max(0, work.seq_len - 1);
@@ -916,10 +966,12 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         }
     }
 
+    RQ_STAMP(kAfterStaging);
     if (early_start) {
         pdl_wait();  // the q/k/v rows usually ARE the previous kernel's output
         pdl_launch_dependents();
     }
+    RQ_STAMP(kAfterWait);
     // Head-sharded serving: q depends, through the output projection, on the gathered rows of the previous call, so this
     // is where the call waits for every peer's stores of that call (bounded; ordered before the barrier below).
     if (p.gather_wait && warp == 1 && lane < p.num_peers) wait_for_peers(p, lane, __ldcg(p.gather_state));
@@ -931,6 +983,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         __syncthreads();
     }
     if (warp == 0) prepare_query<D, C::kMean>(p, row, head, qs, misc + 2, misc + 1, warp_acc);
+    RQ_STAMP(kQueryRotated);
     if (warp == 1 && lane < D / 64) {
         // the live token's V row is read at the very end of the CTA: have it in L2 by then
         const __nv_bfloat16* v_row = p.value + static_cast<int64_t>(row) * p.value_stride + head * D + 64 * lane;
@@ -944,6 +997,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     // with zero operands.  (A 3-lanes-per-token variant that streams 10 tokens per step across page boundaries was
     // measured at the same speed: what it saves in idle lanes it spends on per-step address arithmetic that the
     // fixed token positions of this layout fold into immediate offsets.)
+    RQ_STAMP(kQueryShared);
     const int j = lane & 3;              // slice: channels 32j .. 32j+31
     const bool slice_ok = 32 * j < D;
     const int js = slice_ok ? j : 0;     // lanes without a slice read slice 0 and contribute zero
@@ -975,6 +1029,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         for (int c = 0; c < 32; ++c) qmean += qslice[c] * mean[c];
     }
 
+    RQ_STAMP(kAfterQuery);
     // ---- page loop -----------------------------------------------------------------------------------
     float m_biased = kNever, l = 0.f;  // online-softmax state of this lane's token slot (base-2 logits), see below
     uint32_t acc_b[16];                  // half2 partial sums of V, pair 4b+i = (channel 8b+i, channel 8b+i+4)
@@ -1163,6 +1218,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     if (!kBulkCopy) cp_async_wait<0>();
     flush();
 
+    RQ_STAMP(kAfterPages);
     // ---- fold the 8 token slots of the warp ------------------------------------------------------------
     const float m = m_biased + kWeightBits;  // kNever stays kNever
     float m_warp = m;
@@ -1203,6 +1259,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
     }
     __syncthreads();
 
+    RQ_STAMP(kAfterWarpFold);
     // ---- fold the warps of the CTA: thread c owns channel c ---------------------------------------------
     float part_m = kNever;
 #pragma unroll
@@ -1238,6 +1295,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
             misc[0] = last ? 1.f : 0.f;
         }
         __syncthreads();
+        RQ_STAMP(kAfterTicket);
         if (misc[0] == 0.f) return;
         const float* all = p.partials + (static_cast<int64_t>(work.first) * heads + head) * (D + 2);
         // One pass, eight partitions' (max, denominator, value) loads in flight at a time; the partitions are merged like
@@ -1273,6 +1331,7 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         }
     }
 
+    RQ_STAMP(kAfterPartitions);
     // ---- live token (its score was computed in the prologue), normalisation, optional inverse value rotation, store ---
     const float live = misc[1];
     const float total_m = fmaxf(part_m, live);
@@ -1319,6 +1378,8 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         const int64_t gathered = static_cast<int64_t>(row) * p.gather_stride + (p.gather_head_offset + head) * D + tid;
         for (int peer = 0; peer < p.num_peers; ++peer) p.peer_output[peer][gathered] = result;
     }
+    RQ_STAMP(kAtExit);
+    RQ_STAMP_GLOBAL(kAtExitGlobalNs);
     if (p.gather_publish) {
         // The CTA that finishes the call's last (row, head) tells every GPU that this rank's rows are in place.
         // Every CTA: barrier (orders all of its threads' peer stores before thread 0's fence), a device-scope fence, a
@@ -1416,6 +1477,18 @@ cudaError_t launch_records(const AttentionVariant& v, const AttentionParams& p, 
 }  // namespace
 
 // One translation unit per head dimension (they compile in parallel).
+#if RQ_ATTENTION_TIMELINE
+// Copies the timeline array (uint64 [2][kTimelineCtas][kTimelineSlots]) of this head dimension's kernels to the host.
+#if RQ_ATTENTION_HEAD_DIM == 128
+extern "C" int rq_timeline_d128(void* host, size_t bytes) {
+#else
+extern "C" int rq_timeline_d96(void* host, size_t bytes) {
+#endif
+    if (bytes != sizeof(g_timeline)) return -1;
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
+}
+#endif
+
 #if RQ_ATTENTION_HEAD_DIM == 128
 cudaError_t launch_attention_d128(const AttentionVariant& v, const AttentionParams& p, cudaStream_t stream) {
     return v.page_tokens == 16 ? launch_records<128, 16>(v, p, stream) : launch_records<128, 32>(v, p, stream);

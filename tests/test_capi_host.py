@@ -76,3 +76,9 @@ def test_workspace_size_and_split_heuristic(built_library):
     # dense rotations are applied inside the quantizer: no scratch for any rotation kind
     assert lib.rq_quantize_workspace_bytes(ctypes.byref(spec), 100, 1, 1) == 0
     assert lib.rq_quantize_workspace_bytes(ctypes.byref(spec), 100, 2, 2) == 0
+
+
+def test_regular_build_carries_no_phase_timestamps(built_library):
+    """The phase timestamps of the attention kernels exist only in the separate timeline build (build.py --timeline)."""
+    lib = _lib.load()
+    assert not hasattr(lib, "rq_timeline_d128") and not hasattr(lib, "rq_timeline_d96")
