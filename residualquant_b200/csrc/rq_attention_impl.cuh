@@ -594,7 +594,7 @@ __device__ __forceinline__ void unrotate_history(const AttentionParams& p, int h
 enum TimelineSlot {
     kAtEntryGlobalNs = 0, kAtEntry, kAfterLookup, kAfterStaging, kAfterWait, kAfterQuery, kAfterPages, kAfterWarpFold,
     kAfterTicket, kAfterPartitions, kAtExit, kAtExitGlobalNs, kLookupLoadsIssued, kLookupLoadsArrived, kLookupChosen,
-    kQueryRotated, kQueryShared, kTimelineSlots
+    kQueryRotated, kQueryShared, kSmId, kTimelineSlots
 };
 constexpr int kTimelineCtas = 4096;
 #if RQ_ATTENTION_TIMELINE
@@ -866,6 +866,13 @@ __global__ void __launch_bounds__(kThreads, C::kMinBlocks) attention_kernel(cons
         for (int i = 0; i < kTimelineSlots; ++i) g_timeline[p.loop_index & 1][blockIdx.x][i] = 0ull;
 #endif
     RQ_STAMP_GLOBAL(kAtEntryGlobalNs);
+#if RQ_ATTENTION_TIMELINE
+    if (threadIdx.x == 0 && blockIdx.x < kTimelineCtas) {
+        uint32_t sm;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
+        g_timeline[p.loop_index & 1][blockIdx.x][kSmId] = sm + 1u;   // which SM the CTA ran on (+1: 0 means not launched)
+    }
+#endif
     if (!early_start) {
         pdl_wait();
         pdl_launch_dependents();

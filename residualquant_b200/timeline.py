@@ -27,7 +27,7 @@ from . import _cuda, _lib, rotation, synth
 
 SLOTS = ("entry_global_ns", "entry", "after_lookup", "after_staging", "after_wait", "after_query", "after_pages",
          "after_warp_fold", "after_ticket", "after_partitions", "exit", "exit_global_ns", "lookup_loads_issued",
-         "lookup_loads_arrived", "lookup_chosen", "query_rotated", "query_shared")
+         "lookup_loads_arrived", "lookup_chosen", "query_rotated", "query_shared", "sm_id_plus_one")
 TIMELINE_CTAS = 4096
 PHASES = (  # name, from slot, to slot
     ("work lookup", "entry", "after_lookup"),
@@ -153,7 +153,12 @@ def main():
             if ok.any():
                 us = (hi[ok] - lo[ok]) / ghz / 1000.0
                 phases[label] = [round(float(np.median(us)), 2), round(float(us.max()), 2)]
+        sms = t[worked, index["sm_id_plus_one"]] - 1
+        per_sm = np.bincount(sms, minlength=1)
+        histogram = {int(n): int(c) for n, c in zip(*np.unique(per_sm, return_counts=True))}
         report["launches"].append({"ctas_launched": int(launched.sum()), "ctas_with_work": int(worked.sum()), "phases": phases,
+                                   "working_ctas_per_sm": histogram,
+                                   "sm_of_first_ctas": [int(v) for v in (t[:12, index["sm_id_plus_one"]] - 1)],
                                    "first_entry_ns": int(t[launched, index["entry_global_ns"]].min()),
                                    "last_exit_ns": int(t[:, index["exit_global_ns"]].max())})
     first, second = report["launches"]
@@ -167,6 +172,7 @@ def main():
     print(f"CTAs launched {second['ctas_launched']}, with work {second['ctas_with_work']}; the next launch's CTAs enter "
           f"{report['overlap']['second_enters_before_first_ends_us']} us before this one ends; period "
           f"{report['overlap']['end_to_end_period_us']} us")
+    print(f"SMs by number of working CTAs they ran {second['working_ctas_per_sm']}; SMs of CTAs 0..11: {second['sm_of_first_ctas']}")
     print(f"{'phase (second of two consecutive launches)':46s} {'median us':>10s} {'max us':>8s}")
     for label, (median, worst) in second["phases"].items():
         print(f"{label:46s} {median:10.2f} {worst:8.2f}")
