@@ -1,4 +1,4 @@
-// Packed paged decode attention (anchor reference mode), one launch per call.
+// Packed paged decode attention (anchor and adjacent reference modes), one launch per call.
 //
 // Replaces the reference's three kernels -- attention_prepare_kernel, attention_kernel, attention_merge_kernel
 // (plugins/residual_quantization/csrc/attention/prepare.cuh:391-430, compute.cuh:226-727, merge.cuh:9-84) --
@@ -28,11 +28,15 @@
 //          live token, undoes an explicit value rotation and stores bf16.  No second launch, no spin wait.
 //   launch: as a programmatic dependent of the previous kernel of the stream.  Every CTA waits for the PREVIOUS kernel
 //          to complete (griddepcontrol.wait) before it reads anything, then lets the NEXT kernel be scheduled
-//          (griddepcontrol.launch_dependents) -- so launch latency and CTA scheduling overlap the previous kernel.  When the caller promises that this call's metadata and cache pages were not written by that
-//          previous kernel (early_start), the work lookup, the page-table fetch and the first page copies run BEFORE the
-//          wait as well (through L2 only: ld.global.cg / cp.async.cg), and only the q/k/v rows are read after it.
+//          (griddepcontrol.launch_dependents) -- so launch latency and CTA scheduling overlap the previous kernel.
+//          When the caller promises that this call's metadata and cache pages were not written by that previous kernel
+//          (early_start), the work lookup, the page-table fetch and the first page copies run BEFORE the wait as well
+//          (through L2 only: ld.global.cg / cp.async.cg), and only the q/k/v rows are read after it.
+//   gather: with KV heads sharded over GPUs the finished rows also go into every GPU's gathered buffer (peer stores); the
+//          CTA that finishes the call's last row can publish completion and wait for the peers (bounded).
 //
-// The query rotation (signed Walsh-Hadamard) is fused into the prologue of every CTA (128 values, one warp).
+// The query rotation is fused into the prologue of every CTA: a signed Walsh-Hadamard transform (128 values, one warp),
+// or, for a dense learned matrix, a row-times-matrix product shared by the four warps.
 //
 // In the bulk-copy build every wait on an mbarrier is bounded; on expiry the kernel raises the workspace status word,
 // drains what it can and returns.  The default build has no wait that can fail.
