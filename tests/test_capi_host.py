@@ -82,3 +82,20 @@ def test_regular_build_carries_no_phase_timestamps(built_library):
     """The phase timestamps of the attention kernels exist only in the separate timeline build (build.py --timeline)."""
     lib = _lib.load()
     assert not hasattr(lib, "rq_timeline_d128") and not hasattr(lib, "rq_timeline_d96")
+
+
+def test_timeline_script_and_kernel_agree_on_the_slots():
+    """The phase-timestamp slots are named twice: in the kernel's enum and in the script that reads them back."""
+    import os
+    import re
+
+    from residualquant_b200 import timeline
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    source = open(os.path.join(root, "residualquant_b200", "csrc", "rq_attention_impl.cuh")).read()
+    body = re.search(r"enum TimelineSlot \{(.*?)\};", source, re.S).group(1)
+    names = [n.split("=")[0].strip() for n in body.replace("\n", " ").split(",") if n.strip()]
+    assert names[-1] == "kTimelineSlots" and len(names) - 1 == len(timeline.SLOTS)
+    assert int(re.search(r"kTimelineCtas = (\d+)", source).group(1)) == timeline.TIMELINE_CTAS
+    used = {slot for _, start, stop in timeline.PHASES for slot in (start, stop)}
+    assert used <= set(timeline.SLOTS)
