@@ -218,7 +218,8 @@ typedef struct RqAttentionArgs {
 int32_t rq_attention_default_splits(int32_t num_query_rows, int32_t heads, int32_t max_blocks_per_request,
                                     int32_t page_tokens);
 /* Work items (row partitions) per head that a num_splits == 0 call provides for: the rows plus spare items that long
- * rows are cut into.  A pure host function of its arguments and the SM count -- never of sequence lengths or of the
+ * rows are cut into (one wave of resident CTAs; room for two partitions per row where the unsplit rows would leave
+ * a second wave nearly empty).  A pure host function of its arguments and the SM count -- never of sequence lengths or of the
  * page-table width -- so the grid is stable across CUDA-graph replays (attention/launch.cuh:53-80 of the reference
  * sizes its work list the same way). */
 int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads);
