@@ -303,6 +303,9 @@ int32_t rq_attention_work_capacity(int32_t num_query_rows, int32_t heads) {
     // 236 against 280 us), so such a batch gets room for them.
     const int64_t unsplit = static_cast<int64_t>(num_query_rows) * heads;
     if (unsplit > slots && 5 * unsplit < 8 * slots && spare < num_query_rows) spare = num_query_rows;
+    // Beyond that the rows alone fill the GPU for several waves and only an outlier row is ever cut: half a wave of spare
+    // items is plenty for it, and every spare CTA that finds no work still costs a slot for a microsecond or two.
+    if (5 * unsplit >= 8 * slots) spare = (spare + 1) / 2 < 15 ? 15 : (spare + 1) / 2;
     const int64_t capacity = num_query_rows + spare;
     return capacity > 0x7fffffff / 64 ? 0 : static_cast<int32_t>(capacity);
 }
