@@ -66,6 +66,9 @@ def test_workspace_size_and_split_heuristic(built_library):
     # num_splits 0: sized for the work capacity, which depends on rows, heads and the SM count only (148 without a GPU)
     capacity = lib.rq_attention_work_capacity(64, 16)
     assert capacity == 64 + ((4 * 148 + 15) // 16 + 1) // 2        # several waves of rows: half a wave of spare items
+    assert lib.rq_attention_work_capacity(32, 16) == 32 + 37           # less than a wave of rows: one wave of spare items
+    assert lib.rq_attention_work_capacity(40, 16) == 80                # 1.08 waves of rows: room for two partitions per row
+    assert lib.rq_attention_work_capacity(1, 16) == 16                 # a single row: its sixteen partitions
     assert lib.rq_attention_workspace_bytes(64, 16, 128, 0) == one + (capacity * 16 * 130 * 4 + 255) // 256 * 256
     assert lib.rq_attention_work_capacity(1, 16) == 16 and lib.rq_attention_work_capacity(0, 16) == 0
     assert lib.rq_attention_workspace_bytes(64, 16, 128, -100000) == 0
